@@ -1,0 +1,9 @@
+"""B200-native SSD chunked scan (forward + backward) behind the reference operator interface.
+
+Exports mirror src/kernels/__init__.py:7,18 of the reference for this path.
+"""
+from .ssd_scan import (FusedSSDScan, LazySSDCache, fused_ssd_scan, set_eager_cache, set_kernel_path, ssd_mamba2)
+from .workloads import CONFIGS, SSDConfig, make_inputs, make_reference_test_inputs, shrink
+
+__all__ = ["FusedSSDScan", "LazySSDCache", "fused_ssd_scan", "set_eager_cache", "set_kernel_path", "ssd_mamba2",
+           "CONFIGS", "SSDConfig", "make_inputs", "make_reference_test_inputs", "shrink"]

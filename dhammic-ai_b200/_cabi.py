@@ -1,0 +1,124 @@
+"""ctypes binding of the C-ABI library (include/ssd_b200.h).
+
+There is no CPU fallback: if the library is missing, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+ABI_VERSION = 1
+F32, BF16 = 0, 1
+PASS_FWD, PASS_BWD = 0, 1
+PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
+OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA, EDEVICE = 0, -1, -2, -3, -4, -5
+
+EXPORTS = (
+    "ssd_b200_abi_version", "ssd_b200_last_error", "ssd_b200_workspace_bytes", "ssd_b200_resolve_path",
+    "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix",
+    "ssd_b200_launch_count", "ssd_b200_profile_enable", "ssd_b200_profile_kernels", "ssd_b200_profile_kernel_name",
+    "ssd_b200_profile_read",
+)
+
+
+class Shape(C.Structure):
+    _fields_ = [("abi_version", C.c_int32), ("dtype", C.c_int32), ("a_dtype", C.c_int32), ("path", C.c_int32),
+                ("batch", C.c_int64), ("seqlen", C.c_int64), ("nheads", C.c_int64), ("headdim", C.c_int64),
+                ("dstate", C.c_int64), ("ngroups", C.c_int64), ("chunk", C.c_int64)]
+
+
+class FwdArgs(C.Structure):
+    _fields_ = [("shape", Shape), ("x", C.c_void_p), ("a", C.c_void_p), ("dt", C.c_void_p), ("A_head", C.c_void_p),
+                ("D", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("init", C.c_void_p), ("y", C.c_void_p),
+                ("final_state", C.c_void_p), ("a_cumsum", C.c_void_p), ("cumsum_is_input", C.c_int32),
+                ("reserved", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class BwdArgs(C.Structure):
+    _fields_ = [("shape", Shape), ("x", C.c_void_p), ("a", C.c_void_p), ("dt", C.c_void_p), ("A_head", C.c_void_p),
+                ("D", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("init", C.c_void_p),
+                ("a_cumsum", C.c_void_p), ("dy", C.c_void_p), ("dfinal", C.c_void_p), ("dx", C.c_void_p),
+                ("dB", C.c_void_p), ("dC", C.c_void_p), ("da", C.c_void_p), ("ddt", C.c_void_p),
+                ("dA_head", C.c_void_p), ("dD", C.c_void_p), ("dinit", C.c_void_p),
+                ("cumsum_is_input", C.c_int32), ("reserved", C.c_int32), ("workspace", C.c_void_p),
+                ("workspace_bytes", C.c_size_t)]
+
+
+_lib = None
+
+
+def library_path() -> Path:
+    return Path(__file__).resolve().parent / "csrc" / "libssd_b200.so"
+
+
+def load() -> C.CDLL:
+    """Load libssd_b200.so (once).  Raises ImportError when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not path.exists():
+        raise ImportError(f"{path} is missing: build it first (python {path.parent.parent / 'build.py'}); "
+                          "there is no fallback implementation")
+    lib = C.CDLL(str(path))
+    lib.ssd_b200_abi_version.restype = C.c_int
+    lib.ssd_b200_last_error.restype = C.c_char_p
+    lib.ssd_b200_workspace_bytes.restype = C.c_size_t
+    lib.ssd_b200_workspace_bytes.argtypes = [C.POINTER(Shape), C.c_int]
+    lib.ssd_b200_resolve_path.restype = C.c_int
+    lib.ssd_b200_resolve_path.argtypes = [C.POINTER(Shape)]
+    lib.ssd_b200_fwd.restype = C.c_int
+    lib.ssd_b200_fwd.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
+    lib.ssd_b200_bwd.restype = C.c_int
+    lib.ssd_b200_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
+    lib.ssd_b200_materialize_cache.restype = C.c_int
+    lib.ssd_b200_materialize_cache.argtypes = [C.POINTER(Shape), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                               C.c_void_p]
+    lib.ssd_b200_state_prefix.restype = C.c_int
+    lib.ssd_b200_state_prefix.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                          C.c_int64, C.c_int64, C.c_int32, C.c_void_p]
+    lib.ssd_b200_launch_count.restype = C.c_longlong
+    lib.ssd_b200_profile_enable.argtypes = [C.c_int]
+    lib.ssd_b200_profile_kernel_name.restype = C.c_char_p
+    lib.ssd_b200_profile_kernel_name.argtypes = [C.c_int]
+    lib.ssd_b200_profile_read.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_longlong), C.c_int]
+    if lib.ssd_b200_abi_version() != ABI_VERSION:
+        raise ImportError(f"{path}: ABI version {lib.ssd_b200_abi_version()} != {ABI_VERSION}; rebuild")
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().ssd_b200_last_error().decode()
+
+
+def check(rc: int) -> None:
+    """Turn a negative return code into the exception type the reference operator raises."""
+    if rc >= 0:
+        return
+    msg = last_error()
+    if rc == EINVAL and "not divisible by chunk_size" in msg:
+        raise AssertionError(msg)            # reference: src/kernels/ssd_scan.py:348-350
+    if rc == EINVAL:
+        raise ValueError(msg)
+    if rc == EUNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise RuntimeError(f"ssd_b200 error {rc}: {msg}")
+
+
+def launch_count() -> int:
+    return int(load().ssd_b200_launch_count())
+
+
+def profile_enable(on: bool) -> None:
+    load().ssd_b200_profile_enable(1 if on else 0)
+
+
+def profile_read() -> dict[str, tuple[float, int]]:
+    """Per-kernel (total ms, launches) since the last read; waits for the recorded events."""
+    lib = load()
+    n = lib.ssd_b200_profile_kernels()
+    ms = (C.c_float * n)()
+    cnt = (C.c_longlong * n)()
+    check(lib.ssd_b200_profile_read(ms, cnt, n))
+    return {lib.ssd_b200_profile_kernel_name(i).decode(): (float(ms[i]), int(cnt[i])) for i in range(n) if cnt[i]}

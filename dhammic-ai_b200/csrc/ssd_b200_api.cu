@@ -1,0 +1,441 @@
+// C-ABI entry points of the SSD chunked scan library: argument validation, workspace
+// carving and kernel dispatch.  See include/ssd_b200.h for the contract.
+#include "../../include/ssd_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "ssd_simt.cuh"
+#include "ssd_tc.cuh"
+
+#include <atomic>
+#include <vector>
+
+namespace ssd {
+namespace prof {
+// Launch accounting and optional per-kernel CUDA-event timing (benchmark use, one host thread).
+const char* const kNames[K_COUNT] = {
+    "chunk_cumsum", "chunk_state", "state_passing", "chunk_scan", "chunk_dstate", "state_passing_rev",
+    "bwd_row", "bwd_col", "decay_grad", "reduce_batch", "cache_L", "cache_decay_chunk", "state_prefix",
+    "tc_fwd_walk", "tc_bwd_state", "tc_bwd_walk", "tc_aux"};
+std::atomic<long long> g_launches{0};
+bool g_enabled = false;
+struct Rec {
+    int k;
+    cudaEvent_t a, b;
+};
+std::vector<Rec> g_recs;
+void begin(int k, cudaStream_t st) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (!g_enabled) return;
+    Rec r{k, nullptr, nullptr};
+    if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+    cudaEventRecord(r.a, st);
+    g_recs.push_back(r);
+}
+void end(cudaStream_t st) {
+    if (!g_enabled || g_recs.empty()) return;
+    cudaEventRecord(g_recs.back().b, st);
+}
+}  // namespace prof
+}  // namespace ssd
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+
+int check_shape(const ssd_b200_shape* s) {
+    if (!s) return fail(SSD_B200_EINVAL, "shape is null");
+    if (s->abi_version != SSD_B200_ABI_VERSION)
+        return fail(SSD_B200_EINVAL, "abi_version %d != %d", s->abi_version, SSD_B200_ABI_VERSION);
+    if (s->dtype != SSD_B200_F32 && s->dtype != SSD_B200_BF16) return fail(SSD_B200_EINVAL, "bad dtype %d", s->dtype);
+    if (s->a_dtype != SSD_B200_F32 && s->a_dtype != SSD_B200_BF16)
+        return fail(SSD_B200_EINVAL, "bad a_dtype %d", s->a_dtype);
+    if (s->batch <= 0 || s->seqlen <= 0 || s->nheads <= 0 || s->headdim <= 0 || s->dstate <= 0 || s->ngroups <= 0 ||
+        s->chunk <= 0)
+        return fail(SSD_B200_EINVAL, "non-positive dimension");
+    if (s->seqlen % s->chunk != 0)
+        return fail(SSD_B200_EINVAL, "sequence length %lld not divisible by chunk_size %lld", (long long)s->seqlen,
+                    (long long)s->chunk);
+    if (s->nheads % s->ngroups != 0)
+        return fail(SSD_B200_EINVAL, "nheads %lld not divisible by ngroups %lld", (long long)s->nheads,
+                    (long long)s->ngroups);
+    if (s->batch * (s->seqlen / s->chunk) > 65535 * 32 || s->batch > 65535 || s->nheads > 65535)
+        return fail(SSD_B200_EUNSUPPORTED, "grid dimension too large");
+    if ((double)s->batch * s->seqlen * s->nheads * s->headdim > 2.0e18) return fail(SSD_B200_EINVAL, "size overflow");
+    if (s->path < SSD_B200_PATH_AUTO || s->path > SSD_B200_PATH_TC) return fail(SSD_B200_EINVAL, "bad path %d", s->path);
+    return 0;
+}
+
+ssd::Dims dims_of(const ssd_b200_shape& s) {
+    ssd::Dims d;
+    d.b = (int)s.batch;
+    d.T = (int)s.seqlen;
+    d.h = (int)s.nheads;
+    d.p = (int)s.headdim;
+    d.n = (int)s.dstate;
+    d.g = (int)s.ngroups;
+    d.l = (int)s.chunk;
+    d.c = d.T / d.l;
+    d.hpg = d.h / d.g;
+    return d;
+}
+
+bool simt_supported(const ssd_b200_shape& s, const char** why) {
+    if (s.headdim > 128) {
+        *why = "SIMT path needs headdim <= 128";
+        return false;
+    }
+    if (s.dstate > 256) {
+        *why = "SIMT path needs d_state <= 256";
+        return false;
+    }
+    if (s.batch * (s.seqlen / s.chunk) > 65535) {
+        *why = "SIMT path needs batch * nchunks <= 65535";
+        return false;
+    }
+    if (s.chunk > 1024 || s.chunk * (s.nheads + 1) * 4 > 200 * 1024) {
+        *why = "SIMT path: chunk * nheads too large for the cumsum tile";
+        return false;
+    }
+    return true;
+}
+
+int resolve_path(const ssd_b200_shape& s) {
+    const char* why = "";
+    const bool tc = ssd::tc::supported(s.dtype, (int)s.seqlen, (int)s.nheads, (int)s.headdim, (int)s.dstate,
+                                       (int)s.ngroups, (int)s.chunk);
+    if (s.path == SSD_B200_PATH_TC) {
+        if (!tc) return fail(SSD_B200_EUNSUPPORTED, "tensor-core path does not cover this shape/dtype");
+        return SSD_B200_PATH_TC;
+    }
+    if (s.path == SSD_B200_PATH_AUTO && tc) return SSD_B200_PATH_TC;
+    if (!simt_supported(s, &why)) return fail(SSD_B200_EUNSUPPORTED, "%s", why);
+    return SSD_B200_PATH_SIMT;
+}
+
+// Workspace layout of the SIMT path (all fp32, each block 256-byte aligned).
+struct SimtWs {
+    size_t states, dstates, final_state, g_row, g_col, ddtx, dAh_part, dD_part, dinit, total;
+};
+
+SimtWs simt_ws(const ssd::Dims& d, int pass) {
+    SimtWs w{};
+    size_t off = 0;
+    const size_t st = (size_t)d.b * d.c * d.h * d.p * d.n * 4;
+    const size_t bhpn = (size_t)d.b * d.h * d.p * d.n * 4;
+    const size_t bht = (size_t)d.b * d.h * d.T * 4;
+    const size_t bh = (size_t)d.b * d.h * 4;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off += align_up(bytes);
+        return o;
+    };
+    w.states = take(st);
+    if (pass == SSD_B200_PASS_BWD) {
+        w.dstates = take(st);
+        w.final_state = take(bhpn);
+        w.dinit = take(bhpn);
+        w.g_row = take(bht);
+        w.g_col = take(bht);
+        w.ddtx = take(bht);
+        w.dAh_part = take(bh);
+        w.dD_part = take(bh);
+    }
+    w.total = off;
+    return w;
+}
+
+#define CUDA_LAUNCH_CHECK(what)                                                              \
+    do {                                                                                     \
+        cudaError_t e_ = cudaGetLastError();                                                 \
+        if (e_ != cudaSuccess) return fail(SSD_B200_ECUDA, "%s: %s", what, cudaGetErrorString(e_)); \
+    } while (0)
+
+template <class K>
+int set_smem(K kernel, size_t bytes, const char* name) {
+    if (bytes > 227 * 1024) return fail(SSD_B200_EUNSUPPORTED, "%s needs %zu bytes of shared memory", name, bytes);
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return fail(SSD_B200_ECUDA, "%s: set smem: %s", name, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+template <class T>
+int simt_forward_states(const ssd::simt::Params& P, cudaStream_t st) {
+    using namespace ssd::simt;
+    const ssd::Dims& d = P.d;
+    dim3 gs((d.n + TS - 1) / TS, (d.p + TS - 1) / TS, d.b * d.c * d.h);
+    SSD_LAUNCH(ssd::prof::K_CHUNK_STATE, st, chunk_state_kernel<T><<<gs, NTHR, 0, st>>>(P, 0));
+    CUDA_LAUNCH_CHECK("chunk_state");
+    const size_t pn = (size_t)d.p * d.n;
+    dim3 gp((unsigned)((pn + NTHR - 1) / NTHR), d.h, d.b);
+    SSD_LAUNCH(ssd::prof::K_STATE_PASS, st, state_passing_kernel<<<gp, NTHR, 0, st>>>(P, 0));
+    CUDA_LAUNCH_CHECK("state_passing");
+    return 0;
+}
+
+int launch_cumsum(const ssd::simt::Params& P, cudaStream_t st) {
+    using namespace ssd::simt;
+    const ssd::Dims& d = P.d;
+    size_t sm = (size_t)d.l * (d.h + 1) * 4;
+    if (int rc = set_smem(chunk_cumsum_kernel, sm, "chunk_cumsum")) return rc;
+    SSD_LAUNCH(ssd::prof::K_CUMSUM, st, chunk_cumsum_kernel<<<dim3(d.c, d.b), NTHR, sm, st>>>(P));
+    CUDA_LAUNCH_CHECK("chunk_cumsum");
+    return 0;
+}
+
+template <class T>
+int simt_fwd(const ssd_b200_fwd_args* a, cudaStream_t st) {
+    using namespace ssd::simt;
+    Params P{};
+    P.d = dims_of(a->shape);
+    const ssd::Dims& d = P.d;
+    SimtWs w = simt_ws(d, SSD_B200_PASS_FWD);
+    if (a->workspace_bytes < w.total) return fail(SSD_B200_EWORKSPACE, "workspace %zu < %zu", a->workspace_bytes, w.total);
+    char* ws = (char*)a->workspace;
+    P.x = a->x; P.a = a->a; P.dt = a->dt; P.A_head = a->A_head; P.D = a->D; P.B = a->B; P.C = a->C;
+    P.init = a->init; P.cum = a->a_cumsum; P.states = (float*)(ws + w.states);
+    P.final_state = a->final_state; P.y = a->y; P.a_is_bf16 = a->shape.a_dtype == SSD_B200_BF16;
+    if (!a->cumsum_is_input)
+        if (int rc = launch_cumsum(P, st)) return rc;
+    if (int rc = simt_forward_states<T>(P, st)) return rc;
+    const int PT = (d.p + TS - 1) / TS;
+    const int hrows = d.p > TS ? d.p : TS;
+    size_t sm = ((size_t)TS * (d.n + 1) + (size_t)hrows * (d.n + 1) + (size_t)TS * (PT * TS + 1) + TS * (TS + 1) + 2 * TS) * 4;
+    dim3 g((d.l + TS - 1) / TS, d.h, d.b * d.c);
+    if (PT == 1) {
+        if (int rc = set_smem(chunk_scan_kernel<T, 1>, sm, "chunk_scan")) return rc;
+        SSD_LAUNCH(ssd::prof::K_CHUNK_SCAN, st, chunk_scan_kernel<T, 1><<<g, NTHR, sm, st>>>(P));
+    } else {
+        if (int rc = set_smem(chunk_scan_kernel<T, 2>, sm, "chunk_scan")) return rc;
+        SSD_LAUNCH(ssd::prof::K_CHUNK_SCAN, st, chunk_scan_kernel<T, 2><<<g, NTHR, sm, st>>>(P));
+    }
+    CUDA_LAUNCH_CHECK("chunk_scan");
+    return 0;
+}
+
+template <class T, int NTN>
+int launch_bwd_row(const ssd::simt::Params& P, cudaStream_t st) {
+    using namespace ssd::simt;
+    const ssd::Dims& d = P.d;
+    const int hrows = d.p > TS ? d.p : TS;
+    const int pp_pad = (d.p + 3) / 4 * 4;
+    size_t sm = ((size_t)TS * (d.n + 1) + (size_t)hrows * (d.n + 1) + 2 * (size_t)TS * (pp_pad + 1) + TS * (TS + 1) + 2 * TS) * 4;
+    if (int rc = set_smem(bwd_row_kernel<T, NTN>, sm, "bwd_row")) return rc;
+    SSD_LAUNCH(ssd::prof::K_BWD_ROW, st, bwd_row_kernel<T, NTN><<<dim3((d.l + TS - 1) / TS, d.g, d.b * d.c), NTHR, sm, st>>>(P));
+    CUDA_LAUNCH_CHECK("bwd_row");
+    return 0;
+}
+
+template <class T, int NTN, int PT>
+int launch_bwd_col(const ssd::simt::Params& P, cudaStream_t st) {
+    using namespace ssd::simt;
+    const ssd::Dims& d = P.d;
+    const int hrows = d.p > TS ? d.p : TS;
+    size_t sm = ((size_t)TS * (d.n + 1) + (size_t)hrows * (d.n + 1) + 2 * (size_t)TS * (PT * TS + 1) + 2 * TS * (TS + 1) + 3 * TS) * 4;
+    if (int rc = set_smem(bwd_col_kernel<T, NTN, PT>, sm, "bwd_col")) return rc;
+    SSD_LAUNCH(ssd::prof::K_BWD_COL, st, bwd_col_kernel<T, NTN, PT><<<dim3((d.l + TS - 1) / TS, d.g, d.b * d.c), NTHR, sm, st>>>(P));
+    CUDA_LAUNCH_CHECK("bwd_col");
+    return 0;
+}
+
+template <class T>
+int simt_bwd(const ssd_b200_bwd_args* a, cudaStream_t st) {
+    using namespace ssd::simt;
+    Params P{};
+    P.d = dims_of(a->shape);
+    const ssd::Dims& d = P.d;
+    SimtWs w = simt_ws(d, SSD_B200_PASS_BWD);
+    if (a->workspace_bytes < w.total) return fail(SSD_B200_EWORKSPACE, "workspace %zu < %zu", a->workspace_bytes, w.total);
+    char* ws = (char*)a->workspace;
+    P.x = a->x; P.a = a->a; P.dt = a->dt; P.A_head = a->A_head; P.D = a->D; P.B = a->B; P.C = a->C;
+    P.dy = a->dy; P.init = a->init; P.dfinal = a->dfinal; P.cum = (float*)a->a_cumsum;
+    P.states = (float*)(ws + w.states); P.dstates = (float*)(ws + w.dstates);
+    P.final_state = (float*)(ws + w.final_state);
+    P.dinit = a->dinit ? a->dinit : (float*)(ws + w.dinit);
+    P.dx = a->dx; P.dB = a->dB; P.dC = a->dC;
+    P.g_row = (float*)(ws + w.g_row); P.g_col = (float*)(ws + w.g_col); P.ddtx = (float*)(ws + w.ddtx);
+    P.da = a->cumsum_is_input ? nullptr : a->da;
+    P.ddt = a->ddt; P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = (float*)(ws + w.dD_part);
+    P.a_is_bf16 = a->shape.a_dtype == SSD_B200_BF16;
+    // states entering each chunk (recomputed) and the final state
+    if (int rc = simt_forward_states<T>(P, st)) return rc;
+    // local state gradients and the reverse recurrence
+    dim3 gs((d.n + TS - 1) / TS, (d.p + TS - 1) / TS, d.b * d.c * d.h);
+    SSD_LAUNCH(ssd::prof::K_CHUNK_DSTATE, st, chunk_state_kernel<T><<<gs, NTHR, 0, st>>>(P, 1));
+    CUDA_LAUNCH_CHECK("chunk_dstate");
+    const size_t pn = (size_t)d.p * d.n;
+    SSD_LAUNCH(ssd::prof::K_STATE_PASS_REV, st, state_passing_kernel<<<dim3((unsigned)((pn + NTHR - 1) / NTHR), d.h, d.b), NTHR, 0, st>>>(P, 1));
+    CUDA_LAUNCH_CHECK("state_passing_rev");
+    const int NTN = (d.n + TS - 1) / TS, PT = (d.p + TS - 1) / TS;
+    int rc = 0;
+    if (NTN <= 1) rc = launch_bwd_row<T, 1>(P, st);
+    else if (NTN == 2) rc = launch_bwd_row<T, 2>(P, st);
+    else rc = launch_bwd_row<T, 4>(P, st);
+    if (rc) return rc;
+    if (PT == 1) {
+        if (NTN <= 1) rc = launch_bwd_col<T, 1, 1>(P, st);
+        else if (NTN == 2) rc = launch_bwd_col<T, 2, 1>(P, st);
+        else rc = launch_bwd_col<T, 4, 1>(P, st);
+    } else {
+        if (NTN <= 1) rc = launch_bwd_col<T, 1, 2>(P, st);
+        else if (NTN == 2) rc = launch_bwd_col<T, 2, 2>(P, st);
+        else rc = launch_bwd_col<T, 4, 2>(P, st);
+    }
+    if (rc) return rc;
+    SSD_LAUNCH(ssd::prof::K_DECAY, st, decay_grad_kernel<T><<<dim3(d.h, d.b), NTHR, 0, st>>>(P));
+    CUDA_LAUNCH_CHECK("decay_grad");
+    if (a->dt) {
+        SSD_LAUNCH(ssd::prof::K_REDUCE, st, reduce_batch_kernel<<<(d.h + 127) / 128, 128, 0, st>>>(P.dAh_part, a->dA_head, d.b, d.h));
+        if (a->D) SSD_LAUNCH(ssd::prof::K_REDUCE, st, reduce_batch_kernel<<<(d.h + 127) / 128, 128, 0, st>>>(P.dD_part, a->dD, d.b, d.h));
+        CUDA_LAUNCH_CHECK("reduce_batch");
+    }
+    return 0;
+}
+
+int check_forms(const void* a, const float* dt, const float* A_head, const float* D) {
+    if (a) {
+        if (dt || A_head || D) return fail(SSD_B200_EINVAL, "give either a, or dt and A_head (and D), not both");
+    } else {
+        if (!dt || !A_head) return fail(SSD_B200_EINVAL, "need a, or both dt and A_head");
+    }
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ssd_b200_abi_version(void) { return SSD_B200_ABI_VERSION; }
+
+long long ssd_b200_launch_count(void) { return ssd::prof::g_launches.load(); }
+
+int ssd_b200_profile_enable(int on) {
+    ssd::prof::g_enabled = on != 0;
+    return 0;
+}
+
+int ssd_b200_profile_kernels(void) { return ssd::prof::K_COUNT; }
+
+const char* ssd_b200_profile_kernel_name(int idx) {
+    return (idx >= 0 && idx < ssd::prof::K_COUNT) ? ssd::prof::kNames[idx] : "";
+}
+
+int ssd_b200_profile_read(float* ms, long long* launches, int n) {
+    if (!ms || !launches || n < ssd::prof::K_COUNT) return fail(SSD_B200_EINVAL, "profile_read needs %d slots", ssd::prof::K_COUNT);
+    for (int i = 0; i < n; ++i) { ms[i] = 0.f; launches[i] = 0; }
+    int rc = 0;
+    for (auto& r : ssd::prof::g_recs) {
+        float t = 0.f;
+        if (cudaEventSynchronize(r.b) != cudaSuccess || cudaEventElapsedTime(&t, r.a, r.b) != cudaSuccess) rc = SSD_B200_ECUDA;
+        ms[r.k] += t;
+        launches[r.k] += 1;
+        cudaEventDestroy(r.a);
+        cudaEventDestroy(r.b);
+    }
+    ssd::prof::g_recs.clear();
+    if (rc) return fail(rc, "profile_read: event query failed");
+    return 0;
+}
+
+const char* ssd_b200_last_error(void) { return g_err; }
+
+int ssd_b200_resolve_path(const ssd_b200_shape* shape) {
+    if (int rc = check_shape(shape)) return rc;
+    return resolve_path(*shape);
+}
+
+size_t ssd_b200_workspace_bytes(const ssd_b200_shape* shape, int pass) {
+    if (check_shape(shape)) return 0;
+    if (pass != SSD_B200_PASS_FWD && pass != SSD_B200_PASS_BWD) return 0;
+    int path = resolve_path(*shape);
+    if (path < 0) return 0;
+    ssd::Dims d = dims_of(*shape);
+    if (path == SSD_B200_PATH_TC) return ssd::tc::workspace_bytes(d, pass);
+    return simt_ws(d, pass).total;
+}
+
+int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
+    if (!a) return fail(SSD_B200_EINVAL, "args is null");
+    if (int rc = check_shape(&a->shape)) return rc;
+    if (int rc = check_forms(a->a, a->dt, a->A_head, a->D)) return rc;
+    if (!a->x || !a->B || !a->C || !a->y || !a->a_cumsum) return fail(SSD_B200_EINVAL, "null tensor pointer");
+    int path = resolve_path(a->shape);
+    if (path < 0) return path;
+    if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(SSD_B200_EWORKSPACE, "workspace null or not 256-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (path == SSD_B200_PATH_TC) return ssd::tc::forward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
+    return a->shape.dtype == SSD_B200_BF16 ? simt_fwd<__nv_bfloat16>(a, st) : simt_fwd<float>(a, st);
+}
+
+int ssd_b200_bwd(const ssd_b200_bwd_args* a, void* stream) {
+    if (!a) return fail(SSD_B200_EINVAL, "args is null");
+    if (int rc = check_shape(&a->shape)) return rc;
+    if (int rc = check_forms(a->a, a->dt, a->A_head, a->D)) return rc;
+    if (!a->x || !a->B || !a->C || !a->dy || !a->a_cumsum || !a->dx || !a->dB || !a->dC)
+        return fail(SSD_B200_EINVAL, "null tensor pointer");
+    if (a->dt && (!a->ddt || !a->dA_head || (a->D && !a->dD))) return fail(SSD_B200_EINVAL, "Mamba-2 form needs ddt, dA_head (and dD)");
+    if (a->a && !a->cumsum_is_input && !a->da) return fail(SSD_B200_EINVAL, "operator form needs da");
+    int path = resolve_path(a->shape);
+    if (path < 0) return path;
+    if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(SSD_B200_EWORKSPACE, "workspace null or not 256-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (path == SSD_B200_PATH_TC) return ssd::tc::backward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
+    return a->shape.dtype == SSD_B200_BF16 ? simt_bwd<__nv_bfloat16>(a, st) : simt_bwd<float>(a, st);
+}
+
+int ssd_b200_materialize_cache(const ssd_b200_shape* shape, const float* a_cumsum, void* L, void* decay_chunk,
+                               int32_t dtype, void* stream) {
+    if (int rc = check_shape(shape)) return rc;
+    if (!a_cumsum) return fail(SSD_B200_EINVAL, "a_cumsum is null");
+    ssd::Dims d = dims_of(*shape);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t chunks = (size_t)d.b * d.h * d.c;
+    if (chunks > 2147483647u) return fail(SSD_B200_EUNSUPPORTED, "too many chunks");
+    if (L) {
+        if (dtype == SSD_B200_BF16)
+            SSD_LAUNCH(ssd::prof::K_CACHE_L, st, ssd::simt::cache_L_kernel<<<(unsigned)chunks, 256, 0, st>>>(a_cumsum, (__nv_bfloat16*)L, chunks, d.l));
+        else
+            SSD_LAUNCH(ssd::prof::K_CACHE_L, st, ssd::simt::cache_L_kernel<<<(unsigned)chunks, 256, 0, st>>>(a_cumsum, (float*)L, chunks, d.l));
+        CUDA_LAUNCH_CHECK("cache_L");
+    }
+    if (decay_chunk) {
+        if (d.c + 1 > 65535) return fail(SSD_B200_EUNSUPPORTED, "too many chunks for decay_chunk");
+        dim3 g((unsigned)(d.b * d.h), d.c + 1);
+        if (dtype == SSD_B200_BF16)
+            SSD_LAUNCH(ssd::prof::K_CACHE_DC, st, ssd::simt::cache_decay_chunk_kernel<<<g, 128, 0, st>>>(a_cumsum, (__nv_bfloat16*)decay_chunk, d.c, d.l));
+        else
+            SSD_LAUNCH(ssd::prof::K_CACHE_DC, st, ssd::simt::cache_decay_chunk_kernel<<<g, 128, 0, st>>>(a_cumsum, (float*)decay_chunk, d.c, d.l));
+        CUDA_LAUNCH_CHECK("cache_decay_chunk");
+    }
+    return 0;
+}
+
+int ssd_b200_state_prefix(const float* finals, const float* logp, float* out, int64_t nranks, int64_t rank,
+                          int64_t batch, int64_t nheads, int64_t state_elems, int32_t reverse, void* stream) {
+    if (!finals || !logp || !out) return fail(SSD_B200_EINVAL, "null pointer");
+    if (nranks <= 0 || rank < 0 || rank >= nranks || batch <= 0 || nheads <= 0 || state_elems <= 0 ||
+        batch * nheads > 65535)
+        return fail(SSD_B200_EINVAL, "bad state_prefix dimensions");
+    dim3 g((unsigned)((state_elems + 255) / 256), (unsigned)(batch * nheads));
+    SSD_LAUNCH(ssd::prof::K_PREFIX, (cudaStream_t)stream, ssd::simt::state_prefix_kernel<<<g, 256, 0, (cudaStream_t)stream>>>(finals, logp, out, (int)nranks, (int)rank,
+                                                                        (int)(batch * nheads), (size_t)state_elems,
+                                                                        reverse));
+    CUDA_LAUNCH_CHECK("state_prefix");
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,800 @@
+// fp32-accumulate SIMT kernels for the SSD chunked scan, forward and backward.
+//
+// This is the full-precision path (fp32 storage, 1e-4 parity) and the path for shapes the
+// tensor-core kernels do not cover.  Everything is computed in fp32 whatever the storage type.
+// The algorithm per (batch, head), chunk k, in-chunk positions i, j (l per chunk):
+//
+//   cum_i = sum_{m<=i} a_m          S_k = cum_{l-1}
+//   G     = (C B^T) o L,  L_ij = exp(cum_i - cum_j) for i >= j, 0 above      Y_diag = G X
+//   Hloc  = X^T diag(exp(S_k - cum_j)) B                                      (p x n)
+//   H_{k+1} = exp(S_k) H_k + Hloc_k       (H_0 = initial state)
+//   Y     = Y_diag + diag(exp(cum_i)) C H_k^T   (+ D x)
+//
+// which restates src/kernels/ssd_scan.py:364-418 of the reference with the dense O(c^2) state
+// passing (:408) replaced by the recurrence it equals, exact zeros above the diagonal instead
+// of the reference's exp(-20), and no clamp (all log-decays here are <= 0).
+//
+// Backward (dY, dfinal given), with Q_k = dH_{k+1}:
+//   dH_k = exp(S_k) Q_k + dY_k^T diag(e) C_k                 (reverse recurrence, dH_c = dfinal)
+//   dG = dY X^T ; dS = dG o L ; M = dS o (C B^T)
+//   dX = G^T dY + diag(d) B Q^T ;  dC = dS B + diag(e) dY H_k ;  dB = dS^T C + diag(d) X Q
+//   g_t = rowsum_t(M) - colsum_t(M) + <dC_off_t, C_t> - <dB_st_t, B_t>  (+ <dfinal, final> at T-1)
+//   d a_t = sum_{s >= t} g_s                                  (reverse cumsum over the sequence)
+// This closed form replaces the reference's autograd re-run (src/kernels/ssd_scan.py:468-533)
+// and its O(l^3)-traffic segsum backward (:123-198).
+#pragma once
+#include "ssd_common.cuh"
+
+namespace ssd {
+namespace simt {
+
+constexpr int TS = 64;    // output tile edge of every block-level product
+constexpr int NTHR = 256; // threads per block: 16 x 16, each owning a 4 x 4 micro-tile
+
+struct Params {
+    Dims d;
+    const void* x;
+    const void* a;        // (b,T,h) per-position log-decay in a_dtype, or null
+    const float* dt;      // (b,T,h) or null
+    const float* A_head;  // (h) or null
+    const float* D;       // (h) or null
+    const void* B;
+    const void* C;
+    const void* dy;
+    const float* init;    // (b,h,p,n) or null
+    const float* dfinal;  // (b,h,p,n) or null
+    float* cum;           // (b,h,c,l)
+    float* states;        // (b,c,h,p,n): local chunk states, then states entering each chunk
+    float* dstates;       // (b,c,h,p,n): local state gradients, then dH_{k+1} per chunk
+    float* final_state;   // (b,h,p,n)
+    float* dinit;         // (b,h,p,n)
+    void* y;
+    void* dx;
+    void* dB;
+    void* dC;
+    float* g_row;         // (b,h,T)
+    float* g_col;         // (b,h,T)
+    float* ddtx;          // (b,h,T)  sum_p dX * x
+    float* da;            // (b,T,h)
+    float* ddt;           // (b,T,h)
+    float* dAh_part;      // (b,h)
+    float* dD_part;       // (b,h)
+    int a_is_bf16;
+};
+
+__device__ __forceinline__ float load_a(const Params& P, int bb, int t, int hh) {
+    size_t i = ((size_t)bb * P.d.T + t) * P.d.h + hh;
+    if (P.dt) return P.dt[i] * P.A_head[hh];
+    return P.a_is_bf16 ? __bfloat162float(((const __nv_bfloat16*)P.a)[i]) : ((const float*)P.a)[i];
+}
+
+// acc[r][c] += sum_k a(r,k) * b(k,c); the functors read shared memory.
+template <class FA, class FB>
+__device__ __forceinline__ void tile_mma(float (&acc)[4][4], int K, FA a, FB b) {
+#pragma unroll 2
+    for (int k = 0; k < K; ++k) {
+        float av[4], bv[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) av[r] = a(r, k);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) bv[c] = b(k, c);
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(av[r], bv[c], acc[r][c]);
+    }
+}
+
+__device__ __forceinline__ void zero(float (&acc)[4][4]) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+}
+
+// Load `rows` x `cols` (row r at src + r*stride), zero-filling rows >= valid_rows and columns
+// in [cols, cols_pad), into dst[r*ld + c].
+template <class T>
+__device__ __forceinline__ void load_tile(float* dst, int ld, const T* src, size_t stride, int rows, int valid_rows,
+                                          int cols, int cols_pad) {
+    for (int idx = threadIdx.x; idx < rows * cols_pad; idx += NTHR) {
+        int r = idx / cols_pad, c = idx - r * cols_pad;
+        float v = 0.f;
+        if (r < valid_rows && c < cols) v = to_f(src[(size_t)r * stride + c]);
+        dst[r * ld + c] = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Chunk cumsum: a (b,T,h) -> cum (b,h,c,l), inclusive within each chunk.  One block per
+// (chunk, batch); the [l][h] tile is staged through shared memory so that both the strided
+// read (h contiguous) and the transposed write (l contiguous) are coalesced; each warp scans
+// one head at a time with warp shuffles.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NTHR) chunk_cumsum_kernel(Params P) {
+    extern __shared__ float sm[];
+    const Dims& d = P.d;
+    const int k = blockIdx.x, bb = blockIdx.y;
+    const int ldh = d.h + 1;
+    for (int idx = threadIdx.x; idx < d.l * d.h; idx += NTHR) {
+        int i = idx / d.h, hh = idx - i * d.h;
+        sm[i * ldh + hh] = load_a(P, bb, k * d.l + i, hh);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per = (d.l + 31) / 32;
+    for (int hh = warp; hh < d.h; hh += NTHR / 32) {
+        float local = 0.f;
+        const int i0 = lane * per;
+        for (int q = 0; q < per; ++q)
+            if (i0 + q < d.l) local += sm[(i0 + q) * ldh + hh];
+        float incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            float v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        float run = incl - local;
+        float* out = P.cum + cum_off(d, bb, hh, k);
+        for (int q = 0; q < per; ++q)
+            if (i0 + q < d.l) {
+                run += sm[(i0 + q) * ldh + hh];
+                out[i0 + q] = run;
+            }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Weighted outer-product accumulation over a chunk:
+//   out[b,k,h][pp][nn] = sum_j w_j U[j,pp] V[j,nn]
+// mode 0: U = x, V = B, w_j = exp(S_k - cum_j) * dt_j      (local chunk states)
+// mode 1: U = dy, V = C, w_j = exp(cum_j)                  (local state gradients)
+// ------------------------------------------------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(NTHR) chunk_state_kernel(Params P, int mode) {
+    __shared__ float Us[TS][TS + 4];
+    __shared__ float Vs[TS][TS + 4];
+    __shared__ float w[TS];
+    const Dims& d = P.d;
+    const int nt = blockIdx.x, pt = blockIdx.y;
+    int z = blockIdx.z;
+    const int hh = z % d.h;
+    z /= d.h;
+    const int k = z % d.c, bb = z / d.c;
+    const int gg = hh / d.hpg;
+    const T* U = (const T*)(mode == 0 ? P.x : P.dy);
+    const T* V = (const T*)(mode == 0 ? P.B : P.C);
+    const float* cum = P.cum + cum_off(d, bb, hh, k);
+    const float S = cum[d.l - 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4];
+    zero(acc);
+    for (int j0 = 0; j0 < d.l; j0 += TS) {
+        const int rows = min(TS, d.l - j0);
+        if (threadIdx.x < TS) {
+            int j = j0 + threadIdx.x;
+            float wv = 0.f;
+            if (j < d.l) {
+                if (mode == 0) {
+                    wv = __expf(S - cum[j]);
+                    if (P.dt) wv *= P.dt[((size_t)bb * d.T + k * d.l + j) * d.h + hh];
+                } else {
+                    wv = __expf(cum[j]);
+                }
+            }
+            w[threadIdx.x] = wv;
+        }
+        __syncthreads();
+        const int t0 = k * d.l + j0;
+        for (int idx = threadIdx.x; idx < TS * TS; idx += NTHR) {
+            int r = idx >> 6, cc = idx & 63;
+            float u = 0.f, v = 0.f;
+            if (r < rows) {
+                int pp = pt * TS + cc, nn = nt * TS + cc;
+                if (pp < d.p) u = to_f(U[x_off(d, bb, t0 + r, hh) + pp]) * w[r];
+                if (nn < d.n) v = to_f(V[bc_off(d, bb, t0 + r, gg) + nn]);
+            }
+            Us[r][cc] = u;
+            Vs[r][cc] = v;
+        }
+        __syncthreads();
+        tile_mma(acc, TS, [&](int r, int kk) { return Us[kk][ty * 4 + r]; },
+                 [&](int kk, int cc) { return Vs[kk][tx * 4 + cc]; });
+        __syncthreads();
+    }
+    float* out = (mode == 0 ? P.states : P.dstates) + st_off(d, bb, k, hh);
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+            int pp = pt * TS + ty * 4 + r, nn = nt * TS + tx * 4 + cc;
+            if (pp < d.p && nn < d.n) out[(size_t)pp * d.n + nn] = acc[r][cc];
+        }
+}
+
+// ------------------------------------------------------------------------------------------
+// Inter-chunk state passing, one thread per state element, sequential over chunks.
+// forward : slot k <- H_k (state entering chunk k), H_{k+1} = exp(S_k) H_k + local_k ; final = H_c
+// reverse : slot k <- Q_k = dH_{k+1},               dH_k   = exp(S_k) Q_k + local_k ; dinit = dH_0
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NTHR) state_passing_kernel(Params P, int reverse) {
+    const Dims& d = P.d;
+    const size_t pn = (size_t)d.p * d.n;
+    const size_t e = (size_t)blockIdx.x * NTHR + threadIdx.x;
+    if (e >= pn) return;
+    const int hh = blockIdx.y, bb = blockIdx.z;
+    float* buf = reverse ? P.dstates : P.states;
+    const float* seed = reverse ? P.dfinal : P.init;
+    float H = seed ? seed[((size_t)bb * d.h + hh) * pn + e] : 0.f;
+    for (int s = 0; s < d.c; ++s) {
+        const int k = reverse ? d.c - 1 - s : s;
+        const float S = P.cum[cum_off(d, bb, hh, k) + d.l - 1];
+        float* slot = buf + st_off(d, bb, k, hh) + e;
+        const float loc = *slot;
+        *slot = H;
+        H = __expf(S) * H + loc;
+    }
+    float* out = reverse ? P.dinit : P.final_state;
+    if (out) out[((size_t)bb * d.h + hh) * pn + e] = H;
+}
+
+// ------------------------------------------------------------------------------------------
+// Chunk scan output.  Block = 64 rows i of one (batch, chunk, head); loops the causal column
+// blocks j <= i:  Y_i = sum_j ((C_i B_j^T) o L_ij) X_j  +  diag(e_i) C_i H_k^T  (+ D x_i).
+// ------------------------------------------------------------------------------------------
+template <class T, int PT>
+__global__ void __launch_bounds__(NTHR) chunk_scan_kernel(Params P) {
+    extern __shared__ float sm[];
+    const Dims& d = P.d;
+    const int ib = blockIdx.x, hh = blockIdx.y;
+    const int k = blockIdx.z % d.c, bb = blockIdx.z / d.c;
+    const int gg = hh / d.hpg;
+    const int ldn = d.n + 1, ldp = PT * TS + 1, ldg = TS + 1;
+    const int hrows = max(TS, d.p);
+    float* Cs = sm;                  // [64][n+1]
+    float* Bs = Cs + TS * ldn;       // [max(64,p)][n+1]  (B_j, later H_k)
+    float* Xs = Bs + hrows * ldn;    // [64][PT*64+1]
+    float* Gs = Xs + TS * ldp;       // [64][65]
+    float* cum_i = Gs + TS * ldg;    // [64]
+    float* cum_j = cum_i + TS;       // [64]
+    const T* x = (const T*)P.x;
+    const T* Bp = (const T*)P.B;
+    const T* Cp = (const T*)P.C;
+    const float* cum = P.cum + cum_off(d, bb, hh, k);
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int i0 = ib * TS, t_i0 = k * d.l + i0;
+    const int rows_i = min(TS, d.l - i0);
+
+    load_tile(Cs, ldn, Cp + bc_off(d, bb, t_i0, gg), (size_t)d.g * d.n, TS, rows_i, d.n, d.n);
+    if (threadIdx.x < TS) cum_i[threadIdx.x] = threadIdx.x < rows_i ? cum[i0 + threadIdx.x] : 0.f;
+    float accY[PT][4][4];
+#pragma unroll
+    for (int q = 0; q < PT; ++q) zero(accY[q]);
+
+    for (int jb = 0; jb <= ib; ++jb) {
+        const int j0 = jb * TS, t_j0 = k * d.l + j0;
+        const int rows_j = min(TS, d.l - j0);
+        __syncthreads();
+        load_tile(Bs, ldn, Bp + bc_off(d, bb, t_j0, gg), (size_t)d.g * d.n, TS, rows_j, d.n, d.n);
+        load_tile(Xs, ldp, x + x_off(d, bb, t_j0, hh), (size_t)d.h * d.p, TS, rows_j, d.p, PT * TS);
+        if (threadIdx.x < TS) cum_j[threadIdx.x] = threadIdx.x < rows_j ? cum[j0 + threadIdx.x] : 0.f;
+        __syncthreads();
+        if (P.dt) {  // X = x * dt
+            for (int idx = threadIdx.x; idx < rows_j * PT * TS; idx += NTHR) {
+                int r = idx / (PT * TS), cc = idx - r * (PT * TS);
+                Xs[r * ldp + cc] *= P.dt[((size_t)bb * d.T + t_j0 + r) * d.h + hh];
+            }
+        }
+        float s[4][4];
+        zero(s);
+        tile_mma(s, d.n, [&](int r, int kk) { return Cs[(ty * 4 + r) * ldn + kk]; },
+                 [&](int kk, int cc) { return Bs[(tx * 4 + cc) * ldn + kk]; });
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                int il = ty * 4 + r, jl = tx * 4 + cc;
+                bool ok = (i0 + il >= j0 + jl) && il < rows_i && jl < rows_j;
+                Gs[il * ldg + jl] = ok ? s[r][cc] * __expf(cum_i[il] - cum_j[jl]) : 0.f;
+            }
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < PT; ++q)
+            tile_mma(accY[q], TS, [&](int r, int kk) { return Gs[(ty * 4 + r) * ldg + kk]; },
+                     [&](int kk, int cc) { return Xs[kk * ldp + q * TS + tx * 4 + cc]; });
+    }
+    // state -> output
+    __syncthreads();
+    load_tile(Bs, ldn, P.states + st_off(d, bb, k, hh), (size_t)d.n, hrows, d.p, d.n, d.n);
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < PT; ++q) {
+        float o[4][4];
+        zero(o);
+        tile_mma(o, d.n, [&](int r, int kk) { return Cs[(ty * 4 + r) * ldn + kk]; },
+                 [&](int kk, int cc) { return Bs[min(q * TS + tx * 4 + cc, hrows - 1) * ldn + kk]; });
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float e = __expf(cum_i[ty * 4 + r]);
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) accY[q][r][cc] += e * o[r][cc];
+        }
+    }
+    T* y = (T*)P.y;
+    const float Dh = P.D ? P.D[hh] : 0.f;
+#pragma unroll
+    for (int q = 0; q < PT; ++q)
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                int il = ty * 4 + r, pp = q * TS + tx * 4 + cc;
+                if (il < rows_i && pp < d.p) {
+                    size_t o = x_off(d, bb, t_i0 + il, hh) + pp;
+                    float v = accY[q][r][cc];
+                    if (P.D) v += Dh * to_f(x[o]);
+                    y[o] = from_f<T>(v);
+                }
+            }
+}
+
+// Sum over the 16 threads (tx) that share a row; result valid in every lane of the group.
+__device__ __forceinline__ float row_reduce16(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------
+// Backward, row pass.  Block = 64 rows i of one (batch, chunk, group); loops the heads of the
+// group and the causal column blocks:  dC_i = sum_h [ sum_j dS_ij B_j + diag(e) dY_i H_k ],
+// g_row[i] = rowsum_i(M) + <dC_off_i, C_i> per head.
+// ------------------------------------------------------------------------------------------
+template <class T, int NTN>
+__global__ void __launch_bounds__(NTHR) bwd_row_kernel(Params P) {
+    extern __shared__ float sm[];
+    const Dims& d = P.d;
+    const int ib = blockIdx.x, gg = blockIdx.y;
+    const int k = blockIdx.z % d.c, bb = blockIdx.z / d.c;
+    const int pp_pad = ((d.p + 3) / 4) * 4;
+    const int ldn = d.n + 1, ldp = pp_pad + 1, ldg = TS + 1;
+    const int hrows = max(TS, d.p);
+    float* Cs = sm;                  // [64][n+1]      C_i
+    float* Bs = Cs + TS * ldn;       // [max(64,p)][n+1]  B_j, later H_k
+    float* dYs = Bs + hrows * ldn;   // [64][p+1]      dY_i
+    float* Xs = dYs + TS * ldp;      // [64][p+1]      X_j
+    float* dSs = Xs + TS * ldp;      // [64][65]
+    float* cum_i = dSs + TS * ldg;
+    float* cum_j = cum_i + TS;
+    const T* x = (const T*)P.x;
+    const T* dy = (const T*)P.dy;
+    const T* Bp = (const T*)P.B;
+    const T* Cp = (const T*)P.C;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int i0 = ib * TS, t_i0 = k * d.l + i0;
+    const int rows_i = min(TS, d.l - i0);
+    float dC[NTN][4][4];
+#pragma unroll
+    for (int q = 0; q < NTN; ++q) zero(dC[q]);
+    load_tile(Cs, ldn, Cp + bc_off(d, bb, t_i0, gg), (size_t)d.g * d.n, TS, rows_i, d.n, d.n);
+
+    for (int hl = 0; hl < d.hpg; ++hl) {
+        const int hh = gg * d.hpg + hl;
+        const float* cum = P.cum + cum_off(d, bb, hh, k);
+        __syncthreads();
+        load_tile(dYs, ldp, dy + x_off(d, bb, t_i0, hh), (size_t)d.h * d.p, TS, rows_i, d.p, pp_pad);
+        if (threadIdx.x < TS) cum_i[threadIdx.x] = threadIdx.x < rows_i ? cum[i0 + threadIdx.x] : 0.f;
+        float rowacc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int jb = 0; jb <= ib; ++jb) {
+            const int j0 = jb * TS, t_j0 = k * d.l + j0;
+            const int rows_j = min(TS, d.l - j0);
+            __syncthreads();
+            load_tile(Bs, ldn, Bp + bc_off(d, bb, t_j0, gg), (size_t)d.g * d.n, TS, rows_j, d.n, d.n);
+            load_tile(Xs, ldp, x + x_off(d, bb, t_j0, hh), (size_t)d.h * d.p, TS, rows_j, d.p, pp_pad);
+            if (threadIdx.x < TS) cum_j[threadIdx.x] = threadIdx.x < rows_j ? cum[j0 + threadIdx.x] : 0.f;
+            __syncthreads();
+            if (P.dt) {
+                for (int idx = threadIdx.x; idx < rows_j * pp_pad; idx += NTHR) {
+                    int r = idx / pp_pad, cc = idx - r * pp_pad;
+                    Xs[r * ldp + cc] *= P.dt[((size_t)bb * d.T + t_j0 + r) * d.h + hh];
+                }
+                __syncthreads();
+            }
+            float s[4][4], dg[4][4];
+            zero(s);
+            zero(dg);
+            tile_mma(s, d.n, [&](int r, int kk) { return Cs[(ty * 4 + r) * ldn + kk]; },
+                     [&](int kk, int cc) { return Bs[(tx * 4 + cc) * ldn + kk]; });
+            tile_mma(dg, d.p, [&](int r, int kk) { return dYs[(ty * 4 + r) * ldp + kk]; },
+                     [&](int kk, int cc) { return Xs[(tx * 4 + cc) * ldp + kk]; });
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    int il = ty * 4 + r, jl = tx * 4 + cc;
+                    bool ok = (i0 + il >= j0 + jl) && il < rows_i && jl < rows_j;
+                    float ds = ok ? dg[r][cc] * __expf(cum_i[il] - cum_j[jl]) : 0.f;
+                    rowacc[r] += ds * s[r][cc];
+                    dSs[il * ldg + jl] = ds;
+                }
+            __syncthreads();
+#pragma unroll
+            for (int q = 0; q < NTN; ++q)
+                if (q * TS < d.n)
+                    tile_mma(dC[q], TS, [&](int r, int kk) { return dSs[(ty * 4 + r) * ldg + kk]; },
+                             [&](int kk, int cc) { return Bs[kk * ldn + min(q * TS + tx * 4 + cc, d.n - 1)]; });
+        }
+        // state term: dC_off = diag(e) dY_i H_k
+        __syncthreads();
+        load_tile(Bs, ldn, P.states + st_off(d, bb, k, hh), (size_t)d.n, hrows, d.p, d.n, d.n);
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < NTN; ++q)
+            if (q * TS < d.n) {
+                float o[4][4];
+                zero(o);
+                tile_mma(o, d.p, [&](int r, int kk) { return dYs[(ty * 4 + r) * ldp + kk]; },
+                         [&](int kk, int cc) { return Bs[kk * ldn + min(q * TS + tx * 4 + cc, d.n - 1)]; });
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float e = __expf(cum_i[ty * 4 + r]);
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        int nn = q * TS + tx * 4 + cc;
+                        if (nn < d.n) {
+                            float v = e * o[r][cc];
+                            dC[q][r][cc] += v;
+                            rowacc[r] += v * Cs[(ty * 4 + r) * ldn + nn];
+                        }
+                    }
+                }
+            }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float v = row_reduce16(rowacc[r]);
+            int il = ty * 4 + r;
+            if (tx == 0 && il < rows_i) P.g_row[((size_t)bb * d.h + hh) * d.T + t_i0 + il] = v;
+        }
+    }
+    T* dCo = (T*)P.dC;
+#pragma unroll
+    for (int q = 0; q < NTN; ++q)
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                int il = ty * 4 + r, nn = q * TS + tx * 4 + cc;
+                if (il < rows_i && nn < d.n) dCo[bc_off(d, bb, t_i0 + il, gg) + nn] = from_f<T>(dC[q][r][cc]);
+            }
+}
+
+// ------------------------------------------------------------------------------------------
+// Backward, column pass.  Block = 64 columns j of one (batch, chunk, group); loops the heads and
+// the row blocks i >= j:  dX_j = sum_i G_ij^T dY_i + diag(d) B_j Q^T,
+// dB_j = sum_h [ sum_i dS_ij^T C_i + diag(d) X_j Q ],  g_col[j] = colsum_j(M) + <dB_st_j, B_j>,
+// dx = dX * dt + D * dy,  ddtx[j] = <dX_j, x_j>.
+// ------------------------------------------------------------------------------------------
+template <class T, int NTN, int PT>
+__global__ void __launch_bounds__(NTHR) bwd_col_kernel(Params P) {
+    extern __shared__ float sm[];
+    const Dims& d = P.d;
+    const int jb = blockIdx.x, gg = blockIdx.y;
+    const int k = blockIdx.z % d.c, bb = blockIdx.z / d.c;
+    const int ldn = d.n + 1, ldp = PT * TS + 1, ldg = TS + 1;
+    const int hrows = max(TS, d.p);
+    float* Bs = sm;                   // [64][n+1]          B_j
+    float* Cs = Bs + TS * ldn;        // [max(64,p)][n+1]   C_i, later Q_k
+    float* Xs = Cs + hrows * ldn;     // [64][PT*64+1]      X_j (already scaled by dt)
+    float* dYs = Xs + TS * ldp;       // [64][PT*64+1]      dY_i
+    float* GT = dYs + TS * ldp;       // [64 j][65]         G^T
+    float* dST = GT + TS * ldg;       // [64 j][65]         dS^T
+    float* cum_j = dST + TS * ldg;
+    float* cum_i = cum_j + TS;
+    float* dt_j = cum_i + TS;
+    const T* x = (const T*)P.x;
+    const T* dy = (const T*)P.dy;
+    const T* Bp = (const T*)P.B;
+    const T* Cp = (const T*)P.C;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int j0 = jb * TS, t_j0 = k * d.l + j0;
+    const int rows_j = min(TS, d.l - j0);
+    const int nib = (d.l + TS - 1) / TS;
+    float dBa[NTN][4][4];
+#pragma unroll
+    for (int q = 0; q < NTN; ++q) zero(dBa[q]);
+    load_tile(Bs, ldn, Bp + bc_off(d, bb, t_j0, gg), (size_t)d.g * d.n, TS, rows_j, d.n, d.n);
+
+    for (int hl = 0; hl < d.hpg; ++hl) {
+        const int hh = gg * d.hpg + hl;
+        const float* cum = P.cum + cum_off(d, bb, hh, k);
+        const float S = cum[d.l - 1];
+        __syncthreads();
+        load_tile(Xs, ldp, x + x_off(d, bb, t_j0, hh), (size_t)d.h * d.p, TS, rows_j, d.p, PT * TS);
+        if (threadIdx.x < TS) {
+            bool ok = threadIdx.x < rows_j;
+            cum_j[threadIdx.x] = ok ? cum[j0 + threadIdx.x] : 0.f;
+            dt_j[threadIdx.x] = (ok && P.dt) ? P.dt[((size_t)bb * d.T + t_j0 + threadIdx.x) * d.h + hh] : 1.f;
+        }
+        __syncthreads();
+        if (P.dt) {
+            for (int idx = threadIdx.x; idx < rows_j * PT * TS; idx += NTHR) {
+                int r = idx / (PT * TS), cc = idx - r * (PT * TS);
+                Xs[r * ldp + cc] *= dt_j[r];
+            }
+        }
+        float accX[PT][4][4];
+#pragma unroll
+        for (int q = 0; q < PT; ++q) zero(accX[q]);
+        float colacc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int ib = jb; ib < nib; ++ib) {
+            const int i0 = ib * TS, t_i0 = k * d.l + i0;
+            const int rows_i = min(TS, d.l - i0);
+            __syncthreads();
+            load_tile(Cs, ldn, Cp + bc_off(d, bb, t_i0, gg), (size_t)d.g * d.n, TS, rows_i, d.n, d.n);
+            load_tile(dYs, ldp, dy + x_off(d, bb, t_i0, hh), (size_t)d.h * d.p, TS, rows_i, d.p, PT * TS);
+            if (threadIdx.x < TS) cum_i[threadIdx.x] = threadIdx.x < rows_i ? cum[i0 + threadIdx.x] : 0.f;
+            __syncthreads();
+            float st[4][4], dgt[4][4];  // transposed: rows j, columns i
+            zero(st);
+            zero(dgt);
+            tile_mma(st, d.n, [&](int r, int kk) { return Bs[(ty * 4 + r) * ldn + kk]; },
+                     [&](int kk, int cc) { return Cs[(tx * 4 + cc) * ldn + kk]; });
+            tile_mma(dgt, d.p, [&](int r, int kk) { return Xs[(ty * 4 + r) * ldp + kk]; },
+                     [&](int kk, int cc) { return dYs[(tx * 4 + cc) * ldp + kk]; });
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    int jl = ty * 4 + r, il = tx * 4 + cc;
+                    bool ok = (i0 + il >= j0 + jl) && il < rows_i && jl < rows_j;
+                    float Lv = ok ? __expf(cum_i[il] - cum_j[jl]) : 0.f;
+                    float ds = dgt[r][cc] * Lv;
+                    colacc[r] += ds * st[r][cc];
+                    GT[jl * ldg + il] = st[r][cc] * Lv;
+                    dST[jl * ldg + il] = ds;
+                }
+            __syncthreads();
+#pragma unroll
+            for (int q = 0; q < PT; ++q)
+                tile_mma(accX[q], TS, [&](int r, int kk) { return GT[(ty * 4 + r) * ldg + kk]; },
+                         [&](int kk, int cc) { return dYs[kk * ldp + q * TS + tx * 4 + cc]; });
+#pragma unroll
+            for (int q = 0; q < NTN; ++q)
+                if (q * TS < d.n)
+                    tile_mma(dBa[q], TS, [&](int r, int kk) { return dST[(ty * 4 + r) * ldg + kk]; },
+                             [&](int kk, int cc) { return Cs[kk * ldn + min(q * TS + tx * 4 + cc, d.n - 1)]; });
+        }
+        // state terms with Q_k = dH_{k+1}
+        __syncthreads();
+        load_tile(Cs, ldn, P.dstates + st_off(d, bb, k, hh), (size_t)d.n, hrows, d.p, d.n, d.n);
+        __syncthreads();
+        float dj[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) dj[r] = (ty * 4 + r) < rows_j ? __expf(S - cum_j[ty * 4 + r]) : 0.f;
+#pragma unroll
+        for (int q = 0; q < PT; ++q) {
+            float o[4][4];
+            zero(o);
+            tile_mma(o, d.n, [&](int r, int kk) { return Bs[(ty * 4 + r) * ldn + kk]; },
+                     [&](int kk, int cc) { return Cs[min(q * TS + tx * 4 + cc, hrows - 1) * ldn + kk]; });
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) accX[q][r][cc] += dj[r] * o[r][cc];
+        }
+#pragma unroll
+        for (int q = 0; q < NTN; ++q)
+            if (q * TS < d.n) {
+                float o[4][4];
+                zero(o);
+                tile_mma(o, d.p, [&](int r, int kk) { return Xs[(ty * 4 + r) * ldp + kk]; },
+                         [&](int kk, int cc) { return Cs[kk * ldn + min(q * TS + tx * 4 + cc, d.n - 1)]; });
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        int nn = q * TS + tx * 4 + cc;
+                        if (nn < d.n) {
+                            float v = dj[r] * o[r][cc];
+                            dBa[q][r][cc] += v;
+                            colacc[r] += v * Bs[(ty * 4 + r) * ldn + nn];
+                        }
+                    }
+            }
+        // per-head outputs
+        T* dxo = (T*)P.dx;
+        const float Dh = P.D ? P.D[hh] : 0.f;
+        float ddt_acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q = 0; q < PT; ++q)
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    int jl = ty * 4 + r, pp = q * TS + tx * 4 + cc;
+                    if (jl < rows_j && pp < d.p) {
+                        size_t o = x_off(d, bb, t_j0 + jl, hh) + pp;
+                        float dX = accX[q][r][cc];
+                        float xv = to_f(x[o]);
+                        ddt_acc[r] += dX * xv;
+                        float v = dX * dt_j[jl];
+                        if (P.D) v += Dh * to_f(dy[o]);
+                        dxo[o] = from_f<T>(v);
+                    }
+                }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float gc = row_reduce16(colacc[r]);
+            float dd = row_reduce16(ddt_acc[r]);
+            int jl = ty * 4 + r;
+            if (tx == 0 && jl < rows_j) {
+                size_t o = ((size_t)bb * d.h + hh) * d.T + t_j0 + jl;
+                P.g_col[o] = gc;
+                P.ddtx[o] = dd;
+            }
+        }
+    }
+    T* dBo = (T*)P.dB;
+#pragma unroll
+    for (int q = 0; q < NTN; ++q)
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                int jl = ty * 4 + r, nn = q * TS + tx * 4 + cc;
+                if (jl < rows_j && nn < d.n) dBo[bc_off(d, bb, t_j0 + jl, gg) + nn] = from_f<T>(dBa[q][r][cc]);
+            }
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < NTHR / 32; ++w) t += red[w];
+    return t;
+}
+
+// ------------------------------------------------------------------------------------------
+// Decay gradient.  One block per (head, batch): g = g_row - g_col (+ <dfinal, final> at T-1),
+// d a_t = reverse inclusive cumsum of g over the whole sequence (tiles of 256 with a carry,
+// warp-shuffle scan inside a tile).  Operator form writes da; Mamba-2 form writes
+// ddt = ddtx + da * A_head and the per-(batch, head) partials of dA_head and dD.
+// ------------------------------------------------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
+    __shared__ float red[NTHR / 32];
+    __shared__ float wsum[NTHR / 32];
+    const Dims& d = P.d;
+    const int hh = blockIdx.x, bb = blockIdx.y;
+    const size_t pn = (size_t)d.p * d.n;
+    float gfin = 0.f;
+    if (P.dfinal) {
+        const float* a = P.dfinal + ((size_t)bb * d.h + hh) * pn;
+        const float* f = P.final_state + ((size_t)bb * d.h + hh) * pn;
+        float v = 0.f;
+        for (size_t e = threadIdx.x; e < pn; e += NTHR) v += a[e] * f[e];
+        gfin = block_sum(v, red);
+    }
+    const size_t base = ((size_t)bb * d.h + hh) * d.T;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float carry = 0.f, dAh = 0.f;
+    const float Ah = P.dt ? P.A_head[hh] : 0.f;
+    for (int hi = d.T; hi > 0; hi -= NTHR) {
+        // thread q handles t = hi-1-q, so the scan runs toward smaller t
+        const int t = hi - 1 - (int)threadIdx.x;
+        float v = 0.f;
+        if (t >= 0) {
+            v = P.g_row[base + t] - P.g_col[base + t];
+            if (t == d.T - 1) v += gfin;
+        }
+        float incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            float u = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += u;
+        }
+        __syncthreads();
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        float pre = 0.f, tot = 0.f;
+        for (int w = 0; w < NTHR / 32; ++w) {
+            if (w < warp) pre += wsum[w];
+            tot += wsum[w];
+        }
+        const float dA = carry + pre + incl;
+        carry += tot;
+        if (t >= 0) {
+            const size_t o = ((size_t)bb * d.T + t) * d.h + hh;
+            if (P.dt) {
+                P.ddt[o] = P.ddtx[base + t] + dA * Ah;
+                dAh += dA * P.dt[o];
+            } else if (P.da) {
+                P.da[o] = dA;
+            }
+        }
+    }
+    if (P.dt) {
+        float s = block_sum(dAh, red);
+        if (threadIdx.x == 0) P.dAh_part[(size_t)bb * d.h + hh] = s;
+        if (P.D) {
+            const T* x = (const T*)P.x;
+            const T* dy = (const T*)P.dy;
+            float v = 0.f;
+            for (size_t e = threadIdx.x; e < (size_t)d.T * d.p; e += NTHR) {
+                int t = (int)(e / d.p), pp = (int)(e - (size_t)t * d.p);
+                size_t o = x_off(d, bb, t, hh) + pp;
+                v += to_f(x[o]) * to_f(dy[o]);
+            }
+            float sd = block_sum(v, red);
+            if (threadIdx.x == 0) P.dD_part[(size_t)bb * d.h + hh] = sd;
+        }
+    }
+}
+
+// out[hh] = sum_b part[b,hh]   (fixed order: deterministic)
+__global__ void reduce_batch_kernel(const float* part, float* out, int b, int h) {
+    int hh = blockIdx.x * blockDim.x + threadIdx.x;
+    if (hh >= h) return;
+    float s = 0.f;
+    for (int bb = 0; bb < b; ++bb) s += part[(size_t)bb * h + hh];
+    out[hh] = s;
+}
+
+// ------------------------------------------------------------------------------------------
+// The reference's cache tensors, rebuilt from the chunk cumsum on request
+// (src/kernels/ssd_scan.py:53-55, :371-382, :399-406): masked entries are exp(-20) there.
+// ------------------------------------------------------------------------------------------
+template <class T>
+__global__ void cache_L_kernel(const float* cum, T* L, size_t chunks, int l) {
+    const size_t m = blockIdx.x;  // (b,h,c) flattened
+    if (m >= chunks) return;
+    const float* cu = cum + m * l;
+    T* out = L + m * (size_t)l * l;
+    for (int idx = threadIdx.x; idx < l * l; idx += blockDim.x) {
+        int i = idx / l, j = idx - i * l;
+        float v = i >= j ? fminf(fmaxf(cu[i] - cu[j], -20.f), 20.f) : -20.f;
+        out[idx] = from_f<T>(__expf(v));
+    }
+}
+
+template <class T>
+__global__ void cache_decay_chunk_kernel(const float* cum, T* dc, int c, int l) {
+    const size_t m = blockIdx.x;  // (b,h) flattened
+    const float* cu = cum + m * (size_t)c * l;
+    T* out = dc + m * (size_t)(c + 1) * (c + 1);
+    const int z = blockIdx.y;  // row
+    // padded totals Z_0 = 0, Z_m = S_{m-1};  entry (z,k) = sum_{m=k+1..z} Z_m for z >= k
+    for (int kk = threadIdx.x; kk <= c; kk += blockDim.x) {
+        float v;
+        if (z >= kk) {
+            float s = 0.f;
+            for (int mm = kk + 1; mm <= z; ++mm) s += cu[(size_t)(mm - 1) * l + l - 1];
+            v = fminf(fmaxf(s, -20.f), 20.f);
+        } else {
+            v = -20.f;
+        }
+        out[(size_t)z * (c + 1) + kk] = from_f<T>(__expf(v));
+    }
+}
+
+// Sequence-parallel prefix over gathered per-rank summaries (all in this GPU's memory).
+__global__ void state_prefix_kernel(const float* finals, const float* logp, float* out, int R, int rank, int bh,
+                                    size_t pn, int reverse) {
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int m = blockIdx.y;  // (b,h)
+    if (e >= pn) return;
+    float acc = 0.f;
+    if (!reverse) {
+        for (int q = 0; q < rank; ++q) acc = __expf(logp[(size_t)q * bh + m]) * acc + finals[((size_t)q * bh + m) * pn + e];
+    } else {
+        for (int q = R - 1; q > rank; --q) acc = __expf(logp[(size_t)q * bh + m]) * acc + finals[((size_t)q * bh + m) * pn + e];
+    }
+    out[(size_t)m * pn + e] = acc;
+}
+
+}  // namespace simt
+}  // namespace ssd

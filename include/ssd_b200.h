@@ -1,0 +1,195 @@
+/*
+ * ssd_b200 -- C ABI of the B200 (sm_100a) SSD chunked scan, forward and backward.
+ *
+ * This is the drop-in boundary for the reference's fused SSD scan operator
+ * (reference paths are relative to its r2/dhammic-ai directory):
+ *
+ *   fused_ssd_scan(x, A, B, C, chunk_size, initial_states, cache)   src/kernels/ssd_scan.py:539-583
+ *   FusedSSDScan.forward / .backward                                src/kernels/ssd_scan.py:441-533
+ *   _ssd_forward_impl (the algorithm)                               src/kernels/ssd_scan.py:330-421
+ *
+ * The reference has no native code; its operator is Python over Triton and
+ * cuBLAS.  A maintainer binds these entry points from Python with ctypes
+ * (see INTEGRATION.md).  Conventions:
+ *
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer on the
+ *     current CUDA device unless stated otherwise; tensors are dense row-major
+ *     in the layouts given below;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *     all work is enqueued on it and nothing synchronises the host;
+ *   - every function returns 0 on success or a negative SSD_B200_E* code and
+ *     never throws, aborts or traps; ssd_b200_last_error() gives a
+ *     thread-local message for the last failure on the calling thread;
+ *   - the library allocates nothing: the caller provides outputs and one
+ *     workspace of ssd_b200_workspace_bytes() bytes, 256-byte aligned.
+ *
+ * Symbols: b batch, T seqlen, h heads, p headdim, n d_state, g groups
+ * (g divides h; head j uses group j / (h/g)), l chunk, c = T / l.
+ */
+#ifndef SSD_B200_H_
+#define SSD_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SSD_B200_ABI_VERSION 1
+
+enum {
+    SSD_B200_OK = 0,
+    SSD_B200_EINVAL = -1,       /* bad shape, null pointer, bad flag combination      */
+    SSD_B200_EUNSUPPORTED = -2, /* shape outside what the kernels cover               */
+    SSD_B200_EWORKSPACE = -3,   /* workspace missing, too small or misaligned         */
+    SSD_B200_ECUDA = -4,        /* a CUDA runtime call or launch failed               */
+    SSD_B200_EDEVICE = -5       /* a kernel reported a bounded wait that ran out      */
+};
+
+enum { SSD_B200_F32 = 0, SSD_B200_BF16 = 1 };
+
+enum { SSD_B200_PASS_FWD = 0, SSD_B200_PASS_BWD = 1 };
+
+/* Which kernels run.  AUTO picks the tcgen05 tensor-core path when the shape
+ * and dtype allow it (bf16; p = 64; n in {64,128}; T a multiple of 128) and the
+ * fp32 SIMT path otherwise; the other two force a path (for tests). */
+enum { SSD_B200_PATH_AUTO = 0, SSD_B200_PATH_SIMT = 1, SSD_B200_PATH_TC = 2 };
+
+typedef struct ssd_b200_shape {
+    int32_t abi_version; /* SSD_B200_ABI_VERSION                                      */
+    int32_t dtype;       /* storage of x, B, C, y, dy, dx, dB, dC                      */
+    int32_t a_dtype;     /* storage of the per-position log-decay `a` (when given)     */
+    int32_t path;        /* SSD_B200_PATH_*                                            */
+    int64_t batch, seqlen, nheads, headdim, dstate, ngroups, chunk;
+} ssd_b200_shape;
+
+/*
+ * Forward.  Replaces _ssd_forward_impl (src/kernels/ssd_scan.py:330-421) and,
+ * with dt/A_head/D given, also the caller's input products and D skip
+ * (src/mamba_base_engine.py:170-173, :187).
+ *
+ * Two ways to give the decay and the input scaling:
+ *   (1) operator form:  a != NULL, dt == A_head == D == NULL:  X = x, log-decay = a   (b,T,h)
+ *   (2) Mamba-2 form:   a == NULL, dt (b,T,h) fp32, A_head (h) fp32, D (h) fp32 or NULL:
+ *                       X = x * dt, log-decay = dt * A_head, y += D * x
+ *
+ *   x (b,T,h,p)  B,C (b,T,g,n)  init (b,h,p,n) fp32 or NULL  ->  y (b,T,h,p), final_state (b,h,p,n) fp32
+ *   a_cumsum (b,h,c,l) fp32: within-chunk inclusive cumulative log-decay; written unless
+ *   cumsum_is_input != 0, in which case it is read as given (the reference's cached call,
+ *   src/kernels/ssd_scan.py:364-373).
+ */
+typedef struct ssd_b200_fwd_args {
+    ssd_b200_shape shape;
+    const void *x;
+    const void *a;
+    const float *dt;
+    const float *A_head;
+    const float *D;
+    const void *B;
+    const void *C;
+    const float *init;
+    void *y;
+    float *final_state;
+    float *a_cumsum;
+    int32_t cumsum_is_input;
+    int32_t reserved;
+    void *workspace;
+    size_t workspace_bytes;
+} ssd_b200_fwd_args;
+
+/*
+ * Backward.  Replaces FusedSSDScan.backward (src/kernels/ssd_scan.py:468-533): given dy
+ * (b,T,h,p) and optionally dfinal (b,h,p,n) fp32 it writes
+ *   dx (b,T,h,p), dB, dC (b,T,g,n) in storage dtype, dinit (b,h,p,n) fp32 (optional), and
+ *   operator form : da (b,T,h) fp32 -- gradient of the per-position log-decay; skipped (may be
+ *                   NULL) when cumsum_is_input != 0, matching the reference, whose cached call
+ *                   returns no decay gradient (src/kernels/ssd_scan.py:494-500, :533);
+ *   Mamba-2 form  : ddt (b,T,h) fp32, dA_head (h) fp32, dD (h) fp32 (dD only when D != NULL).
+ * a_cumsum is the tensor the forward produced (or was given).
+ */
+typedef struct ssd_b200_bwd_args {
+    ssd_b200_shape shape;
+    const void *x;
+    const void *a;
+    const float *dt;
+    const float *A_head;
+    const float *D;
+    const void *B;
+    const void *C;
+    const float *init;
+    const float *a_cumsum;
+    const void *dy;
+    const float *dfinal;
+    void *dx;
+    void *dB;
+    void *dC;
+    float *da;
+    float *ddt;
+    float *dA_head;
+    float *dD;
+    float *dinit;
+    int32_t cumsum_is_input;
+    int32_t reserved;
+    void *workspace;
+    size_t workspace_bytes;
+} ssd_b200_bwd_args;
+
+/* ABI version of the loaded library (compare with SSD_B200_ABI_VERSION). */
+int ssd_b200_abi_version(void);
+
+/* Message for the last failure on this thread ("" if none).  The pointer stays valid until
+ * the next failing call on the same thread. */
+const char *ssd_b200_last_error(void);
+
+/* Bytes of workspace one call of the given pass needs for this shape (0 on a bad shape). */
+size_t ssd_b200_workspace_bytes(const ssd_b200_shape *shape, int pass);
+
+/* Which path AUTO resolves to for this shape: SSD_B200_PATH_SIMT or SSD_B200_PATH_TC
+ * (negative code on a bad shape).  Host-only, needs no GPU. */
+int ssd_b200_resolve_path(const ssd_b200_shape *shape);
+
+int ssd_b200_fwd(const ssd_b200_fwd_args *args, void *stream);
+int ssd_b200_bwd(const ssd_b200_bwd_args *args, void *stream);
+
+/*
+ * The reference operator also returns its decay masks as a cache
+ * (src/kernels/ssd_scan.py:420, :465; shapes pinned by tests/kernels/test_ssd_scan.py:107-110).
+ * This builds them from a_cumsum on demand:
+ *   L (b,h,c,l,l)          = exp(clamp(cum_i - cum_j, -20, 20)) for i >= j, exp(-20) above
+ *   decay_chunk (b,h,c+1,c+1) = the same construction over the zero-padded chunk totals
+ * in `dtype` storage.  Either output may be NULL.
+ */
+int ssd_b200_materialize_cache(const ssd_b200_shape *shape, const float *a_cumsum, void *L,
+                               void *decay_chunk, int32_t dtype, void *stream);
+
+/*
+ * Sequence-parallel state prefix (no counterpart in the reference, which has no multi-GPU
+ * path; it builds on the operator's initial_states / final_state contract,
+ * src/kernels/ssd_scan.py:395-397, :410).  `finals` (R,b,h,p,n) fp32 holds every rank's
+ * zero-init final state and `logp` (R,b,h) fp32 every rank's total log-decay, both already
+ * gathered into THIS GPU's memory.  Writes
+ *   out[b,h,p,n] = sum_{q<rank} exp(sum_{q<k<rank} logp[k]) * finals[q]      (reverse == 0)
+ *   out[b,h,p,n] = sum_{q>rank} exp(sum_{rank<k<q} logp[k]) * finals[q]      (reverse != 0)
+ */
+int ssd_b200_state_prefix(const float *finals, const float *logp, float *out, int64_t nranks,
+                          int64_t rank, int64_t batch, int64_t nheads, int64_t state_elems,
+                          int32_t reverse, void *stream);
+
+/*
+ * Measurement hooks (no counterpart in the reference).  ssd_b200_launch_count() is the number of
+ * kernels this library has launched in the process.  With profiling enabled every launch is
+ * bracketed by CUDA events on its stream; ssd_b200_profile_read() waits for them, adds their
+ * durations (ms) and launch counts per kernel slot into ms[n] / launches[n]
+ * (n >= ssd_b200_profile_kernels()) and clears the record.  For single-threaded benchmark use.
+ */
+long long ssd_b200_launch_count(void);
+int ssd_b200_profile_enable(int on);
+int ssd_b200_profile_kernels(void);
+const char *ssd_b200_profile_kernel_name(int idx);
+int ssd_b200_profile_read(float *ms, long long *launches, int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSD_B200_H_ */

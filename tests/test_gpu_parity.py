@@ -1,0 +1,197 @@
+"""GPU parity tests: the CUDA path, called through the C ABI by the operator, against the CPU oracle
+and the golden fixtures.  Metric: max|a-b| / max|b| per output tensor; bars: 1e-4 for fp32,
+2e-2 for bf16 inputs with fp32 accumulation (the oracle then runs in fp32 on the bf16-rounded inputs,
+as the reference's own bf16 test does, tests/kernels/test_ssd_scan.py:74-96)."""
+import glob
+from dataclasses import replace
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, TOL_BF16, TOL_FP32, load_golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+REF_CASES = sorted(p.split("/")[-1] for p in glob.glob(str(GOLDEN / "ref_*.npz")))
+
+
+def _t(a, dtype=None):
+    t = torch.from_numpy(np.asarray(a))
+    return t if dtype is None else t.to(dtype)
+
+
+def run_operator(pkg, x, A, B, C, chunk, init=None, dY=None, dfinal=None, cache=None):
+    """fused_ssd_scan forward + backward on the GPU; returns CPU tensors."""
+    leaves = [t.detach().to(DEV).requires_grad_(True) for t in (x, A, B, C)]
+    il = init.detach().to(DEV).requires_grad_(True) if init is not None else None
+    Y, fs, ch = pkg.fused_ssd_scan(*leaves, chunk, il, cache)
+    res = {"Y": Y.detach().cpu(), "final": fs.detach().cpu(), "cache": ch}
+    if dY is not None:
+        outs, gouts = [Y], [dY.to(DEV).to(Y.dtype)]
+        if dfinal is not None:
+            outs.append(fs)
+            gouts.append(dfinal.to(DEV).to(fs.dtype))
+        ins = leaves + ([il] if il is not None else [])
+        grads = torch.autograd.grad(outs, ins, gouts, allow_unused=True)
+        for k, g in zip(("dx", "dA", "dB", "dC", "dinit"), grads):
+            res[k] = None if g is None else g.detach().cpu()
+    torch.cuda.synchronize()
+    return res
+
+
+@pytest.mark.parametrize("name", REF_CASES)
+def test_fp32_against_reference_fixtures(pkg, cabi, name):
+    g = load_golden(name)
+    chunk = int(g["chunk"])
+    init = _t(g["init"]) if g["init"].size else None
+    dfinal = _t(g["dfinal"]) if g["dfinal"].size else None
+    r = run_operator(pkg, _t(g["x"]), _t(g["A"]), _t(g["B"]), _t(g["C"]), chunk, init, _t(g["dY"]), dfinal)
+    assert rel_err(r["Y"], _t(g["Y"])) < TOL_FP32
+    assert rel_err(r["final"], _t(g["final_state"])) < TOL_FP32
+    assert rel_err(r["cache"]["A_cumsum"], _t(g["A_cumsum"])) < TOL_FP32
+    for k in ("dx", "dA", "dB", "dC"):
+        assert rel_err(r[k], _t(g[k])) < TOL_FP32, k
+    if init is not None:
+        assert rel_err(r["dinit"], _t(g["dinit"])) < TOL_FP32
+    # cached second call (the caller's beta path): same A and C, shifted x and B; no decay gradient
+    r2 = run_operator(pkg, _t(g["x2"]), _t(g["A"]), _t(g["B2"]), _t(g["C"]), chunk, None, _t(g["dY"]), None,
+                      cache=r["cache"])
+    assert rel_err(r2["Y"], _t(g["Y_cached"])) < TOL_FP32
+    assert r2["dA"] is None
+    for k in ("dx", "dB", "dC"):
+        assert rel_err(r2[k], _t(g[k + "_cached"])) < TOL_FP32, k
+
+
+@pytest.mark.parametrize("shape", [(2, 512, 4, 32, 8), (2, 256, 4, 16, 8), (1, 1024, 4, 16, 8), (2, 512, 8, 32, 8)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reference_test_shapes(pkg, cabi, oracle, shape, dtype):
+    """Shapes, value ranges and chunk size of the reference's own scan tests
+    (tests/kernels/test_ssd_scan.py:31-52), forward and gradients."""
+    b, T, h, p, n = shape
+    x, A, B, C = pkg.make_reference_test_inputs(b, T, h, p, n, dtype, seed=0)
+    gen = torch.Generator().manual_seed(5)
+    dY = torch.randn(b, T, h, p, generator=gen).to(dtype)
+    r = run_operator(pkg, x, A, B, C, 128, None, dY)
+    lv = [t.float().requires_grad_(True) for t in (x, A, B, C)]
+    Yo, fo, co = oracle.ssd_chunked(*lv, 128)
+    go = torch.autograd.grad([Yo], lv, [dY.float()])
+    tol = TOL_FP32 if dtype == torch.float32 else TOL_BF16
+    assert r["Y"].dtype == dtype and r["final"].dtype == dtype
+    assert rel_err(r["Y"], Yo) < tol and rel_err(r["final"], fo) < tol
+    for k, g in zip(("dx", "dA", "dB", "dC"), go):
+        assert rel_err(r[k], g) < tol, k
+    # cache contract: keys and shapes (tests/kernels/test_ssd_scan.py:99-110), values as the reference builds them
+    c = T // 128
+    cache = r["cache"]
+    assert set(cache.keys()) == {"L", "decay_chunk", "A_cumsum"}
+    assert cache["A_cumsum"].shape == (b, h, c, 128)
+    assert cache["L"].shape == (b, h, c, 128, 128) and cache["decay_chunk"].shape == (b, h, c + 1, c + 1)
+    assert rel_err(cache["L"], co["L"]) < tol and rel_err(cache["decay_chunk"], co["decay_chunk"]) < tol
+
+
+def mamba2_gpu(pkg, inp, chunk, init=None, dfinal=None):
+    leaves = {k: inp[k].detach().to(DEV).requires_grad_(True) for k in ("x", "dt", "A_head", "B", "C", "D")}
+    il = init.detach().to(DEV).requires_grad_(True) if init is not None else None
+    y, fs = pkg.ssd_mamba2(leaves["x"], leaves["dt"], leaves["A_head"], leaves["B"], leaves["C"], leaves["D"], chunk, il)
+    outs, gouts = [y], [inp["dy"].to(DEV)]
+    if dfinal is not None:
+        outs.append(fs)
+        gouts.append(dfinal.to(DEV))
+    ins = list(leaves.values()) + ([il] if il is not None else [])
+    grads = torch.autograd.grad(outs, ins, gouts)
+    res = {"y": y.detach().cpu(), "final_state": fs.detach().cpu()}
+    for k, g in zip(list(leaves.keys()) + (["init"] if il is not None else []), grads):
+        res["d" + k] = g.detach().cpu()
+    torch.cuda.synchronize()
+    return res
+
+
+def check_mamba2(pkg, oracle, cfg, tol, init=False, dfinal=False, seed=None):
+    inp = pkg.make_inputs(cfg, seed=seed)
+    g = torch.Generator().manual_seed(77)
+    i0 = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g) * 0.2 if init else None
+    df = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g) if dfinal else None
+    got = mamba2_gpu(pkg, inp, cfg.chunk, i0, df)
+    want = oracle.mamba2_fwd_bwd(inp, cfg.chunk, torch.float32, None if i0 is None else i0.unsqueeze(1), df)
+    errs = {k: rel_err(got[k], want[k].reshape(got[k].shape)) for k in got}
+    bad = {k: v for k, v in errs.items() if not v < tol}
+    assert not bad, (cfg.name, errs)
+    return errs
+
+
+def test_config0_fp32_full_size(pkg, cabi, oracle):
+    check_mamba2(pkg, oracle, pkg.CONFIGS[0], TOL_FP32)
+
+
+def test_config0_fp32_with_states(pkg, cabi, oracle):
+    check_mamba2(pkg, oracle, pkg.CONFIGS[0], TOL_FP32, init=True, dfinal=True)
+
+
+@pytest.mark.parametrize("path", ["simt", "auto"])
+@pytest.mark.parametrize("idx,batch,seqlen", [(1, 2, 512), (2, 1, 512), (2, 2, 256)])
+def test_bf16_config_shapes_reduced(pkg, cabi, oracle, idx, batch, seqlen, path):
+    """Per-token shapes of the bf16 benchmark configurations at oracle-sized batch / sequence."""
+    pkg.set_kernel_path(path)
+    try:
+        check_mamba2(pkg, oracle, pkg.shrink(pkg.CONFIGS[idx], batch, seqlen), TOL_BF16, init=(batch == 2),
+                     dfinal=(batch == 2))
+    finally:
+        pkg.set_kernel_path("auto")
+
+
+@pytest.mark.parametrize("h,p,n,g,l,T", [(3, 24, 12, 1, 32, 96), (4, 80, 40, 2, 48, 96), (6, 16, 72, 3, 100, 200),
+                                         (2, 128, 130, 1, 64, 64), (2, 8, 8, 2, 16, 16)])
+def test_ragged_shapes_fp32(pkg, cabi, oracle, h, p, n, g, l, T):
+    """Sizes that are not multiples of the 64-wide tiles, odd head/group counts, a single chunk."""
+    cfg = replace(pkg.CONFIGS[0], batch=2, seqlen=T, nheads=h, headdim=p, d_state=n, ngroups=g, chunk=l)
+    check_mamba2(pkg, oracle, cfg, TOL_FP32, init=True, dfinal=True, seed=4242)
+
+
+def test_sequence_split_through_states(pkg, cabi, oracle):
+    """Two halves chained through final_state -> initial_states reproduce the full run (fwd and grads)."""
+    cfg = pkg.shrink(pkg.CONFIGS[0], batch=1, seqlen=256)
+    inp = pkg.make_inputs(cfg)
+    full = mamba2_gpu(pkg, inp, cfg.chunk)
+    lo = {k: (v[:, :128] if v.dim() >= 3 else v) for k, v in inp.items()}
+    hi = {k: (v[:, 128:] if v.dim() >= 3 else v) for k, v in inp.items()}
+    first = mamba2_gpu(pkg, lo, cfg.chunk)
+    second = mamba2_gpu(pkg, hi, cfg.chunk, init=first["final_state"])
+    assert rel_err(torch.cat([first["y"], second["y"]], 1), full["y"]) < TOL_FP32
+    assert rel_err(second["final_state"], full["final_state"]) < TOL_FP32
+    # backward: the second half's d_init is the first half's dfinal
+    first_b = mamba2_gpu(pkg, lo, cfg.chunk, dfinal=second["dinit"])
+    assert rel_err(torch.cat([first_b["dx"], second["dx"]], 1), full["dx"]) < TOL_FP32
+    assert rel_err(torch.cat([first_b["ddt"], second["ddt"]], 1), full["ddt"]) < TOL_FP32
+    assert rel_err(first_b["dA_head"] + second["dA_head"], full["dA_head"]) < TOL_FP32
+
+
+def test_error_behaviour_on_gpu(pkg, cabi):
+    x = torch.zeros(1, 100, 2, 8, device=DEV)
+    A = torch.zeros(1, 100, 2, device=DEV)
+    B = torch.zeros(1, 100, 2, 4, device=DEV)
+    with pytest.raises(AssertionError, match="not divisible"):
+        pkg.fused_ssd_scan(x, A, B, B, 64)
+    with pytest.raises(RuntimeError, match="same dtype"):
+        pkg.fused_ssd_scan(x[:, :64], A[:, :64], B[:, :64].bfloat16(), B[:, :64], 64)
+
+
+def test_noncontiguous_inputs_and_determinism(pkg, cabi):
+    """The caller passes products and padded views (src/mamba_base_engine.py:170-181); results are
+    bitwise reproducible run to run."""
+    x, A, B, C = pkg.make_reference_test_inputs(2, 256, 4, 16, 8, torch.float32, seed=3)
+    xv = torch.cat([x, x], -1).to(DEV)[..., :16]
+    Bv = B.to(DEV).transpose(1, 2).contiguous().transpose(1, 2)
+    assert not xv.is_contiguous() and not Bv.is_contiguous()
+    outs = []
+    for _ in range(2):
+        xl = xv.detach().requires_grad_(True)
+        Al = A.to(DEV).requires_grad_(True)
+        Y, fs, _ = pkg.fused_ssd_scan(xl, Al, Bv, C.to(DEV), 128)
+        gx, gA = torch.autograd.grad([Y], [xl, Al], [torch.ones_like(Y)])
+        outs.append((Y, fs, gx, gA))
+    Yc, fc, _ = pkg.fused_ssd_scan(x.to(DEV), A.to(DEV), B.to(DEV), C.to(DEV), 128)
+    assert torch.equal(outs[0][0], Yc) and torch.equal(outs[0][1], fc)
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
