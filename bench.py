@@ -1,0 +1,296 @@
+#!/usr/bin/env python3
+"""Benchmark of the SSD chunked scan, forward + backward, in tokens/s.
+
+    python bench.py --gpus N --steps K --warmup W [--config I] [--impl ours|reference]
+
+One step = one forward + backward pass of the Mamba-2 style scan operator over one batch of
+seeded synthetic input.  The default workload is the 1.3B-layer shape (batch 16 per GPU, weak
+scaling: every rank runs its own batch, no data-path collective).  For N > 1 the script is
+launched by torchrun, one rank per GPU.
+
+``value``   : tokens/s with inputs resident in HBM (CUDA events, barrier + sync both sides, max over ranks)
+``e2e``     : same metric through the public operator with HOST buffers; every step copies the inputs
+              host->device from pinned memory and all results device->host, inside the timed region
+``roofline``: the dominant kernel's algorithmic bytes / its CUDA-event duration vs the measured HBM peak
+``cpu_baseline`` / ``--impl reference``: the CPU oracle (the reference's eager PyTorch SSD path restated)
+              timed on the host cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 0.0))), "measured"
+    return FALLBACK_HBM_GBS, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v.lower() == "active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_oracle_tokens_per_s(cfg, pkg, repeats: int = 3, target_s: float = 20.0):
+    """Time the CPU oracle (forward + backward) on a bounded sample of the workload."""
+    from oracle import ssd_oracle as O
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    batch, seqlen = 1, min(cfg.seqlen, 1024)
+    small = pkg.shrink(cfg, batch, seqlen)
+    inp = pkg.make_inputs(small)
+    O.mamba2_fwd_bwd(inp, small.chunk)  # warm-up
+    times = []
+    t_begin = time.perf_counter()
+    while len(times) < repeats or (time.perf_counter() - t_begin < target_s / 2 and len(times) < 20):
+        t0 = time.perf_counter()
+        O.mamba2_fwd_bwd(inp, small.chunk)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return small.tokens / med, threads, f"batch {batch} x seqlen {seqlen} of {cfg.name}, fp32 on bf16-rounded inputs, median of {len(times)}"
+
+
+def run_reference(args, cfg, pkg, rank):
+    """The reference arm: the reference's own eager CPU path (restated as the oracle), host cores only."""
+    if rank != 0:
+        return
+    vals = []
+    sample = ""
+    threads = 1
+    for i in range(args.warmup + args.steps):
+        v, threads, sample = cpu_oracle_tokens_per_s(cfg, pkg, repeats=1, target_s=0.0)
+        if i >= args.warmup:
+            vals.append(v)
+    value = statistics.median(vals)
+    small_tokens = min(cfg.seqlen, 1024)
+    line = {
+        "impl": "reference", "metric": "ssd_scan_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * small_tokens / value,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg.name, "note": "CPU arm: the reference has no packaging to install; its eager PyTorch SSD "
+                   "path (restated in oracle/ssd_oracle.py, pinned bit-exact against the imported reference) runs on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", type=int, default=2)
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (debug)")
+    ap.add_argument("--seqlen", type=int, default=0, help="override the sequence length (debug)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    pkg = importlib.import_module("dhammic-ai_b200")
+    cfg = pkg.CONFIGS[args.config]
+    if args.batch or args.seqlen:
+        cfg = pkg.shrink(cfg, args.batch or None, args.seqlen or None)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, cfg, pkg, rank)
+        return
+
+    import torch.distributed as dist
+    cabi = importlib.import_module("dhammic-ai_b200._cabi")
+    cabi.load()  # fails loudly if the CUDA library is missing
+    pkg.set_kernel_path(args.path)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize(dev)
+
+    host = pkg.make_inputs(cfg, rank=rank)
+    names = ("x", "dt", "A_head", "B", "C", "D", "dy")
+    pinned = {k: host[k].pin_memory() for k in names}
+    devin = {k: pinned[k].to(dev, non_blocking=True) for k in names}
+    leaves = {k: devin[k].detach().requires_grad_(True) for k in names if k != "dy"}
+
+    def step_device():
+        y, _ = pkg.ssd_mamba2(leaves["x"], leaves["dt"], leaves["A_head"], leaves["B"], leaves["C"], leaves["D"],
+                              cfg.chunk)
+        return y, torch.autograd.grad([y], list(leaves.values()), [devin["dy"]])
+
+    for _ in range(args.warmup):
+        step_device()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = cabi.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step_device()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = cabi.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    tokens_all = cfg.tokens * world
+    value = tokens_all * args.steps / (ms_max * 1e-3)
+
+    # per-kernel durations (CUDA events inside the library, on the launching stream), same steps again
+    cabi.profile_enable(True)
+    for _ in range(args.steps):
+        step_device()
+    torch.cuda.synchronize(dev)
+    prof = cabi.profile_read()
+    cabi.profile_enable(False)
+    hbm_peak, tc_peak, peak_kind = measured_peaks()
+    total_kernel_ms = sum(v[0] for v in prof.values()) or 1.0
+    kernels = {k: {"ms_per_launch": v[0] / v[1], "launches_per_step": v[1] / args.steps,
+                   "share": v[0] / total_kernel_ms} for k, v in prof.items()}
+    top = max(prof.items(), key=lambda kv: kv[1][0])[0]
+    alg = pkg.kernel_algorithmic_bytes(cfg)
+    top_bytes = alg.get(top, 0)
+    top_ms = kernels[top]["ms_per_launch"]
+    achieved = top_bytes / (top_ms * 1e-3) / 1e9 if top_bytes else 0.0
+    step_bytes = cfg.bytes_per_token() * cfg.tokens
+    step_flops = cfg.flops_per_token() * cfg.tokens
+    ms_step = ms_max / args.steps
+    roofline = {
+        "bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+        "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+        "whole_step": {"algorithmic_GB": step_bytes / 1e9, "algorithmic_TFLOP": step_flops / 1e12,
+                       "hbm_frac": step_bytes / (ms_step * 1e-3) / 1e9 / hbm_peak,
+                       "tensor_frac": step_flops / (ms_step * 1e-3) / 1e12 / tc_peak if tc_peak else None},
+        "kernels": kernels,
+    }
+
+    # end to end: host buffers in, host buffers out, through the public operator
+    e2e = None
+    if not args.no_e2e:
+        out_host = None
+        h2d = sum(pinned[k].numel() * pinned[k].element_size() for k in names)
+
+        def step_e2e():
+            nonlocal out_host
+            d = {k: pinned[k].to(dev, non_blocking=True) for k in names}
+            lv = {k: d[k].requires_grad_(True) for k in names if k != "dy"}
+            y, _ = pkg.ssd_mamba2(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
+            grads = torch.autograd.grad([y], list(lv.values()), [d["dy"]])
+            outs = [y.detach(), *grads]
+            if out_host is None:
+                out_host = [torch.empty(o.shape, dtype=o.dtype, pin_memory=True) for o in outs]
+            for o, hbuf in zip(outs, out_host):
+                hbuf.copy_(o, non_blocking=True)
+            return outs
+
+        e2e_steps = max(2, min(args.steps, 5))
+        step_e2e()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            step_e2e()
+        e1.record()
+        barrier()
+        t2 = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        d2h = sum(o.numel() * o.element_size() for o in out_host)
+        e2e = {"value": tokens_all * e2e_steps / (float(t2.item()) * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+
+    cpu_base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v, threads, sample = cpu_oracle_tokens_per_s(cfg, pkg)
+        cpu_base = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": "ssd_scan_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cfg.dtype == "bf16" else "f32",
+            "data": "synthetic",
+            "config": {"workload": cfg.name, "batch_per_gpu": cfg.batch, "seqlen": cfg.seqlen, "nheads": cfg.nheads,
+                       "headdim": cfg.headdim, "d_state": cfg.d_state, "ngroups": cfg.ngroups, "chunk": cfg.chunk,
+                       "parallelism": f"batch-sharded x{world}, no data-path collective",
+                       "kernel_path": pkg.resolved_path_name(cfg), "accumulate": "fp32",
+                       "l2": "inputs larger than L2 (x alone %.0f MB per GPU)" % (cfg.tokens * cfg.nheads * cfg.headdim * 2 / 1e6)},
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_base,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

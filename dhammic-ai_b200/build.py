@@ -40,7 +40,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile csrc/*.cu into csrc/libssd_b200.so (only when sources are newer, unless forced)."""
     if not force and not is_stale():
         return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS, "-lcuda", "-o", str(LIB)] + [str(CSRC / s) for s in SOURCES]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB)] + [str(CSRC / s) for s in SOURCES]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

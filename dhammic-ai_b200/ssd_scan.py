@@ -317,3 +317,13 @@ def ssd_mamba2(x: Tensor, dt: Tensor, A_head: Tensor, B: Tensor, C: Tensor, D: T
     initial_states (b,h,p,n) or (b,1,h,p,n).  Returns (Y, final_state fp32 (b,h,p,n)).
     """
     return _SSDMamba2.apply(x, dt, A_head, B, C, D, int(chunk_size), initial_states)
+
+
+def resolved_path_name(cfg) -> str:
+    """'simt' or 'tc': the kernels the library picks for a workload configuration under the current setting."""
+    lib = _cabi.load()
+    shape = _cabi.Shape(_cabi.ABI_VERSION, _cabi.BF16 if cfg.dtype == "bf16" else _cabi.F32, _cabi.F32, _FORCE_PATH,
+                        cfg.batch, cfg.seqlen, cfg.nheads, cfg.headdim, cfg.d_state, cfg.ngroups, cfg.chunk)
+    rc = lib.ssd_b200_resolve_path(C.byref(shape))
+    _cabi.check(rc)
+    return {_cabi.PATH_SIMT: "simt", _cabi.PATH_TC: "tc"}[rc]

@@ -143,3 +143,28 @@ def make_reference_test_inputs(b: int, seqlen: int, n_heads: int, d_head: int, d
     B = torch.randn(b, seqlen, n_heads, d_state, generator=g) * 0.5
     C = torch.randn(b, seqlen, n_heads, d_state, generator=g) * 0.5
     return tuple(t.to(dtype) for t in (x, A, B, C))
+
+
+def kernel_algorithmic_bytes(cfg: SSDConfig) -> dict[str, int]:
+    """Algorithmic HBM bytes ONE launch of each kernel moves for this workload: the operator inputs it
+    must read and the operator outputs it must write, each once at storage width.  Intermediates
+    (chunk states, cumulative decays, partial sums) count zero, so a kernel that re-reads or spills
+    shows up as a lower achieved bandwidth."""
+    w = 2 if cfg.dtype == "bf16" else 4
+    ex = cfg.nheads * cfg.headdim * w
+    eb = cfg.ngroups * cfg.d_state * w
+    edt = cfg.nheads * 4
+    tok = cfg.tokens
+    per_token = {
+        "chunk_cumsum": edt,
+        "chunk_state": ex + eb + edt,
+        "chunk_scan": 2 * ex + 2 * eb + edt,
+        "chunk_dstate": ex + eb,
+        "bwd_row": 2 * ex + 3 * eb,
+        "bwd_col": 3 * ex + 3 * eb + edt,
+        "decay_grad": 2 * edt,
+        "tc_fwd_walk": 2 * ex + 2 * eb + edt,
+        "tc_bwd_state": 2 * ex + 2 * eb + edt,
+        "tc_bwd_walk": 3 * ex + 4 * eb + 2 * edt,
+    }
+    return {k: v * tok for k, v in per_token.items()}
