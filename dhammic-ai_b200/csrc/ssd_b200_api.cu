@@ -7,7 +7,7 @@
 #include <cstring>
 
 #include "ssd_simt.cuh"
-#include "ssd_tc.cuh"
+#include "ssd_tc_host.cuh"
 
 #include <atomic>
 #include <vector>
@@ -395,6 +395,21 @@ int ssd_b200_bwd(const ssd_b200_bwd_args* a, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (path == SSD_B200_PATH_TC) return ssd::tc::backward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
     return a->shape.dtype == SSD_B200_BF16 ? simt_bwd<__nv_bfloat16>(a, st) : simt_bwd<float>(a, st);
+}
+
+int ssd_b200_device_status(const ssd_b200_shape* shape, const void* workspace, void* stream) {
+    if (int rc = check_shape(shape)) return rc;
+    if (!workspace) return fail(SSD_B200_EINVAL, "workspace is null");
+    int path = resolve_path(*shape);
+    if (path < 0) return path;
+    if (path != SSD_B200_PATH_TC) return 0;  // only the tensor-core kernels have bounded waits to report
+    int status = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(&status, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(SSD_B200_ECUDA, "device_status: %s", cudaGetErrorString(e));
+    if (status != 0) return fail(SSD_B200_EDEVICE, "a kernel gave up on a bounded wait (status %d); results are invalid", status);
+    return 0;
 }
 
 int ssd_b200_materialize_cache(const ssd_b200_shape* shape, const float* a_cumsum, void* L, void* decay_chunk,

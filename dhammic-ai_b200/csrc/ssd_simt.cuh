@@ -55,6 +55,7 @@ struct Params {
     float* g_row;         // (b,h,T)
     float* g_col;         // (b,h,T)
     float* ddtx;          // (b,h,T)  sum_p dX * x
+    const float* dyx;     // (b,h,T)  sum_p dy * x, or null (then the decay kernel reads x and dy itself)
     float* da;            // (b,T,h)
     float* ddt;           // (b,T,h)
     float* dAh_part;      // (b,h)
@@ -688,7 +689,8 @@ __global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
         const int t = hi - 1 - (int)threadIdx.x;
         float v = 0.f;
         if (t >= 0) {
-            v = P.g_row[base + t] - P.g_col[base + t];
+            v = P.g_row[base + t];
+            if (P.g_col) v -= P.g_col[base + t];
             if (t == d.T - 1) v += gfin;
         }
         float incl = v;
@@ -724,10 +726,14 @@ __global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
             const T* x = (const T*)P.x;
             const T* dy = (const T*)P.dy;
             float v = 0.f;
-            for (size_t e = threadIdx.x; e < (size_t)d.T * d.p; e += NTHR) {
-                int t = (int)(e / d.p), pp = (int)(e - (size_t)t * d.p);
-                size_t o = x_off(d, bb, t, hh) + pp;
-                v += to_f(x[o]) * to_f(dy[o]);
+            if (P.dyx) {
+                for (int t = threadIdx.x; t < d.T; t += NTHR) v += P.dyx[base + t];
+            } else {
+                for (size_t e = threadIdx.x; e < (size_t)d.T * d.p; e += NTHR) {
+                    int t = (int)(e / d.p), pp = (int)(e - (size_t)t * d.p);
+                    size_t o = x_off(d, bb, t, hh) + pp;
+                    v += to_f(x[o]) * to_f(dy[o]);
+                }
             }
             float sd = block_sum(v, red);
             if (threadIdx.x == 0) P.dD_part[(size_t)bb * d.h + hh] = sd;

@@ -1,0 +1,209 @@
+// Host side of the tensor-core path: tensor maps, workspace layout and launches.
+#pragma once
+#include <cstdio>
+
+#include "../../include/ssd_b200.h"
+#include "ssd_tc.cuh"
+
+namespace ssd {
+namespace tc {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so that the library links against the CUDA
+// runtime only and loads on machines without a driver.
+inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+// 2D bf16 tensor [rows][cols] (cols contiguous), box 64 columns x 128 rows, 128-byte swizzle.
+inline bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t es[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Ws {
+    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, dAh_part, dD_part, total;
+};
+
+inline Ws ws_layout(const Dims& d, int pass) {
+    Ws w{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off += (bytes + 255) / 256 * 256;
+        return o;
+    };
+    const size_t bht = (size_t)d.b * d.h * d.T * 4;
+    const size_t bhpn = (size_t)d.b * d.h * d.p * d.n * 4;
+    const size_t st = (size_t)d.b * (d.T / LT) * d.h * DN * HP * 2;
+    w.status = take(256);
+    w.tcum = take(bht);
+    w.dtT = take(bht);
+    if (pass == SSD_B200_PASS_BWD) {
+        w.Hst = take(st);
+        w.Qst = take(st);
+        w.final_state = take(bhpn);
+        w.dinit = take(bhpn);
+        w.g = take(bht);
+        w.ddtx = take(bht);
+        w.dyx = take(bht);
+        w.dAh_part = take((size_t)d.b * d.h * 4);
+        w.dD_part = take((size_t)d.b * d.h * 4);
+    }
+    w.total = off;
+    return w;
+}
+
+inline size_t workspace_bytes(const Dims& d, int pass) { return ws_layout(d, pass).total; }
+
+#define SSD_TC_FAIL(code, ...)              \
+    do {                                    \
+        snprintf(err, errn, __VA_ARGS__);   \
+        return code;                        \
+    } while (0)
+
+#define SSD_TC_CHECK(what)                                                                        \
+    do {                                                                                          \
+        cudaError_t e_ = cudaGetLastError();                                                      \
+        if (e_ != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "%s: %s", what, cudaGetErrorString(e_)); \
+    } while (0)
+
+inline int set_walk_attrs(char* err, size_t errn) {
+    cudaError_t e = cudaFuncSetAttribute(walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWalkSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWalkSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWalkSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem);
+    if (e != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "set shared memory size: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+inline int launch_tile_cumsum(const Dims& d, const float* cum, const float* dt, float* tcum, float* dtT,
+                              cudaStream_t st, char* err, size_t errn) {
+    dim3 g((d.T + 255) / 256, d.h, d.b);
+    SSD_LAUNCH(prof::K_TC_AUX, st, tile_cumsum_kernel<<<g, 256, 0, st>>>(cum, dt, tcum, dtT, d.b, d.T, d.h, d.l));
+    SSD_TC_CHECK("tile_cumsum");
+    return 0;
+}
+
+inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, char* err, size_t errn) {
+    Ws w = ws_layout(d, SSD_B200_PASS_FWD);
+    if (a->workspace_bytes < w.total) SSD_TC_FAIL(SSD_B200_EWORKSPACE, "workspace %zu < %zu", a->workspace_bytes, w.total);
+    if (!encode_fn()) SSD_TC_FAIL(SSD_B200_ECUDA, "cuTensorMapEncodeTiled is not available");
+    for (const void* p : {a->x, a->B, a->C, (const void*)a->y})
+        if ((uintptr_t)p & 15) SSD_TC_FAIL(SSD_B200_EINVAL, "tensor-core path needs 16-byte aligned tensors");
+    char* ws = (char*)a->workspace;
+    int* status = (int*)(ws + w.status);
+    float* tcum = (float*)(ws + w.tcum);
+    float* dtT = a->dt ? (float*)(ws + w.dtT) : nullptr;
+    if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
+    if (!a->cumsum_is_input) {
+        simt::Params P{};
+        P.d = d; P.a = a->a; P.dt = a->dt; P.A_head = a->A_head; P.cum = a->a_cumsum;
+        P.a_is_bf16 = a->shape.a_dtype == SSD_B200_BF16;
+        size_t sm = (size_t)d.l * (d.h + 1) * 4;
+        if (sm > 48 * 1024 &&
+            cudaFuncSetAttribute(simt::chunk_cumsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
+            SSD_TC_FAIL(SSD_B200_ECUDA, "chunk_cumsum: set shared memory size failed");
+        SSD_LAUNCH(prof::K_CUMSUM, st, simt::chunk_cumsum_kernel<<<dim3(d.c, d.b), simt::NTHR, sm, st>>>(P));
+        SSD_TC_CHECK("chunk_cumsum");
+    }
+    if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, st, err, errn)) return rc;
+    if (int rc = set_walk_attrs(err, errn)) return rc;
+    WalkParams P{};
+    const uint64_t rows = (uint64_t)d.b * d.T;
+    bool ok = make_map(&P.mU, a->x, rows, (uint64_t)d.h * HP) && make_map(&P.mV, a->B, rows, (uint64_t)d.g * DN) &&
+              make_map(&P.mC, a->C, rows, (uint64_t)d.g * DN) && make_map(&P.mY, a->y, rows, (uint64_t)d.h * HP);
+    if (!ok) SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
+    P.mS = P.mY;
+    P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.seed = a->init; P.out_state = a->final_state; P.status = status;
+    P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = d.T / LT;
+    SSD_LAUNCH(prof::K_TC_FWD, st, walk_kernel<0><<<dim3(d.h, d.b), 128, kWalkSmem, st>>>(P));
+    SSD_TC_CHECK("tc_fwd_walk");
+    return 0;
+}
+
+inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, char* err, size_t errn) {
+    Ws w = ws_layout(d, SSD_B200_PASS_BWD);
+    if (a->workspace_bytes < w.total) SSD_TC_FAIL(SSD_B200_EWORKSPACE, "workspace %zu < %zu", a->workspace_bytes, w.total);
+    if (!encode_fn()) SSD_TC_FAIL(SSD_B200_ECUDA, "cuTensorMapEncodeTiled is not available");
+    for (const void* p : {a->x, a->B, a->C, a->dy, (const void*)a->dx, (const void*)a->dB, (const void*)a->dC})
+        if ((uintptr_t)p & 15) SSD_TC_FAIL(SSD_B200_EINVAL, "tensor-core path needs 16-byte aligned tensors");
+    char* ws = (char*)a->workspace;
+    int* status = (int*)(ws + w.status);
+    float* tcum = (float*)(ws + w.tcum);
+    float* dtT = a->dt ? (float*)(ws + w.dtT) : nullptr;
+    void* Hst = ws + w.Hst;
+    void* Qst = ws + w.Qst;
+    float* fin = (float*)(ws + w.final_state);
+    float* dinit = a->dinit ? a->dinit : (float*)(ws + w.dinit);
+    if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
+    if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, st, err, errn)) return rc;
+    if (int rc = set_walk_attrs(err, errn)) return rc;
+    const int nt = d.T / LT;
+    const uint64_t rows = (uint64_t)d.b * d.T, srows = (uint64_t)d.b * nt * d.h * DN;
+    CUtensorMap mX, mdY, mB, mC, mH, mQ, mdX, mdB, mdC;
+    bool ok = make_map(&mX, a->x, rows, (uint64_t)d.h * HP) && make_map(&mdY, a->dy, rows, (uint64_t)d.h * HP) &&
+              make_map(&mB, a->B, rows, (uint64_t)d.g * DN) && make_map(&mC, a->C, rows, (uint64_t)d.g * DN) &&
+              make_map(&mH, Hst, srows, HP) && make_map(&mQ, Qst, srows, HP) &&
+              make_map(&mdX, a->dx, rows, (uint64_t)d.h * HP) && make_map(&mdB, a->dB, rows, (uint64_t)d.g * DN) &&
+              make_map(&mdC, a->dC, rows, (uint64_t)d.g * DN);
+    if (!ok) SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
+    {   // states entering every tile, and the final state
+        WalkParams P{};
+        P.mU = mX; P.mV = mB; P.mC = mC; P.mY = mdX; P.mS = mH;
+        P.tcum = tcum; P.dtT = dtT; P.D = nullptr; P.seed = a->init; P.out_state = fin; P.status = status;
+        P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<1><<<dim3(d.h, d.b), 128, kWalkSmem, st>>>(P));
+        SSD_TC_CHECK("tc_bwd_state");
+    }
+    {   // reverse walk: gradient of the state leaving every tile, and d(initial state)
+        WalkParams P{};
+        P.mU = mdY; P.mV = mC; P.mC = mC; P.mY = mdX; P.mS = mQ;
+        P.tcum = tcum; P.dtT = nullptr; P.D = nullptr; P.seed = a->dfinal; P.out_state = dinit; P.status = status;
+        P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<2><<<dim3(d.h, d.b), 128, kWalkSmem, st>>>(P));
+        SSD_TC_CHECK("tc_bwd_dstate");
+    }
+    {
+        BwdParams P{};
+        P.mX = mX; P.mdY = mdY; P.mB = mB; P.mC = mC; P.mH = mH; P.mQ = mQ; P.mdX = mdX; P.mdB = mdB; P.mdC = mdC;
+        P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
+        P.dyx = (float*)(ws + w.dyx); P.status = status; P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
+        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 128, kBwdSmem, st>>>(P));
+        SSD_TC_CHECK("tc_bwd_walk");
+    }
+    {
+        simt::Params P{};
+        P.d = d; P.x = a->x; P.dy = a->dy; P.dt = a->dt; P.A_head = a->A_head; P.D = a->D; P.dfinal = a->dfinal;
+        P.final_state = fin; P.g_row = (float*)(ws + w.g); P.g_col = nullptr; P.ddtx = (float*)(ws + w.ddtx);
+        P.dyx = (float*)(ws + w.dyx); P.da = a->cumsum_is_input ? nullptr : a->da; P.ddt = a->ddt;
+        P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = (float*)(ws + w.dD_part);
+        SSD_LAUNCH(prof::K_DECAY, st, simt::decay_grad_kernel<__nv_bfloat16><<<dim3(d.h, d.b), simt::NTHR, 0, st>>>(P));
+        SSD_TC_CHECK("decay_grad");
+        if (a->dt) {
+            SSD_LAUNCH(prof::K_REDUCE, st, simt::reduce_batch_kernel<<<(d.h + 127) / 128, 128, 0, st>>>(P.dAh_part, a->dA_head, d.b, d.h));
+            if (a->D) SSD_LAUNCH(prof::K_REDUCE, st, simt::reduce_batch_kernel<<<(d.h + 127) / 128, 128, 0, st>>>(P.dD_part, a->dD, d.b, d.h));
+            SSD_TC_CHECK("reduce_batch");
+        }
+    }
+    return 0;
+}
+
+}  // namespace tc
+}  // namespace ssd

@@ -29,6 +29,7 @@ Y = SSD(x*dt, dt*A_head, B, C) + D*x with gradients dx, ddt, dA_head, dB, dC, dD
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 from torch import Tensor
@@ -37,6 +38,19 @@ from . import _cabi
 
 _EAGER_CACHE = False
 _FORCE_PATH = _cabi.PATH_AUTO
+_CHECK_STATUS = os.environ.get("SSD_B200_CHECK_STATUS", "0") == "1"
+
+
+def set_check_status(flag: bool) -> None:
+    """After every call, synchronise and raise if a kernel reported a bounded wait that ran out
+    (debug / test use: it costs a stream synchronisation per call)."""
+    global _CHECK_STATUS
+    _CHECK_STATUS = bool(flag)
+
+
+def _status(lib, shape, ws, dev) -> None:
+    if _CHECK_STATUS:
+        _cabi.check(lib.ssd_b200_device_status(C.byref(shape), _ptr(ws), _stream(dev)))
 
 
 def set_eager_cache(flag: bool) -> None:
@@ -162,6 +176,7 @@ def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in):
                              _ptr(y), _ptr(final), _ptr(cum), 1 if a_cumsum_in is not None else 0, 0, _ptr(ws),
                              ws.numel())
         _cabi.check(lib.ssd_b200_fwd(C.byref(args), _stream(dev)))
+        _status(lib, shape, ws, dev)
     return y, final, cum, shape
 
 
@@ -225,6 +240,7 @@ class FusedSSDScan(torch.autograd.Function):
                                  _ptr(dB), _ptr(dC), _ptr(da), None, None, None, _ptr(dinit),
                                  1 if ctx.cached else 0, 0, _ptr(ws), ws.numel())
             _cabi.check(lib.ssd_b200_bwd(C.byref(args), _stream(dev)))
+            _status(lib, shape, ws, dev)
         dA = None if da is None else da.to(A.dtype)
         dis = None
         if ctx.has_init:
@@ -303,6 +319,7 @@ class _SSDMamba2(torch.autograd.Function):
                                  _ptr(dx), _ptr(dB), _ptr(dC), None, _ptr(ddt), _ptr(dAh), _ptr(dD), _ptr(dinit),
                                  0, 0, _ptr(ws), ws.numel())
             _cabi.check(lib.ssd_b200_bwd(C.byref(args), _stream(dev)))
+            _status(lib, shape, ws, dev)
         dtd, ahd, dd = ctx.in_dtypes
         return (dx, ddt.to(dtd), dAh.to(ahd), dB, dC, None if dD is None else dD.to(dd), None,
                 None if dinit is None else dinit.reshape(ctx.init_shape))

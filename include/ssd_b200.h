@@ -153,6 +153,13 @@ int ssd_b200_fwd(const ssd_b200_fwd_args *args, void *stream);
 int ssd_b200_bwd(const ssd_b200_bwd_args *args, void *stream);
 
 /*
+ * Optional check after a call (it synchronises `stream`): the tensor-core kernels bound every
+ * wait on a barrier; if one ran out, the kernel finished anyway, set a status word at the start
+ * of the workspace and this returns SSD_B200_EDEVICE.  No counterpart in the reference.
+ */
+int ssd_b200_device_status(const ssd_b200_shape *shape, const void *workspace, void *stream);
+
+/*
  * The reference operator also returns its decay masks as a cache
  * (src/kernels/ssd_scan.py:420, :465; shapes pinned by tests/kernels/test_ssd_scan.py:107-110).
  * This builds them from a_cumsum on demand:

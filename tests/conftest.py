@@ -45,6 +45,14 @@ def cabi():
     return mod
 
 
+@pytest.fixture(scope="session", autouse=True)
+def _check_device_status(request):
+    """On a GPU box every operator call is followed by the library's bounded-wait status check."""
+    if torch.cuda.is_available():
+        importlib.import_module("dhammic-ai_b200").set_check_status(True)
+    yield
+
+
 @pytest.fixture(scope="session")
 def oracle():
     from oracle import ssd_oracle

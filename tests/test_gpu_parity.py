@@ -129,7 +129,7 @@ def test_config0_fp32_with_states(pkg, cabi, oracle):
     check_mamba2(pkg, oracle, pkg.CONFIGS[0], TOL_FP32, init=True, dfinal=True)
 
 
-@pytest.mark.parametrize("path", ["simt", "auto"])
+@pytest.mark.parametrize("path", ["simt", "tc"])
 @pytest.mark.parametrize("idx,batch,seqlen", [(1, 2, 512), (2, 1, 512), (2, 2, 256)])
 def test_bf16_config_shapes_reduced(pkg, cabi, oracle, idx, batch, seqlen, path):
     """Per-token shapes of the bf16 benchmark configurations at oracle-sized batch / sequence."""
@@ -195,3 +195,52 @@ def test_noncontiguous_inputs_and_determinism(pkg, cabi):
     assert torch.equal(outs[0][0], Yc) and torch.equal(outs[0][1], fc)
     for a, b in zip(outs[0], outs[1]):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("chunk", [64, 128, 256])
+@pytest.mark.parametrize("a_dtype", [torch.bfloat16, torch.float32])
+def test_tensor_core_path_operator_form(pkg, cabi, oracle, chunk, a_dtype):
+    """fused_ssd_scan on the tcgen05 kernels (one head per group, as the reference caller uses it):
+    forward, all gradients, initial/final state, and the cached second call."""
+    b, T, h, p, n = 2, 512, 3, 64, 128
+    x, A, B, C = pkg.make_reference_test_inputs(b, T, h, p, n, torch.bfloat16, seed=11)
+    A = (A.float() * 3.0).to(a_dtype)
+    gen = torch.Generator().manual_seed(12)
+    dY = torch.randn(b, T, h, p, generator=gen).bfloat16()
+    init = (torch.randn(b, 1, h, p, n, generator=gen) * 0.3).bfloat16()
+    dfinal = torch.randn(b, h, p, n, generator=gen).bfloat16()
+    pkg.set_kernel_path("tc")
+    try:
+        r = run_operator(pkg, x, A, B, C, chunk, init, dY, dfinal)
+        x2 = torch.nn.functional.pad(x[:, :-1], (0, 0, 0, 0, 1, 0))
+        B2 = torch.nn.functional.pad(B[:, :-1], (0, 0, 0, 0, 1, 0))
+        r2 = run_operator(pkg, x2, A, B2, C, chunk, None, dY, None, cache=r["cache"])
+    finally:
+        pkg.set_kernel_path("auto")
+    lv = [t.float().requires_grad_(True) for t in (x, A, B, C)]
+    il = init.float().requires_grad_(True)
+    Yo, fo, co = oracle.ssd_chunked(*lv, chunk, il)
+    go = torch.autograd.grad([Yo, fo], lv + [il], [dY.float(), dfinal.float()])
+    errs = {"Y": rel_err(r["Y"], Yo), "final": rel_err(r["final"], fo)}
+    for k, g in zip(("dx", "dA", "dB", "dC", "dinit"), go):
+        errs[k] = rel_err(r[k], g)
+    l2 = [t.float().requires_grad_(True) for t in (x2, A, B2, C)]
+    Y2, _, _ = oracle.fused_ssd_scan_oracle(*l2, chunk, None, co)
+    g2 = torch.autograd.grad([Y2], [l2[0], l2[2], l2[3]], [dY.float()])
+    errs["Y_cached"] = rel_err(r2["Y"], Y2)
+    for k, g in zip(("dx", "dB", "dC"), g2):
+        errs[k + "_cached"] = rel_err(r2[k], g)
+    assert r2["dA"] is None
+    bad = {k: v for k, v in errs.items() if not v < TOL_BF16}
+    assert not bad, errs
+
+
+def test_tensor_core_path_is_deterministic_and_selected(pkg, cabi):
+    cfg = pkg.shrink(pkg.CONFIGS[2], 2, 512)
+    assert pkg.resolved_path_name(cfg) == "tc"
+    assert pkg.resolved_path_name(pkg.CONFIGS[0]) == "simt"
+    inp = pkg.make_inputs(cfg)
+    a = mamba2_gpu(pkg, inp, cfg.chunk)
+    b = mamba2_gpu(pkg, inp, cfg.chunk)
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
