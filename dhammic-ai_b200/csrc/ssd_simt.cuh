@@ -61,6 +61,9 @@ struct Params {
     float* dAh_part;      // (b,h)
     float* dD_part;       // (b,h)
     int a_is_bf16;
+    int scan_len;         // decay gradient: 0 = reverse cumsum over the whole sequence (g holds the
+                          // row-minus-column terms), 128 = reverse cumsum inside each 128-tile (g holds the
+                          // gradient with respect to the tile-cumulative log-decay)
 };
 
 __device__ __forceinline__ float load_a(const Params& P, int bb, int t, int hh) {
@@ -673,7 +676,7 @@ __global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
     const int hh = blockIdx.x, bb = blockIdx.y;
     const size_t pn = (size_t)d.p * d.n;
     float gfin = 0.f;
-    if (P.dfinal) {
+    if (P.dfinal && P.scan_len != 128) {
         const float* a = P.dfinal + ((size_t)bb * d.h + hh) * pn;
         const float* f = P.final_state + ((size_t)bb * d.h + hh) * pn;
         float v = 0.f;
@@ -691,7 +694,7 @@ __global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
         if (t >= 0) {
             v = P.g_row[base + t];
             if (P.g_col) v -= P.g_col[base + t];
-            if (t == d.T - 1) v += gfin;
+            if (t == d.T - 1 && P.scan_len != 128) v += gfin;
         }
         float incl = v;
 #pragma unroll
@@ -703,12 +706,13 @@ __global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
         if (lane == 31) wsum[warp] = incl;
         __syncthreads();
         float pre = 0.f, tot = 0.f;
+        const int seg_first = P.scan_len == 128 ? (warp & ~3) : 0;  // 4 warps = one 128-tile
         for (int w = 0; w < NTHR / 32; ++w) {
-            if (w < warp) pre += wsum[w];
+            if (w >= seg_first && w < warp) pre += wsum[w];
             tot += wsum[w];
         }
         const float dA = carry + pre + incl;
-        carry += tot;
+        if (P.scan_len != 128) carry += tot;
         if (t >= 0) {
             const size_t o = ((size_t)bb * d.T + t) * d.h + hh;
             if (P.dt) {

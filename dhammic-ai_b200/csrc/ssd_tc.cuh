@@ -375,6 +375,7 @@ __global__ void __launch_bounds__(128, 1) bwd_tile_kernel(const __grid_constant_
     __shared__ uint64_t bar_cb, bar_ld, bar_m1, bar_m2;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
+    __shared__ float sred[4];
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int k = blockIdx.x, gg = blockIdx.y, bb = blockIdx.z;
@@ -466,6 +467,21 @@ __global__ void __launch_bounds__(128, 1) bwd_tile_kernel(const __grid_constant_
             float2 fy = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&yr[q]));
             dyx += fx.x * fy.x + fx.y * fy.y;
         }
+        // <Q_k, H_k> over this thread's state row (n = tid): the gradient of the inter-tile decay exp(S_k)
+        float qh = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+            uint4 hv = *reinterpret_cast<const uint4*>(sH + sw128(tid, ch));
+            uint4 qv = *reinterpret_cast<const uint4*>(sQ + sw128(tid, ch));
+            const uint32_t* hu = reinterpret_cast<const uint32_t*>(&hv);
+            const uint32_t* qu = reinterpret_cast<const uint32_t*>(&qv);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float2 fh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hu[q]));
+                float2 fq = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu[q]));
+                qh += fh.x * fq.x + fh.y * fq.y;
+            }
+        }
         mbar_wait(&bar_m1, ph, &failed);
         tc_fence_after();
         float rowacc = 0.f;
@@ -481,10 +497,12 @@ __global__ void __launch_bounds__(128, 1) bwd_tile_kernel(const __grid_constant_
                 for (int q = 0; q < 32; ++q) {
                     const int j = cb + q;
                     const float Lv = (j <= tid) ? __expf(cumv - scum[j]) : 0.f;
-                    const float s = __uint_as_float(rs[q]);
-                    gv[q] = s * Lv;
-                    dv[q] = __uint_as_float(rg[q]) * Lv * sdt[j];
-                    rowacc += dv[q] * s;
+                    const float dg = __uint_as_float(rg[q]) * sdt[j];
+                    gv[q] = __uint_as_float(rs[q]) * Lv;
+                    dv[q] = dg * Lv;
+                    // the same bf16-rounded G that the dX product uses, so that row and column sums
+                    // of dG o G cancel exactly
+                    rowacc += dg * __bfloat162float(__float2bfloat16_rn(gv[q]));
                 }
             } else {
 #pragma unroll
@@ -551,7 +569,7 @@ __global__ void __launch_bounds__(128, 1) bwd_tile_kernel(const __grid_constant_
         // per-row epilogue: dx, ddtx, g
         {
             const float Dh = P.D ? P.D[hh] : 0.f;
-            float ddt_acc = 0.f, yo_acc = 0.f;
+            float ddt_acc = 0.f, yo_acc = 0.f, st_acc = 0.f;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t a[32], b2[32], o[32];
@@ -567,19 +585,28 @@ __global__ void __launch_bounds__(128, 1) bwd_tile_kernel(const __grid_constant_
                     const float e0 = __uint_as_float(a[2 * q]) + dj * __uint_as_float(b2[2 * q]);
                     const float e1 = __uint_as_float(a[2 * q + 1]) + dj * __uint_as_float(b2[2 * q + 1]);
                     ddt_acc += e0 * fx.x + e1 * fx.y;
+                    st_acc += __uint_as_float(b2[2 * q]) * fx.x + __uint_as_float(b2[2 * q + 1]) * fx.y;
                     yo_acc += __uint_as_float(o[2 * q]) * fy.x + __uint_as_float(o[2 * q + 1]) * fy.y;
                     dxv[2 * q] = e0 * dtv + Dh * fy.x;
                     dxv[2 * q + 1] = e1 * dtv + Dh * fy.y;
                 }
                 store_row32(sG, tid, half * 32, dxv);
             }
-            P.g[tpos] = rowacc + ei * yo_acc - dtv * ddt_acc;
+            // gradient with respect to the tile-cumulative log-decay at this position; the terms that
+            // act through S_k = cum[127] (state weights d_j and the inter-tile decay) go to the last row
+            const float gi = rowacc + ei * yo_acc - dtv * ddt_acc;
+            float red = dj * dtv * st_acc + __expf(Sk) * qh;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) red += __shfl_xor_sync(0xffffffffu, red, o);
+            if ((tid & 31) == 0) sred[warp] = red;
+            if (tid != LT - 1) P.g[tpos] = gi;
             P.ddtx[tpos] = ddt_acc;
             P.dyx[tpos] = dyx;
+            tc_fence_before();
+            fence_async_smem();
+            __syncthreads();
+            if (tid == LT - 1) P.g[tpos] = gi + sred[0] + sred[1] + sred[2] + sred[3];
         }
-        tc_fence_before();
-        fence_async_smem();
-        __syncthreads();
         if (tid == 0) {
             tma_store_2d(&P.mdX, sG, hh * HP, row0);
             tma_store_commit();

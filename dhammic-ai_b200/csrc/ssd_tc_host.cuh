@@ -194,6 +194,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.final_state = fin; P.g_row = (float*)(ws + w.g); P.g_col = nullptr; P.ddtx = (float*)(ws + w.ddtx);
         P.dyx = (float*)(ws + w.dyx); P.da = a->cumsum_is_input ? nullptr : a->da; P.ddt = a->ddt;
         P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = (float*)(ws + w.dD_part);
+        P.scan_len = LT;
         SSD_LAUNCH(prof::K_DECAY, st, simt::decay_grad_kernel<__nv_bfloat16><<<dim3(d.h, d.b), simt::NTHR, 0, st>>>(P));
         SSD_TC_CHECK("decay_grad");
         if (a->dt) {
