@@ -10,6 +10,7 @@
 #include "ssd_tc_host.cuh"
 
 #include <atomic>
+#include <mutex>
 #include <vector>
 
 namespace ssd {
@@ -396,6 +397,64 @@ int ssd_b200_bwd(const ssd_b200_bwd_args* a, void* stream) {
     if (path == SSD_B200_PATH_TC) return ssd::tc::backward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
     return a->shape.dtype == SSD_B200_BF16 ? simt_bwd<__nv_bfloat16>(a, st) : simt_bwd<float>(a, st);
 }
+
+// ------------------------------------------------------------------------------------------
+// Forward for callers that cannot hand over a workspace.
+//
+// Some hosts only ever see the device pointers of their inputs and outputs: a plugin running under
+// a framework that owns the whole device-memory pool and gives plugins no allocator, or a process
+// started with a fixed device-memory reservation in which cudaMalloc after start-up is not allowed.
+// Such a caller has nowhere to get the scratch buffer ssd_b200_fwd asks for.  For them the library
+// carries its own scratch: one fixed array in device memory, part of the loaded module.
+//
+// The array below exists once per GPU that loads this library and stays until the process exits.
+// In host code its name is only a handle, not a device address; the address on the current device
+// comes from cudaGetSymbolAddress, looked up the first time the entry point runs on that device.
+// ------------------------------------------------------------------------------------------
+#define SSD_B200_STATIC_SCRATCH_BYTES (64u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[SSD_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mu;
+void* g_static_scratch_addr[64] = {};  // per device ordinal, filled on first use
+
+int static_scratch_on_current_device(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(SSD_B200_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(SSD_B200_EUNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (!g_static_scratch_addr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(SSD_B200_ECUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+        g_static_scratch_addr[dev] = p;
+    }
+    *out = g_static_scratch_addr[dev];
+    return 0;
+}
+}  // namespace
+
+int ssd_b200_fwd_static_scratch(const ssd_b200_fwd_args* a, void* stream) {
+    if (!a) return fail(SSD_B200_EINVAL, "args is null");
+    if (int rc = check_shape(&a->shape)) return rc;
+    int path = resolve_path(a->shape);
+    if (path < 0) return path;
+    const size_t need = ssd_b200_workspace_bytes(&a->shape, SSD_B200_PASS_FWD);
+    if (need > (size_t)SSD_B200_STATIC_SCRATCH_BYTES)
+        return fail(SSD_B200_EWORKSPACE,
+                    "this shape needs %zu bytes of scratch but the built-in array holds %u; use ssd_b200_fwd with a "
+                    "caller workspace", need, (unsigned)SSD_B200_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    if (int rc = static_scratch_on_current_device(&scratch)) return rc;
+    ssd_b200_fwd_args b = *a;
+    b.workspace = scratch;
+    b.workspace_bytes = (size_t)SSD_B200_STATIC_SCRATCH_BYTES;
+    return ssd_b200_fwd(&b, stream);
+}
+
+size_t ssd_b200_static_scratch_bytes(void) { return (size_t)SSD_B200_STATIC_SCRATCH_BYTES; }
 
 int ssd_b200_device_status(const ssd_b200_shape* shape, const void* workspace, void* stream) {
     if (int rc = check_shape(shape)) return rc;

@@ -153,6 +153,30 @@ int ssd_b200_fwd(const ssd_b200_fwd_args *args, void *stream);
 int ssd_b200_bwd(const ssd_b200_bwd_args *args, void *stream);
 
 /*
+ * Forward without a caller workspace.  This entry point has no counterpart in the reference.
+ *
+ * Same arguments and results as ssd_b200_fwd, except that `workspace` and `workspace_bytes` are
+ * ignored: the scratch comes from a fixed array of ssd_b200_static_scratch_bytes() (64 MiB) that
+ * is part of the library's device code.  It is meant for hosts that cannot obtain device memory
+ * of their own -- a plugin under a framework that hands it only input and output pointers, or a
+ * process whose device memory was reserved up front and where cudaMalloc is off limits -- and so
+ * could never supply the buffer ssd_b200_fwd needs.  It calls no cudaMalloc, cudaFree or other
+ * allocating routine (keep the profiling hooks off, they create events).
+ *
+ *   - Limit: a shape whose forward scratch (ssd_b200_workspace_bytes(shape, SSD_B200_PASS_FWD))
+ *     exceeds the array is refused with SSD_B200_EWORKSPACE and a message naming both sizes.
+ *   - Every GPU on which the library is loaded holds the array until the process exits.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  It keeps whatever the previous call left; the
+ *     kernels overwrite what they read and the one word that must start at zero is cleared on
+ *     the stream at the start of each call.  Two calls that overlap on the GPU (different
+ *     streams, or different host threads) race on it: serialise them.
+ */
+int ssd_b200_fwd_static_scratch(const ssd_b200_fwd_args *args, void *stream);
+size_t ssd_b200_static_scratch_bytes(void);
+
+/*
  * Optional check after a call (it synchronises `stream`): the tensor-core kernels bound every
  * wait on a barrier; if one ran out, the kernel finished anyway, set a status word at the start
  * of the workspace and this returns SSD_B200_EDEVICE.  No counterpart in the reference.
