@@ -57,7 +57,7 @@ __global__ void tile_cumsum_kernel(const float* __restrict__ cum, const float* _
         for (int kk = k0; kk < k; ++kk) v += cu[(size_t)kk * l + l - 1];
     }
     const size_t o = ((size_t)bb * h + hh) * T + t;
-    tcum[o] = v;
+    tcum[o] = v * 1.4426950408889634f;  // stored in log2 units: every consumer uses exp2
     if (dt) dtT[o] = dt[((size_t)bb * T + t) * h + hh];
 }
 
@@ -116,233 +116,11 @@ __device__ __forceinline__ void store_row32(uint8_t* panel, int row, int col0_in
     }
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(128, 1) walk_kernel(const __grid_constant__ WalkParams P) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* sV = sm;                    // 2 panels: B (or C in mode 2)   [pos][n]
-    uint8_t* sU = sV + 2 * PANEL;        // 1 panel : x (or dy)            [pos][p]
-    uint8_t* sUd = sU + PANEL;           // 1 panel : weighted copy of sU
-    uint8_t* sH = sUd + PANEL;           // 1 panel : state, bf16, [n][p]
-    uint8_t* sC = sH + PANEL;            // 2 panels: C (mode 0)
-    uint8_t* sG = sC + 2 * PANEL;        // 2 panels: masked C B^T (mode 0); first panel doubles as y staging
-    float* scum = reinterpret_cast<float*>(sG + 2 * PANEL);
-    float* sdt = scum + LT;
-    __shared__ uint64_t bar_ld, bar_m1, bar_m2;
-    __shared__ uint32_t tmem_slot;
-    __shared__ int failed;
-
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int hh = blockIdx.x, bb = blockIdx.y;
-    const int gg = hh / P.hpg;
-    const size_t bh = (size_t)bb * P.h + hh;
-    const float* tcum = P.tcum + bh * P.T;
-    const float* dtT = P.dtT ? P.dtT + bh * P.T : nullptr;
-    constexpr bool REV = (MODE == 2);
-    constexpr uint32_t LOAD_BYTES = (MODE == 0 ? 5 : 3) * PANEL;
-
-    if (tid == 0) {
-        failed = 0;
-        mbar_init(&bar_ld, 1);
-        mbar_init(&bar_m1, 1);
-        mbar_init(&bar_m2, 1);
-        mbar_fence_init();
-        prefetch_tmap(&P.mU);
-        prefetch_tmap(&P.mV);
-    }
-    if (warp == 0) {
-        tmem_alloc(&tmem_slot, 512);
-        tmem_relinquish();
-    }
-    // state row of this thread: n = tid, 64 values over p
-    float H[HP];
-    if (P.seed) {
-        const float* s = P.seed + bh * (size_t)HP * DN;
-#pragma unroll
-        for (int pp = 0; pp < HP; ++pp) H[pp] = s[(size_t)pp * DN + tid];
-    } else {
-#pragma unroll
-        for (int pp = 0; pp < HP; ++pp) H[pp] = 0.f;
-    }
-    {
-        float v[32];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-#pragma unroll
-            for (int q = 0; q < 32; ++q) v[q] = H[half * 32 + q];
-            store_row32(sH, tid, half * 32, v);
-        }
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tm = tmem_slot;
-    const uint32_t tS = tm, tYd = tm + 128, tYo = tm + 192, tHl = tm + 256;
-    const uint32_t lanes = lane_base(warp);
-
-    auto issue_loads = [&](int k) {
-        const int row = bb * P.T + k * LT;
-        mbar_expect_tx(&bar_ld, LOAD_BYTES);
-        tma_load_2d(sU, &P.mU, &bar_ld, hh * HP, row);
-        tma_load_2d(sV, &P.mV, &bar_ld, gg * DN, row);
-        tma_load_2d(sV + PANEL, &P.mV, &bar_ld, gg * DN + 64, row);
-        if (MODE == 0) {
-            tma_load_2d(sC, &P.mC, &bar_ld, gg * DN, row);
-            tma_load_2d(sC + PANEL, &P.mC, &bar_ld, gg * DN + 64, row);
-        }
-    };
-    if (tid == 0) issue_loads(REV ? P.nt - 1 : 0);
-
-    for (int it = 0; it < P.nt; ++it) {
-        const int k = REV ? P.nt - 1 - it : it;
-        const uint32_t ph = it & 1;
-        const float cumv = tcum[(size_t)k * LT + tid];
-        const float dtv = (MODE != 2 && dtT) ? dtT[(size_t)k * LT + tid] : 1.f;
-        scum[tid] = cumv;
-        sdt[tid] = dtv;
-        if (tid == 0) tma_store_wait_read();  // previous tile's store no longer reads sG / sH
-        mbar_wait(&bar_ld, ph, &failed);
-        __syncthreads();
-        const float Sk = scum[LT - 1];
-        if (MODE != 0 && tid == 0) {
-            // sH holds the state entering this tile (H_k, or Q_k in the reverse walk)
-            tma_store_2d(&P.mS, sH, 0, (int)((((size_t)bb * P.nt + k) * P.h + hh) * DN));
-            tma_store_commit();
-        }
-        if (MODE == 0 && tid == 0) {
-            tc_fence_after();
-            const uint32_t c0 = smem_u32(sC), v0 = smem_u32(sV), h0 = smem_u32(sH);
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-                const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                mma_ss(tS, smem_desc(c0 + off, 16, 1024), smem_desc(v0 + off, 16, 1024), kIdescS, kk > 0);
-            }
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-                const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                mma_ss(tYo, smem_desc(c0 + off, 16, 1024), smem_desc(h0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
-            }
-            mma_commit(&bar_m1);
-        }
-        // weighted copy of this thread's row: x * dt * exp(S - cum)   (dy * exp(cum) in the reverse walk)
-        uint32_t xrow[32];
-        if (MODE == 0 && P.D) {
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                uint4 v = *reinterpret_cast<const uint4*>(sU + sw128(tid, ch));
-                xrow[ch * 4 + 0] = v.x; xrow[ch * 4 + 1] = v.y; xrow[ch * 4 + 2] = v.z; xrow[ch * 4 + 3] = v.w;
-            }
-        }
-        const float w = REV ? __expf(cumv) : __expf(Sk - cumv) * dtv;
-        scale_row(sU, sUd, tid, w);
-        if (MODE == 0) {
-            mbar_wait(&bar_m1, ph, &failed);
-            tc_fence_after();
-#pragma unroll 1
-            for (int c0 = 0; c0 < LT; c0 += 32) {
-                float g[32];
-                if (c0 <= warp * 32) {
-                    uint32_t r[32];
-                    tmem_ld32(tS + lanes + c0, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int q = 0; q < 32; ++q) {
-                        const int j = c0 + q;
-                        g[q] = (j <= tid) ? __uint_as_float(r[q]) * __expf(cumv - scum[j]) * sdt[j] : 0.f;
-                    }
-                } else {
-#pragma unroll
-                    for (int q = 0; q < 32; ++q) g[q] = 0.f;
-                }
-                store_row32(sG + (c0 >> 6) * PANEL, tid, c0 & 63, g);
-            }
-            tc_fence_before();
-        }
-        if (MODE != 0 && tid == 0) tma_store_wait_read();  // the state store has read sH before anyone rewrites it
-        fence_async_smem();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            const uint32_t v0 = smem_u32(sV), u0 = smem_u32(sU), ud0 = smem_u32(sUd), g0 = smem_u32(sG);
-            if (MODE == 0) {
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                    mma_ss(tYd, smem_desc(g0 + off, 16, 1024), smem_desc(u0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
-                }
-            }
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-                mma_ss(tHl, smem_desc(v0 + kk * 2048, PANEL, 1024), smem_desc(ud0 + kk * 2048, PANEL, 1024), kIdescMM,
-                       kk > 0);
-            mma_commit(&bar_m2);
-        }
-        mbar_wait(&bar_m2, ph, &failed);
-        tc_fence_after();
-        if (tid == 0 && it + 1 < P.nt) issue_loads(REV ? k - 1 : k + 1);
-        if (MODE == 0) {
-            const float e = __expf(cumv);
-            const float Dh = P.D ? P.D[hh] : 0.f;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t a[32], o[32];
-                tmem_ld32(tYd + lanes + half * 32, a);
-                tmem_ld32(tYo + lanes + half * 32, o);
-                tmem_ld_wait();
-                float y[32];
-#pragma unroll
-                for (int q = 0; q < 32; ++q) y[q] = __uint_as_float(a[q]) + e * __uint_as_float(o[q]);
-                if (P.D) {
-#pragma unroll
-                    for (int q = 0; q < 16; ++q) {
-                        float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xrow[half * 16 + q]));
-                        y[2 * q] += Dh * f.x;
-                        y[2 * q + 1] += Dh * f.y;
-                    }
-                }
-                store_row32(sG, tid, half * 32, y);
-            }
-        }
-        {
-            const float dec = __expf(Sk);
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t r[32];
-                tmem_ld32(tHl + lanes + half * 32, r);
-                tmem_ld_wait();
-                float v[32];
-#pragma unroll
-                for (int q = 0; q < 32; ++q) {
-                    H[half * 32 + q] = dec * H[half * 32 + q] + __uint_as_float(r[q]);
-                    v[q] = H[half * 32 + q];
-                }
-                store_row32(sH, tid, half * 32, v);
-            }
-        }
-        tc_fence_before();
-        fence_async_smem();
-        __syncthreads();
-        if (MODE == 0 && tid == 0) {
-            tma_store_2d(&P.mY, sG, hh * HP, bb * P.T + k * LT);
-            tma_store_commit();
-        }
-    }
-    if (P.out_state) {
-        float* o = P.out_state + bh * (size_t)HP * DN;
-#pragma unroll
-        for (int pp = 0; pp < HP; ++pp) o[(size_t)pp * DN + tid] = H[pp];
-    }
-    if (tid == 0) {
-        tma_store_wait_all();
-        if (failed) atomicExch(P.status, 1);
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tm, 512);
-}
-
-constexpr size_t kWalkSmem = 9 * PANEL + 2 * LT * 4 + 1024;
+}  // namespace tc
+}  // namespace ssd
+#include "ssd_tc_walk.cuh"
+namespace ssd {
+namespace tc {
 
 // ------------------------------------------------------------------------------------------
 struct BwdParams {
@@ -458,8 +236,8 @@ __global__ void __launch_bounds__(128, 1) bwd_tile_kernel(const __grid_constant_
             uint4 u = *reinterpret_cast<const uint4*>(sdY + sw128(tid, ch));
             yr[ch * 4 + 0] = u.x; yr[ch * 4 + 1] = u.y; yr[ch * 4 + 2] = u.z; yr[ch * 4 + 3] = u.w;
         }
-        const float ei = __expf(cumv);
-        const float dj = __expf(Sk - cumv);
+        const float ei = exp2f(cumv);
+        const float dj = exp2f(Sk - cumv);
         float dyx = 0.f;
 #pragma unroll
         for (int q = 0; q < 32; ++q) {
@@ -496,7 +274,7 @@ __global__ void __launch_bounds__(128, 1) bwd_tile_kernel(const __grid_constant_
 #pragma unroll
                 for (int q = 0; q < 32; ++q) {
                     const int j = cb + q;
-                    const float Lv = (j <= tid) ? __expf(cumv - scum[j]) : 0.f;
+                    const float Lv = (j <= tid) ? exp2f(cumv - scum[j]) : 0.f;
                     const float dg = __uint_as_float(rg[q]) * sdt[j];
                     gv[q] = __uint_as_float(rs[q]) * Lv;
                     dv[q] = dg * Lv;
@@ -595,7 +373,7 @@ __global__ void __launch_bounds__(128, 1) bwd_tile_kernel(const __grid_constant_
             // gradient with respect to the tile-cumulative log-decay at this position; the terms that
             // act through S_k = cum[127] (state weights d_j and the inter-tile decay) go to the last row
             const float gi = rowacc + ei * yo_acc - dtv * ddt_acc;
-            float red = dj * dtv * st_acc + __expf(Sk) * qh;
+            float red = dj * dtv * st_acc + exp2f(Sk) * qh;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) red += __shfl_xor_sync(0xffffffffu, red, o);
             if ((tid & 31) == 0) sred[warp] = red;

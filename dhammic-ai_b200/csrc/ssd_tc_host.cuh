@@ -85,9 +85,9 @@ inline size_t workspace_bytes(const Dims& d, int pass) { return ws_layout(d, pas
     } while (0)
 
 inline int set_walk_attrs(char* err, size_t errn) {
-    cudaError_t e = cudaFuncSetAttribute(walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWalkSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWalkSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWalkSmem);
+    cudaError_t e = cudaFuncSetAttribute(walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<0>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<1>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<2>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem);
     if (e != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "set shared memory size: %s", cudaGetErrorString(e));
     return 0;
@@ -133,7 +133,7 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     P.mS = P.mY;
     P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.seed = a->init; P.out_state = a->final_state; P.status = status;
     P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = d.T / LT;
-    SSD_LAUNCH(prof::K_TC_FWD, st, walk_kernel<0><<<dim3(d.h, d.b), 128, kWalkSmem, st>>>(P));
+    SSD_LAUNCH(prof::K_TC_FWD, st, walk_kernel<0><<<dim3(d.h, d.b), 288, WalkCfg<0>::SMEM, st>>>(P));
     SSD_TC_CHECK("tc_fwd_walk");
     return 0;
 }
@@ -169,7 +169,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.mU = mX; P.mV = mB; P.mC = mC; P.mY = mdX; P.mS = mH;
         P.tcum = tcum; P.dtT = dtT; P.D = nullptr; P.seed = a->init; P.out_state = fin; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
-        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<1><<<dim3(d.h, d.b), 128, kWalkSmem, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<1><<<dim3(d.h, d.b), 288, WalkCfg<1>::SMEM, st>>>(P));
         SSD_TC_CHECK("tc_bwd_state");
     }
     {   // reverse walk: gradient of the state leaving every tile, and d(initial state)
@@ -177,7 +177,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.mU = mdY; P.mV = mC; P.mC = mC; P.mY = mdX; P.mS = mQ;
         P.tcum = tcum; P.dtT = nullptr; P.D = nullptr; P.seed = a->dfinal; P.out_state = dinit; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
-        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<2><<<dim3(d.h, d.b), 128, kWalkSmem, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<2><<<dim3(d.h, d.b), 288, WalkCfg<2>::SMEM, st>>>(P));
         SSD_TC_CHECK("tc_bwd_dstate");
     }
     {

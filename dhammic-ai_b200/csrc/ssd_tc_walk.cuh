@@ -1,0 +1,338 @@
+// Tile walk kernels of the tensor-core path (included by ssd_tc.cuh).
+//
+// One CTA per (batch, head) walks the 128-position tiles in order with the recurrent state
+// (64 x 128, fp32) in registers.  Nine warps:
+//   warps 0-7  "row" warps: thread (row = tid & 127, half = tid >> 7) owns TMEM lane `row` and one
+//              half of the columns of every accumulator; they do the decay-mask epilogue, the output
+//              epilogue and the state update;
+//   warp 8     control: one lane issues every TMA load and every tcgen05.mma.
+// Loads are multi-buffered (NST stages), the decay-masked C.B^T operand lives in TMEM (bf16 pairs,
+// A operand of the next MMA), and S = C.B^T of tile k+1 is issued before the epilogue of tile k.
+//
+// mbarriers (phase = tile parity unless noted):
+//   bar_ld[s]  TMA bytes of stage s landed                        (phase = (tile / NST) & 1)
+//   bar_s      S = C.B^T of the tile is in TMEM                   (control -> row warps)
+//   bar_g      masked operand + weighted rows written, 256 arrive (row warps -> control)
+//   bar_m2     every MMA of the tile has completed                (control -> row warps)
+//   bar_h      accumulators read, new state written, 256 arrive   (row warps -> control)
+//
+// MODE 0 forward (writes y), MODE 1 states only (stores the state entering every tile, bf16),
+// MODE 2 reverse walk over dy and C (stores the state gradient leaving every tile).
+#pragma once
+
+namespace ssd {
+namespace tc {
+
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Write 32 fp32 values as bf16 into chunks [chunk0, chunk0+4) of this row of a swizzled panel.
+__device__ __forceinline__ void store_half_row(uint8_t* panel, int row, int chunk0, const float (&v)[32]) {
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+        uint4 o;
+        o.x = pack_bf16(v[ch * 8 + 0], v[ch * 8 + 1]);
+        o.y = pack_bf16(v[ch * 8 + 2], v[ch * 8 + 3]);
+        o.z = pack_bf16(v[ch * 8 + 4], v[ch * 8 + 5]);
+        o.w = pack_bf16(v[ch * 8 + 6], v[ch * 8 + 7]);
+        *reinterpret_cast<uint4*>(panel + sw128(row, chunk0 + ch)) = o;
+    }
+}
+
+template <int MODE>
+struct WalkCfg {
+    static constexpr int NST = (MODE == 0) ? 2 : 3;              // load stages
+    static constexpr int STAGE_PANELS = (MODE == 0) ? 5 : 3;     // V(2) U(1) [C(2)]
+    static constexpr uint32_t STAGE_BYTES = STAGE_PANELS * PANEL;
+    // stages | sUd | sH | sY (mode 0) | scum2[2][128] sf[2][128] | alignment slack
+    static constexpr size_t SMEM = (size_t)NST * STAGE_BYTES + 2 * PANEL + (MODE == 0 ? PANEL : 0) + 4 * LT * 4 + 1024;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ WalkParams P) {
+    using Cfg = WalkCfg<MODE>;
+    constexpr int NST = Cfg::NST;
+    constexpr bool REV = (MODE == 2);
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sStage = sm;                                  // per stage: V panels 0,1 | U | C panels 0,1
+    uint8_t* sUd = sStage + (size_t)NST * Cfg::STAGE_BYTES;  // weighted copy of U
+    uint8_t* sH = sUd + PANEL;                             // state, bf16, [n][p]
+    uint8_t* sY = sH + PANEL;                              // y staging (mode 0 only)
+    float* scum2 = reinterpret_cast<float*>(sH + PANEL + (MODE == 0 ? PANEL : 0));  // [2][128]
+    float* sf = scum2 + 2 * LT;                            // [2][128] column factors dt_j 2^(cend - c_j)
+    __shared__ uint64_t bar_ld[3], bar_s, bar_g, bar_m2, bar_h;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hh = blockIdx.x, bb = blockIdx.y;
+    const int gg = hh / P.hpg;
+    const size_t bh = (size_t)bb * P.h + hh;
+    const int nt = P.nt;
+
+    if (tid == 0) {
+        failed = 0;
+        for (int s = 0; s < NST; ++s) mbar_init(&bar_ld[s], 1);
+        mbar_init(&bar_s, 1);
+        mbar_init(&bar_g, 256);
+        mbar_init(&bar_m2, 1);
+        mbar_init(&bar_h, 256);
+        mbar_fence_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(&tmem_slot, 512);
+        tmem_relinquish();
+    }
+    const int row = tid & 127, hf = (tid >> 7) & 1;
+    // state row of this thread: n = row, p in [hf*32, hf*32+32)
+    float H[32];
+    if (warp < 8) {
+        if (P.seed) {
+            const float* s = P.seed + bh * (size_t)HP * DN;
+#pragma unroll
+            for (int q = 0; q < 32; ++q) H[q] = s[(size_t)(hf * 32 + q) * DN + row];
+        } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q) H[q] = 0.f;
+        }
+        store_half_row(sH, row, hf * 4, H);
+        fence_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = tmem_slot;
+    // S double-buffered [0,256), masked operand (bf16 pairs) [256,320), Yd [320,384), Yo [384,448), Hl [448,512)
+    const uint32_t tG = tm + 256, tYd = tm + 320, tYo = tm + 384, tHl = tm + 448;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ control lane
+        if (lane == 0) {
+            prefetch_tmap(&P.mU);
+            prefetch_tmap(&P.mV);
+            auto issue_loads = [&](int it) {
+                const int k = REV ? nt - 1 - it : it;
+                const int s = it % NST;
+                uint8_t* st = sStage + (size_t)s * Cfg::STAGE_BYTES;
+                const int grow = bb * P.T + k * LT;
+                mbar_expect_tx(&bar_ld[s], Cfg::STAGE_BYTES);
+                tma_load_2d(st, &P.mV, &bar_ld[s], gg * DN, grow);
+                tma_load_2d(st + PANEL, &P.mV, &bar_ld[s], gg * DN + 64, grow);
+                tma_load_2d(st + 2 * PANEL, &P.mU, &bar_ld[s], hh * HP, grow);
+                if (MODE == 0) {
+                    tma_load_2d(st + 3 * PANEL, &P.mC, &bar_ld[s], gg * DN, grow);
+                    tma_load_2d(st + 4 * PANEL, &P.mC, &bar_ld[s], gg * DN + 64, grow);
+                }
+            };
+            auto issue_S = [&](int it) {  // S = C B^T of tile `it` into TMEM buffer it & 1
+                const uint32_t st = smem_u32(sStage + (size_t)(it % NST) * Cfg::STAGE_BYTES);
+                const uint32_t v0 = st, c0 = st + 3 * PANEL, tS = tm + (it & 1) * 128;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
+                    mma_ss(tS, smem_desc(c0 + off, 16, 1024), smem_desc(v0 + off, 16, 1024), kIdescS, kk > 0);
+                }
+                mma_commit(&bar_s);
+            };
+            for (int it = 0; it < NST - 1 && it < nt; ++it) issue_loads(it);
+            for (int it = 0; it < nt; ++it) {
+                const int s = it % NST;
+                const uint32_t ph = it & 1;
+                if (it + NST - 1 < nt) issue_loads(it + NST - 1);  // its stage was released by bar_m2 of tile it-1
+                mbar_wait(&bar_ld[s], (it / NST) & 1, &failed);
+                const uint32_t st = smem_u32(sStage + (size_t)s * Cfg::STAGE_BYTES);
+                const uint32_t v0 = st, u0 = st + 2 * PANEL, c0 = st + 3 * PANEL;
+                if (MODE == 0 && it == 0) issue_S(0);
+                if (it > 0) mbar_wait(&bar_h, (it - 1) & 1, &failed);  // new state in sH, accumulators free
+                tc_fence_after();
+                if (MODE == 0) {
+                    const uint32_t h0 = smem_u32(sH);
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {  // Yo = C H^T : A = C K-major, B = state [n][p] MN-major
+                        const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
+                        mma_ss(tYo, smem_desc(c0 + off, 16, 1024), smem_desc(h0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
+                    }
+                }
+                mbar_wait(&bar_g, ph, &failed);
+                tc_fence_after();
+                if (MODE == 0) {
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)  // Yd = G' x : A in TMEM (K = j), B = x [j][p] MN-major
+                        mma_ts(tYd, tG + kk * 8, smem_desc(u0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
+                }
+                {
+                    const uint32_t ud0 = smem_u32(sUd);
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)  // Hl = V^T Ud : both MN-major, K = position
+                        mma_ss(tHl, smem_desc(v0 + kk * 2048, PANEL, 1024), smem_desc(ud0 + kk * 2048, PANEL, 1024), kIdescMM, kk > 0);
+                }
+                mma_commit(&bar_m2);
+                if (MODE == 0 && it + 1 < nt) {
+                    mbar_wait(&bar_ld[(it + 1) % NST], ((it + 1) / NST) & 1, &failed);
+                    tc_fence_after();
+                    issue_S(it + 1);
+                }
+                mbar_wait(&bar_m2, ph, &failed);  // stage s and sUd may be overwritten from here on
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ row warps
+        const float* tcum = P.tcum + bh * P.T;
+        const float* dtT = (MODE != 2 && P.dtT) ? P.dtT + bh * P.T : nullptr;
+        const uint32_t lanes = lane_base(warp);
+        const float Dh = (MODE == 0 && P.D) ? P.D[hh] : 0.f;
+        // per-tile scalars are fetched one tile ahead
+        auto tile_of = [&](int it) { return REV ? nt - 1 - it : it; };
+        float c_n = tcum[(size_t)tile_of(0) * LT + row];
+        float cend_n = tcum[(size_t)tile_of(0) * LT + (row | 31)];
+        float dt_n = dtT ? dtT[(size_t)tile_of(0) * LT + row] : 1.f;
+
+        for (int it = 0; it < nt; ++it) {
+            const int k = tile_of(it);
+            const int s = it % NST, buf = it & 1;
+            const uint32_t ph = it & 1;
+            const float c_i = c_n, cend = cend_n, dtv = dt_n;
+            if (it + 1 < nt) {
+                const size_t o = (size_t)tile_of(it + 1) * LT;
+                c_n = tcum[o + row];
+                cend_n = tcum[o + (row | 31)];
+                dt_n = dtT ? dtT[o + row] : 1.f;
+            }
+            if (hf == 0) {
+                scum2[buf * LT + row] = c_i;
+                sf[buf * LT + row] = dtv * exp2f(cend - c_i);
+            }
+            if (tid == 0) tma_store_wait_read();  // the previous tile's y / state store has read its staging
+            mbar_wait(&bar_ld[s], (it / NST) & 1, &failed);
+            named_barrier(1, 256);
+            const float Sk = scum2[buf * LT + LT - 1];
+            uint8_t* st = sStage + (size_t)s * Cfg::STAGE_BYTES;
+            uint8_t* sU = st + 2 * PANEL;
+            if (MODE != 0 && tid == 0) {
+                // sH holds the state entering this tile (or the state gradient leaving it, reverse walk)
+                tma_store_2d(&P.mS, sH, 0, (int)((((size_t)bb * nt + k) * P.h + hh) * DN));
+                tma_store_commit();
+            }
+            // this thread's half row of U: keep x for the D skip, write the weighted copy
+            uint32_t xrow[16];
+            {
+                const float w = REV ? exp2f(c_i) : exp2f(Sk - c_i) * dtv;
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint4 v = *reinterpret_cast<const uint4*>(sU + sw128(row, hf * 4 + ch));
+                    uint32_t* u = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        xrow[ch * 4 + q] = u[q];
+                        float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u[q]));
+                        u[q] = pack_bf16(f.x * w, f.y * w);
+                    }
+                    *reinterpret_cast<uint4*>(sUd + sw128(row, hf * 4 + ch)) = v;
+                }
+            }
+            if (MODE == 0) {
+                mbar_wait(&bar_s, ph, &failed);
+                tc_fence_after();
+                const uint32_t tS = tm + (it & 1) * 128;
+                const int rowblk = row & ~31;  // warp-uniform
+                uint32_t packed[32];
+#pragma unroll
+                for (int blk = 0; blk < 2; ++blk) {
+                    const int c0 = hf * 64 + blk * 32;
+                    if (c0 > rowblk) {
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) packed[blk * 16 + q] = 0u;
+                    } else {
+                        uint32_t r[32];
+                        tmem_ld32(tS + lanes + c0, r);
+                        // row factor relative to the block's last column: <= 1 below the diagonal block
+                        const float rf = exp2f(c_i - scum2[buf * LT + c0 + 31]);
+                        const float4* f4 = reinterpret_cast<const float4*>(sf + buf * LT + c0);
+                        tmem_ld_wait();
+                        const bool diag = (c0 == rowblk);
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            const float4 f = f4[q4];
+                            float v0 = __uint_as_float(r[q4 * 4 + 0]) * (rf * f.x);
+                            float v1 = __uint_as_float(r[q4 * 4 + 1]) * (rf * f.y);
+                            float v2 = __uint_as_float(r[q4 * 4 + 2]) * (rf * f.z);
+                            float v3 = __uint_as_float(r[q4 * 4 + 3]) * (rf * f.w);
+                            if (diag) {
+                                const int j = c0 + q4 * 4;
+                                if (j + 0 > row) v0 = 0.f;
+                                if (j + 1 > row) v1 = 0.f;
+                                if (j + 2 > row) v2 = 0.f;
+                                if (j + 3 > row) v3 = 0.f;
+                            }
+                            packed[blk * 16 + q4 * 2] = pack_bf16(v0, v1);
+                            packed[blk * 16 + q4 * 2 + 1] = pack_bf16(v2, v3);
+                        }
+                    }
+                }
+                tmem_st32(tG + lanes + hf * 32, packed);
+                tmem_st_wait();
+            }
+            if (MODE != 0 && tid == 0) tma_store_wait_read();  // the state store has read sH before E2 rewrites it
+            tc_fence_before();
+            fence_async_smem();
+            mbar_arrive(&bar_g);
+
+            mbar_wait(&bar_m2, ph, &failed);
+            tc_fence_after();
+            if (MODE == 0) {
+                uint32_t a[32], o[32];
+                tmem_ld32(tYd + lanes + hf * 32, a);
+                tmem_ld32(tYo + lanes + hf * 32, o);
+                const float e = exp2f(c_i);
+                tmem_ld_wait();
+                float y[32];
+#pragma unroll
+                for (int q = 0; q < 32; ++q) y[q] = __uint_as_float(a[q]) + e * __uint_as_float(o[q]);
+                if (P.D) {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) {
+                        float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xrow[q]));
+                        y[2 * q] += Dh * f.x;
+                        y[2 * q + 1] += Dh * f.y;
+                    }
+                }
+                store_half_row(sY, row, hf * 4, y);
+            }
+            {
+                uint32_t r[32];
+                tmem_ld32(tHl + lanes + hf * 32, r);
+                const float dec = exp2f(Sk);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 32; ++q) H[q] = dec * H[q] + __uint_as_float(r[q]);
+                store_half_row(sH, row, hf * 4, H);
+            }
+            tc_fence_before();
+            fence_async_smem();
+            mbar_arrive(&bar_h);
+            if (MODE == 0) {
+                named_barrier(2, 256);
+                if (tid == 0) {
+                    tma_store_2d(&P.mY, sY, hh * HP, bb * P.T + k * LT);
+                    tma_store_commit();
+                }
+            }
+        }
+        if (P.out_state) {
+            float* o = P.out_state + bh * (size_t)HP * DN;
+#pragma unroll
+            for (int q = 0; q < 32; ++q) o[(size_t)(hf * 32 + q) * DN + row] = H[q];
+        }
+        if (tid == 0) tma_store_wait_all();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && failed) atomicExch(P.status, 1);
+    if (warp == 8) tmem_dealloc(tm, 512);
+}
+
+}  // namespace tc
+}  // namespace ssd
