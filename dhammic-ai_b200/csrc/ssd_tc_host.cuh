@@ -38,7 +38,7 @@ inline bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t c
 }
 
 struct Ws {
-    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, dAh_part, dD_part, total;
+    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, rterm, dAh_part, dD_part, total;
 };
 
 inline Ws ws_layout(const Dims& d, int pass) {
@@ -63,6 +63,7 @@ inline Ws ws_layout(const Dims& d, int pass) {
         w.g = take(bht);
         w.ddtx = take(bht);
         w.dyx = take(bht);
+        w.rterm = take(2 * bht);
         w.dAh_part = take((size_t)d.b * d.h * 4);
         w.dD_part = take((size_t)d.b * d.h * 4);
     }
@@ -174,7 +175,8 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     }
     {   // reverse walk: gradient of the state leaving every tile, and d(initial state)
         WalkParams P{};
-        P.mU = mdY; P.mV = mC; P.mC = mC; P.mY = mdX; P.mS = mQ;
+        P.mU = mdY; P.mV = mC; P.mC = mH; P.mY = mdX; P.mS = mQ;
+        P.rterm = (float*)(ws + w.rterm);
         P.tcum = tcum; P.dtT = nullptr; P.D = nullptr; P.seed = a->dfinal; P.out_state = dinit; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
         SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<2><<<dim3(d.h, d.b), 288, WalkCfg<2>::SMEM, st>>>(P));
@@ -184,8 +186,9 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         BwdParams P{};
         P.mX = mX; P.mdY = mdY; P.mB = mB; P.mC = mC; P.mH = mH; P.mQ = mQ; P.mdX = mdX; P.mdB = mdB; P.mdC = mdC;
         P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
-        P.dyx = (float*)(ws + w.dyx); P.status = status; P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
-        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 128, kBwdSmem, st>>>(P));
+        P.dyx = (float*)(ws + w.dyx); P.rterm = (const float*)(ws + w.rterm); P.status = status; P.T = d.T; P.h = d.h;
+        P.hpg = d.hpg; P.nt = nt; P.b = d.b;
+        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 288, kBwdSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_walk");
     }
     {

@@ -42,8 +42,8 @@ __device__ __forceinline__ void store_half_row(uint8_t* panel, int row, int chun
 
 template <int MODE>
 struct WalkCfg {
-    static constexpr int NST = (MODE == 0) ? 2 : 3;              // load stages
-    static constexpr int STAGE_PANELS = (MODE == 0) ? 5 : 3;     // V(2) U(1) [C(2)]
+    static constexpr int NST = (MODE == 1) ? 3 : 2;                           // load stages
+    static constexpr int STAGE_PANELS = (MODE == 0) ? 5 : (MODE == 2 ? 4 : 3);  // V(2) U(1) [C(2) | H_k(1)]
     static constexpr uint32_t STAGE_BYTES = STAGE_PANELS * PANEL;
     // stages | sUd | sH | sY (mode 0) | scum2[2][128] sf[2][128] | alignment slack
     static constexpr size_t SMEM = (size_t)NST * STAGE_BYTES + 2 * PANEL + (MODE == 0 ? PANEL : 0) + 4 * LT * 4 + 1024;
@@ -125,6 +125,8 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     tma_load_2d(st + 3 * PANEL, &P.mC, &bar_ld[s], gg * DN, grow);
                     tma_load_2d(st + 4 * PANEL, &P.mC, &bar_ld[s], gg * DN + 64, grow);
                 }
+                if (MODE == 2)  // the state that entered this tile in the forward direction (mC = its map here)
+                    tma_load_2d(st + 3 * PANEL, &P.mC, &bar_ld[s], 0, (int)((((size_t)bb * nt + k) * P.h + hh) * DN));
             };
             auto issue_S = [&](int it) {  // S = C B^T of tile `it` into TMEM buffer it & 1
                 const uint32_t st = smem_u32(sStage + (size_t)(it % NST) * Cfg::STAGE_BYTES);
@@ -147,12 +149,15 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 if (MODE == 0 && it == 0) issue_S(0);
                 if (it > 0) mbar_wait(&bar_h, (it - 1) & 1, &failed);  // new state in sH, accumulators free
                 tc_fence_after();
-                if (MODE == 0) {
-                    const uint32_t h0 = smem_u32(sH);
+                if (MODE == 0 || MODE == 2) {
+                    // Yo = C H^T : A = C K-major, B = state [n][p] MN-major.  Forward: the running state in
+                    // sH.  Reverse walk: C is the V operand and H_k comes from the stored forward states.
+                    const uint32_t h0 = MODE == 0 ? smem_u32(sH) : st + 3 * PANEL;
+                    const uint32_t a0 = MODE == 0 ? c0 : v0;
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {  // Yo = C H^T : A = C K-major, B = state [n][p] MN-major
+                    for (int kk = 0; kk < 8; ++kk) {
                         const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                        mma_ss(tYo, smem_desc(c0 + off, 16, 1024), smem_desc(h0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
+                        mma_ss(tYo, smem_desc(a0 + off, 16, 1024), smem_desc(h0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
                     }
                 }
                 mbar_wait(&bar_g, ph, &failed);
@@ -300,6 +305,21 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     }
                 }
                 store_half_row(sY, row, hf * 4, y);
+            }
+            if (MODE == 2) {
+                // state part of the decay gradient of row i: e_i * sum_p dY[i,p] (C_i . H_k[p,:]); each half
+                // of the row writes its own partial
+                uint32_t o[32];
+                tmem_ld32(tYo + lanes + hf * 32, o);
+                const float e = exp2f(c_i);
+                tmem_ld_wait();
+                float acc = 0.f;
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xrow[q]));
+                    acc += __uint_as_float(o[2 * q]) * f.x + __uint_as_float(o[2 * q + 1]) * f.y;
+                }
+                P.rterm[((size_t)hf * gridDim.y * P.h + bh) * P.T + (size_t)k * LT + row] = e * acc;
             }
             {
                 uint32_t r[32];
