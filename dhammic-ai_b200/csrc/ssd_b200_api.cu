@@ -456,6 +456,13 @@ int ssd_b200_fwd_static_scratch(const ssd_b200_fwd_args* a, void* stream) {
 
 size_t ssd_b200_static_scratch_bytes(void) { return (size_t)SSD_B200_STATIC_SCRATCH_BYTES; }
 
+#ifdef SSD_TC_TIMELINE
+int ssd_b200_debug_timeline(long long* out, int n) {
+    if (n > 4096) n = 4096;
+    return cudaMemcpyFromSymbol(out, ssd::tc::g_timeline, (size_t)n * sizeof(long long)) == cudaSuccess ? 0 : -4;
+}
+#endif
+
 int ssd_b200_device_status(const ssd_b200_shape* shape, const void* workspace, void* stream) {
     if (int rc = check_shape(shape)) return rc;
     if (!workspace) return fail(SSD_B200_EINVAL, "workspace is null");

@@ -188,7 +188,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
         P.dyx = (float*)(ws + w.dyx); P.rterm = (const float*)(ws + w.rterm); P.status = status; P.T = d.T; P.h = d.h;
         P.hpg = d.hpg; P.nt = nt; P.b = d.b;
-        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 288, kBwdSmem, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 256, kBwdSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_walk");
     }
     {
