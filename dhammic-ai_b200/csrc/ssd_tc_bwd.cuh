@@ -24,7 +24,7 @@ namespace tc {
 __device__ long long g_timeline[4096];
 #define SSD_TL(slot)                                                                              \
     do {                                                                                          \
-        if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 4096) g_timeline[(slot)] = clock64(); \
+        if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 4096 && (slot) >= 0) g_timeline[(slot)] = clock64(); \
     } while (0)
 #else
 #define SSD_TL(slot) do {} while (0)
@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     const int hpg = P.hpg;
     const int row = tid & 127, hf = tid >> 7;
     const int rowblk = row & ~31;
+    // control thread: lane 0 of warp 4 (rows 0-31, second column half), whose mask work is all zeros
+    constexpr int CTL = 128;
 
     if (tid == 0) {
         failed = 0;
@@ -104,7 +106,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (tid == 0) {
+    if (tid == CTL) {
         mbar_expect_tx(&bar_cb, 4 * PANEL);
         tma_load_2d(sC, &P.mC, &bar_cb, gg * DN, row0);
         tma_load_2d(sC + PANEL, &P.mC, &bar_cb, gg * DN + 64, row0);
@@ -121,6 +123,18 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     const uint32_t lanes = lane_base(warp);
     const uint32_t c0a = smem_u32(sC), b0a = smem_u32(sB), g0a = smem_u32(sG), h0a = smem_u32(sH), q0a = smem_u32(sQ);
     const size_t bhT = (size_t)P.b * P.h * P.T;
+    auto issue_phase1 = [&](int hl) {  // S = C B^T (K = n) and dG = dY x^T (K = p) of head hl
+        const uint32_t x0 = smem_u32(sXY + (2 * (hl & 1)) * PANEL), y0 = x0 + PANEL;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
+            mma_ss(tS, smem_desc(c0a + off, 16, 1024), smem_desc(b0a + off, 16, 1024), kIdescKK128, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+            mma_ss(tdG, smem_desc(y0 + kk * 32, 16, 1024), smem_desc(x0 + kk * 32, 16, 1024), kIdescKK128, kk > 0);
+        mma_commit(&bar_m1);
+    };
 
     float dSsum[64];
 #pragma unroll
@@ -130,6 +144,12 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     float dt_n = P.dtT ? P.dtT[pos_of(0) + row] : 1.f;
     float r0_n = P.rterm[pos_of(0) + row], r1_n = P.rterm[bhT + pos_of(0) + row];
     mbar_wait(&bar_cb, 0, &failed);
+    if (tid == CTL) {
+        mbar_wait(&bar_xy[0], 0, &failed);
+        tc_fence_after();
+        issue_phase1(0);
+        if (hpg > 1) load_xy(1);
+    }
 
     for (int hl = 0; hl < hpg; ++hl) {
         const int hh = gg * hpg + hl, xb = hl & 1, buf = hl & 1;
@@ -149,26 +169,13 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             sfL[buf * LT + row] = exp2f(cend - c_i);
             sdt[buf * LT + row] = dtv;
         }
-        if (tid == 0) tma_store_wait_read();  // the previous head's dx store has read its staging (sG panel 0)
+        if (tid == CTL) tma_store_wait_read();  // the previous head's dx store has read its staging (sG panel 0)
         mbar_wait(&bar_xy[xb], (hl >> 1) & 1, &failed);
         tc_fence_before();
         __syncthreads();  // (A) previous head fully retired by every thread
         uint8_t* sX = sXY + (2 * xb) * PANEL;
         uint8_t* sdY = sX + PANEL;
-        const uint32_t x0 = smem_u32(sX), y0 = x0 + PANEL;
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {  // S = C B^T, K = n
-                const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                mma_ss(tS, smem_desc(c0a + off, 16, 1024), smem_desc(b0a + off, 16, 1024), kIdescKK128, kk > 0);
-            }
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)  // dG = dY x^T, K = p
-                mma_ss(tdG, smem_desc(y0 + kk * 32, 16, 1024), smem_desc(x0 + kk * 32, 16, 1024), kIdescKK128, kk > 0);
-            mma_commit(&bar_m1);
-            if (hl + 1 < hpg) load_xy(hl + 1);  // the other buffer was released by bar_m2 of head hl-1
-        }
+        const uint32_t x0 = smem_u32(sX), y0 = x0 + PANEL;  // phase 1 of this head was issued one step earlier
         const float Sk = scum2[buf * LT + LT - 1];
         // this thread's half rows of x and dy (raw)
         uint32_t xr[16], yr[16];
@@ -269,7 +276,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         tc_fence_before();
         fence_async_smem();
         __syncthreads();  // (B) G, Xd, dYe complete; H / Q read by everyone
-        if (tid == 0) {
+        if (tid == CTL) {
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk)  // dX1 = G^T dY : A = G MN-major (M = j, K = i), B = dY MN-major
@@ -290,7 +297,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         }
         mbar_wait(&bar_m2, ph, &failed);
         tc_fence_after();
-        if (tid == 0 && hl + 1 < hpg) load_hq(hl + 1);
+        if (tid == CTL && hl + 1 < hpg) load_hq(hl + 1);
         float ddt_acc = 0.f, st_acc = 0.f;
         {
             const float Dh = P.D ? P.D[hh] : 0.f;
@@ -327,9 +334,17 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         tc_fence_before();
         fence_async_smem();
         __syncthreads();  // (C) dx staged, partial sums visible, TMEM reads done
-        if (tid == 0) {
+        if (tid == CTL) {
             tma_store_2d(&P.mdX, sG, hh * HP, row0);
             tma_store_commit();
+            if (hl + 1 < hpg) {
+                // everyone has read dX1 / dX2, so S and dG of the next head may overwrite them now; its x / dy
+                // tiles were prefetched during this head, and this head's buffer is free for head hl + 2
+                mbar_wait(&bar_xy[xb ^ 1], ((hl + 1) >> 1) & 1, &failed);
+                tc_fence_after();
+                issue_phase1(hl + 1);
+                if (hl + 2 < hpg) load_xy(hl + 2);
+            }
         }
         if (hf == 0) {
             const float* sp = spart + buf * 5 * LT;
@@ -352,7 +367,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         }
     }
     // ---- group terms: stage sum_h dS as bf16 [i][j] (panel = column half) for the two closing products
-    if (tid == 0) tma_store_wait_read();  // last dx store has read sG panel 0
+    if (tid == CTL) tma_store_wait_read();  // last dx store has read sG panel 0
     {
         float v[32];
 #pragma unroll
@@ -365,7 +380,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     tc_fence_before();
     fence_async_smem();
     __syncthreads();
-    if (tid == 0) {
+    if (tid == CTL) {
         tc_fence_after();
         const uint32_t s0 = smem_u32(sXY);
 #pragma unroll
@@ -395,7 +410,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     tc_fence_before();
     fence_async_smem();
     __syncthreads();
-    if (tid == 0) {
+    if (tid == CTL) {
         tma_store_2d(&P.mdC, sG, gg * DN, row0);
         tma_store_2d(&P.mdC, sG + PANEL, gg * DN + 64, row0);
         tma_store_2d(&P.mdB, sXY + 2 * PANEL, gg * DN, row0);
