@@ -14,7 +14,8 @@ PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA, EDEVICE = 0, -1, -2, -3, -4, -5
 
 EXPORTS = (
-    "ssd_b200_abi_version", "ssd_b200_last_error", "ssd_b200_workspace_bytes", "ssd_b200_resolve_path",
+    "ssd_b200_abi_version", "ssd_b200_last_error", "ssd_b200_workspace_bytes", "ssd_b200_states_bytes",
+    "ssd_b200_resolve_path",
     "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix",
     "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status",
     "ssd_b200_launch_count", "ssd_b200_profile_enable", "ssd_b200_profile_kernels", "ssd_b200_profile_kernel_name",
@@ -32,7 +33,8 @@ class FwdArgs(C.Structure):
     _fields_ = [("shape", Shape), ("x", C.c_void_p), ("a", C.c_void_p), ("dt", C.c_void_p), ("A_head", C.c_void_p),
                 ("D", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("init", C.c_void_p), ("y", C.c_void_p),
                 ("final_state", C.c_void_p), ("a_cumsum", C.c_void_p), ("cumsum_is_input", C.c_int32),
-                ("reserved", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("reserved", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+                ("states", C.c_void_p)]
 
 
 class BwdArgs(C.Structure):
@@ -42,7 +44,7 @@ class BwdArgs(C.Structure):
                 ("dB", C.c_void_p), ("dC", C.c_void_p), ("da", C.c_void_p), ("ddt", C.c_void_p),
                 ("dA_head", C.c_void_p), ("dD", C.c_void_p), ("dinit", C.c_void_p),
                 ("cumsum_is_input", C.c_int32), ("reserved", C.c_int32), ("workspace", C.c_void_p),
-                ("workspace_bytes", C.c_size_t)]
+                ("workspace_bytes", C.c_size_t), ("states", C.c_void_p)]
 
 
 _lib = None
@@ -66,6 +68,8 @@ def load() -> C.CDLL:
     lib.ssd_b200_last_error.restype = C.c_char_p
     lib.ssd_b200_workspace_bytes.restype = C.c_size_t
     lib.ssd_b200_workspace_bytes.argtypes = [C.POINTER(Shape), C.c_int]
+    lib.ssd_b200_states_bytes.restype = C.c_size_t
+    lib.ssd_b200_states_bytes.argtypes = [C.POINTER(Shape)]
     lib.ssd_b200_resolve_path.restype = C.c_int
     lib.ssd_b200_resolve_path.argtypes = [C.POINTER(Shape)]
     lib.ssd_b200_fwd.restype = C.c_int

@@ -369,6 +369,12 @@ size_t ssd_b200_workspace_bytes(const ssd_b200_shape* shape, int pass) {
     return simt_ws(d, pass).total;
 }
 
+size_t ssd_b200_states_bytes(const ssd_b200_shape* shape) {
+    if (check_shape(shape)) return 0;
+    if (resolve_path(*shape) != SSD_B200_PATH_TC) return 0;
+    return ssd::tc::states_bytes(dims_of(*shape));
+}
+
 int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
     if (!a) return fail(SSD_B200_EINVAL, "args is null");
     if (int rc = check_shape(&a->shape)) return rc;
@@ -378,6 +384,7 @@ int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
     if (path < 0) return path;
     if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(SSD_B200_EWORKSPACE, "workspace null or not 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
+    if (a->states && path != SSD_B200_PATH_TC) return fail(SSD_B200_EINVAL, "`states` is only used by the tensor-core path");
     if (path == SSD_B200_PATH_TC) return ssd::tc::forward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
     return a->shape.dtype == SSD_B200_BF16 ? simt_fwd<__nv_bfloat16>(a, st) : simt_fwd<float>(a, st);
 }
@@ -394,6 +401,7 @@ int ssd_b200_bwd(const ssd_b200_bwd_args* a, void* stream) {
     if (path < 0) return path;
     if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(SSD_B200_EWORKSPACE, "workspace null or not 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
+    if (a->states && path != SSD_B200_PATH_TC) return fail(SSD_B200_EINVAL, "`states` is only used by the tensor-core path");
     if (path == SSD_B200_PATH_TC) return ssd::tc::backward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
     return a->shape.dtype == SSD_B200_BF16 ? simt_bwd<__nv_bfloat16>(a, st) : simt_bwd<float>(a, st);
 }
@@ -457,6 +465,10 @@ int ssd_b200_fwd_static_scratch(const ssd_b200_fwd_args* a, void* stream) {
 size_t ssd_b200_static_scratch_bytes(void) { return (size_t)SSD_B200_STATIC_SCRATCH_BYTES; }
 
 #ifdef SSD_TC_TIMELINE
+int ssd_b200_debug_wtimeline(long long* out, int n) {
+    if (n > 4096) n = 4096;
+    return cudaMemcpyFromSymbol(out, ssd::tc::g_wtimeline, (size_t)n * sizeof(long long)) == cudaSuccess ? 0 : -4;
+}
 int ssd_b200_debug_timeline(long long* out, int n) {
     if (n > 4096) n = 4096;
     return cudaMemcpyFromSymbol(out, ssd::tc::g_timeline, (size_t)n * sizeof(long long)) == cudaSuccess ? 0 : -4;

@@ -61,6 +61,10 @@ struct Params {
     float* dAh_part;      // (b,h)
     float* dD_part;       // (b,h)
     int a_is_bf16;
+    const float* g_row2;  // tile form only: second partial of g / ddtx / dyx (column halves), or null
+    const float* ddtx2;
+    const float* dyx2;
+    const float* gS;      // tile form only: (b,h,T/128,8) terms added to the last row of every tile, or null
     int scan_len;         // decay gradient: 0 = reverse cumsum over the whole sequence (g holds the
                           // row-minus-column terms), 128 = reverse cumsum inside each 128-tile (g holds the
                           // gradient with respect to the tile-cumulative log-decay)
@@ -694,6 +698,11 @@ __global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
         if (t >= 0) {
             v = P.g_row[base + t];
             if (P.g_col) v -= P.g_col[base + t];
+            if (P.g_row2) v += P.g_row2[base + t];
+            if (P.gS && (t & 127) == 127) {
+                const float* q = P.gS + (base / 128 + t / 128) * 8;
+                v += ((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]));
+            }
             if (t == d.T - 1 && P.scan_len != 128) v += gfin;
         }
         float incl = v;
@@ -716,7 +725,7 @@ __global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
         if (t >= 0) {
             const size_t o = ((size_t)bb * d.T + t) * d.h + hh;
             if (P.dt) {
-                P.ddt[o] = P.ddtx[base + t] + dA * Ah;
+                P.ddt[o] = P.ddtx[base + t] + (P.ddtx2 ? P.ddtx2[base + t] : 0.f) + dA * Ah;
                 dAh += dA * P.dt[o];
             } else if (P.da) {
                 P.da[o] = dA;
@@ -731,7 +740,7 @@ __global__ void __launch_bounds__(NTHR) decay_grad_kernel(Params P) {
             const T* dy = (const T*)P.dy;
             float v = 0.f;
             if (P.dyx) {
-                for (int t = threadIdx.x; t < d.T; t += NTHR) v += P.dyx[base + t];
+                for (int t = threadIdx.x; t < d.T; t += NTHR) v += P.dyx[base + t] + (P.dyx2 ? P.dyx2[base + t] : 0.f);
             } else {
                 for (size_t e = threadIdx.x; e < (size_t)d.T * d.p; e += NTHR) {
                     int t = (int)(e / d.p), pp = (int)(e - (size_t)t * d.p);

@@ -66,13 +66,14 @@ struct WalkParams {
     CUtensorMap mU;   // x (modes 0,1) or dy (mode 2): 2D [b*T][h*64]
     CUtensorMap mV;   // B (modes 0,1) or C (mode 2):  2D [b*T][g*128]
     CUtensorMap mC;   // C (mode 0)
-    CUtensorMap mY;   // y store (mode 0)
-    CUtensorMap mS;   // state store (modes 1,2): 2D [b*nt*h*128][64]
     const float* tcum;
     const float* dtT;
     const float* D;
     const float* seed;   // init (modes 0,1) or dfinal (mode 2), (b,h,p,n) fp32, may be null
     float* out_state;    // final_state (modes 0,1) or dinit (mode 2), may be null
+    CUtensorMap mY;   // y store (mode 0)
+    CUtensorMap mS;   // state store: 2D [b*nt*h*128][64]
+    int save_states;  // store the state entering every tile of the walk through mS
     float* rterm;        // mode 2: (2,b,h,T) halves of e_i * sum_p dY[i,p] (C_i . H_k[p,:])
     int* status;
     int T, h, hpg, nt;

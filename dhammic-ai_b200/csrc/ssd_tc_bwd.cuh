@@ -38,15 +38,16 @@ struct BwdParams {
     const float* dtT;              // (b,h,T) or null
     const float* D;                // (h) or null
     const float* rterm;            // (2,b,h,T) state part of d/dcum from the reverse walk
-    float* g;                      // (b,h,T)  gradient w.r.t. the tile-cumulative log-decay
-    float* ddtx;                   // (b,h,T)  sum_p dX * x
-    float* dyx;                    // (b,h,T)  sum_p dy * x
+    float* g;                      // (2,b,h,T) per column half: gradient w.r.t. the tile-cumulative log-decay
+    float* ddtx;                   // (2,b,h,T) per column half: sum_p dX * x
+    float* dyx;                    // (2,b,h,T) per column half: sum_p dy * x
+    float* gS;                     // (b,h,nt,8) per warp: terms that act through S = cum[127] of the tile
     int* status;
     int T, h, hpg, nt, b;
 };
 
 
-constexpr size_t kBwdSmem = 12 * PANEL + 6 * LT * 4 + 10 * LT * 4 + 1024;
+constexpr size_t kBwdSmem = 12 * PANEL + 6 * LT * 4 + 1024;
 
 __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant__ BwdParams P) {
     extern __shared__ uint8_t smem_raw[];
@@ -60,11 +61,9 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     float* scum2 = reinterpret_cast<float*>(sQ + PANEL);  // [2][128] each:
     float* sfL = scum2 + 2 * LT;       //   2^(cend - c_j)
     float* sdt = sfL + 2 * LT;         //   dt_j
-    float* spart = sdt + 2 * LT;       // [2][5][128] partial row sums of the second column half
     __shared__ uint64_t bar_cb, bar_xy[2], bar_hq, bar_m1, bar_m2, bar_m3;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
-    __shared__ float sred[4];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k = blockIdx.x, gg = blockIdx.y, bb = blockIdx.z;
@@ -323,17 +322,22 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
                 *reinterpret_cast<uint4*>(sG + sw128(row, hf * 4 + sub * 2 + 1)) = make_uint4(dxp[4], dxp[5], dxp[6], dxp[7]);
             }
         }
-        if (hf == 1) {
-            float* sp = spart + buf * 5 * LT;
-            sp[0 * LT + row] = rowacc;
-            sp[1 * LT + row] = ddt_acc;
-            sp[2 * LT + row] = st_acc;
-            sp[3 * LT + row] = dyx;
-            sp[4 * LT + row] = qh;
+        {
+            // gradient w.r.t. the tile-cumulative log-decay of this row, one partial per column half; the
+            // terms that act through S = cum[127] (state weights d_j and the inter-tile decay) are summed
+            // per warp and added to the tile's last row by the decay kernel, in a fixed order
+            const size_t o = (size_t)hf * bhT + tpos;
+            P.g[o] = rowacc - dtv * ddt_acc + (hf == 0 ? rt0 + rt1 : 0.f);
+            P.ddtx[o] = ddt_acc;
+            P.dyx[o] = dyx;
+            float red = dj * dtv * st_acc + exp2f(Sk) * qh;
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) red += __shfl_xor_sync(0xffffffffu, red, of);
+            if (lane == 0) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + warp] = red;
         }
         tc_fence_before();
         fence_async_smem();
-        __syncthreads();  // (C) dx staged, partial sums visible, TMEM reads done
+        __syncthreads();  // (C) dx staged, TMEM reads done
         if (tid == CTL) {
             tma_store_2d(&P.mdX, sG, hh * HP, row0);
             tma_store_commit();
@@ -345,25 +349,6 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
                 issue_phase1(hl + 1);
                 if (hl + 2 < hpg) load_xy(hl + 2);
             }
-        }
-        if (hf == 0) {
-            const float* sp = spart + buf * 5 * LT;
-            rowacc += sp[0 * LT + row];
-            ddt_acc += sp[1 * LT + row];
-            st_acc += sp[2 * LT + row];
-            dyx += sp[3 * LT + row];
-            qh += sp[4 * LT + row];
-            // gradient w.r.t. the tile-cumulative log-decay of this row; the terms that act through
-            // S = cum[127] (state weights d_j and the inter-tile decay) go to the last row
-            const float gi = rowacc + (rt0 + rt1) - dtv * ddt_acc;
-            float red = dj * dtv * st_acc + exp2f(Sk) * qh;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) red += __shfl_xor_sync(0xffffffffu, red, o);
-            if (lane == 0) sred[warp] = red;
-            named_barrier(3, 128);
-            P.g[tpos] = (row == LT - 1) ? gi + sred[0] + sred[1] + sred[2] + sred[3] : gi;
-            P.ddtx[tpos] = ddt_acc;
-            P.dyx[tpos] = dyx;
         }
     }
     // ---- group terms: stage sum_h dS as bf16 [i][j] (panel = column half) for the two closing products

@@ -38,7 +38,7 @@ inline bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t c
 }
 
 struct Ws {
-    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, rterm, dAh_part, dD_part, total;
+    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, rterm, gS, dAh_part, dD_part, total;
 };
 
 inline Ws ws_layout(const Dims& d, int pass) {
@@ -60,10 +60,11 @@ inline Ws ws_layout(const Dims& d, int pass) {
         w.Qst = take(st);
         w.final_state = take(bhpn);
         w.dinit = take(bhpn);
-        w.g = take(bht);
-        w.ddtx = take(bht);
-        w.dyx = take(bht);
+        w.g = take(2 * bht);
+        w.ddtx = take(2 * bht);
+        w.dyx = take(2 * bht);
         w.rterm = take(2 * bht);
+        w.gS = take((size_t)d.b * d.h * (d.T / LT) * 8 * 4);
         w.dAh_part = take((size_t)d.b * d.h * 4);
         w.dD_part = take((size_t)d.b * d.h * 4);
     }
@@ -72,6 +73,7 @@ inline Ws ws_layout(const Dims& d, int pass) {
 }
 
 inline size_t workspace_bytes(const Dims& d, int pass) { return ws_layout(d, pass).total; }
+inline size_t states_bytes(const Dims& d) { return (size_t)d.b * (d.T / LT) * d.h * DN * HP * 2; }
 
 #define SSD_TC_FAIL(code, ...)              \
     do {                                    \
@@ -130,8 +132,14 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     const uint64_t rows = (uint64_t)d.b * d.T;
     bool ok = make_map(&P.mU, a->x, rows, (uint64_t)d.h * HP) && make_map(&P.mV, a->B, rows, (uint64_t)d.g * DN) &&
               make_map(&P.mC, a->C, rows, (uint64_t)d.g * DN) && make_map(&P.mY, a->y, rows, (uint64_t)d.h * HP);
+    if (a->states && ((uintptr_t)a->states & 15)) SSD_TC_FAIL(SSD_B200_EINVAL, "`states` must be 16-byte aligned");
+    if (ok && a->states) {
+        ok = make_map(&P.mS, a->states, (uint64_t)d.b * (d.T / LT) * d.h * DN, HP);
+        P.save_states = 1;
+    } else {
+        P.mS = P.mY;
+    }
     if (!ok) SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
-    P.mS = P.mY;
     P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.seed = a->init; P.out_state = a->final_state; P.status = status;
     P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = d.T / LT;
     SSD_LAUNCH(prof::K_TC_FWD, st, walk_kernel<0><<<dim3(d.h, d.b), 288, WalkCfg<0>::SMEM, st>>>(P));
@@ -149,7 +157,8 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     int* status = (int*)(ws + w.status);
     float* tcum = (float*)(ws + w.tcum);
     float* dtT = a->dt ? (float*)(ws + w.dtT) : nullptr;
-    void* Hst = ws + w.Hst;
+    const void* Hst = a->states ? a->states : (const void*)(ws + w.Hst);
+    if ((uintptr_t)Hst & 15) SSD_TC_FAIL(SSD_B200_EINVAL, "`states` must be 16-byte aligned");
     void* Qst = ws + w.Qst;
     float* fin = (float*)(ws + w.final_state);
     float* dinit = a->dinit ? a->dinit : (float*)(ws + w.dinit);
@@ -165,9 +174,9 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
               make_map(&mdX, a->dx, rows, (uint64_t)d.h * HP) && make_map(&mdB, a->dB, rows, (uint64_t)d.g * DN) &&
               make_map(&mdC, a->dC, rows, (uint64_t)d.g * DN);
     if (!ok) SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
-    {   // states entering every tile, and the final state
+    if (!a->states) {  // states entering every tile (skipped when the forward saved them)
         WalkParams P{};
-        P.mU = mX; P.mV = mB; P.mC = mC; P.mY = mdX; P.mS = mH;
+        P.mU = mX; P.mV = mB; P.mC = mC; P.mY = mdX; P.mS = mH; P.save_states = 1;
         P.tcum = tcum; P.dtT = dtT; P.D = nullptr; P.seed = a->init; P.out_state = fin; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
         SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<1><<<dim3(d.h, d.b), 288, WalkCfg<1>::SMEM, st>>>(P));
@@ -175,7 +184,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     }
     {   // reverse walk: gradient of the state leaving every tile, and d(initial state)
         WalkParams P{};
-        P.mU = mdY; P.mV = mC; P.mC = mH; P.mY = mdX; P.mS = mQ;
+        P.mU = mdY; P.mV = mC; P.mC = mH; P.mY = mdX; P.mS = mQ; P.save_states = 1;
         P.rterm = (float*)(ws + w.rterm);
         P.tcum = tcum; P.dtT = nullptr; P.D = nullptr; P.seed = a->dfinal; P.out_state = dinit; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
@@ -187,7 +196,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.mX = mX; P.mdY = mdY; P.mB = mB; P.mC = mC; P.mH = mH; P.mQ = mQ; P.mdX = mdX; P.mdB = mdB; P.mdC = mdC;
         P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
         P.dyx = (float*)(ws + w.dyx); P.rterm = (const float*)(ws + w.rterm); P.status = status; P.T = d.T; P.h = d.h;
-        P.hpg = d.hpg; P.nt = nt; P.b = d.b;
+        P.hpg = d.hpg; P.nt = nt; P.b = d.b; P.gS = (float*)(ws + w.gS);
         SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 256, kBwdSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_walk");
     }
@@ -198,6 +207,8 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.dyx = (float*)(ws + w.dyx); P.da = a->cumsum_is_input ? nullptr : a->da; P.ddt = a->ddt;
         P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = (float*)(ws + w.dD_part);
         P.scan_len = LT;
+        const size_t half = (size_t)d.b * d.h * d.T;
+        P.g_row2 = P.g_row + half; P.ddtx2 = P.ddtx + half; P.dyx2 = P.dyx + half; P.gS = (const float*)(ws + w.gS);
         SSD_LAUNCH(prof::K_DECAY, st, simt::decay_grad_kernel<__nv_bfloat16><<<dim3(d.h, d.b), simt::NTHR, 0, st>>>(P));
         SSD_TC_CHECK("decay_grad");
         if (a->dt) {

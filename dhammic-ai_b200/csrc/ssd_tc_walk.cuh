@@ -12,7 +12,8 @@
 // mbarriers (phase = tile parity unless noted):
 //   bar_ld[s]  TMA bytes of stage s landed                        (phase = (tile / NST) & 1)
 //   bar_s      S = C.B^T of the tile is in TMEM                   (control -> row warps)
-//   bar_g      masked operand + weighted rows written, 256 arrive (row warps -> control)
+//   bar_u      weighted rows written, 256 arrive                   (row warps -> control)
+//   bar_g      masked operand written (mode 0), 256 arrive         (row warps -> control)
 //   bar_m2     every MMA of the tile has completed                (control -> row warps)
 //   bar_h      accumulators read, new state written, 256 arrive   (row warps -> control)
 //
@@ -22,6 +23,16 @@
 
 namespace ssd {
 namespace tc {
+
+#ifdef SSD_TC_TIMELINE
+__device__ long long g_wtimeline[4096];
+#define SSD_WTL(slot)                                                                              \
+    do {                                                                                           \
+        if (MODE == 0 && blockIdx.x == 1 && blockIdx.y == 0 && (slot) < 4096 && (slot) >= 0) g_wtimeline[(slot)] = clock64(); \
+    } while (0)
+#else
+#define SSD_WTL(slot) do {} while (0)
+#endif
 
 __device__ __forceinline__ void named_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -37,6 +48,20 @@ __device__ __forceinline__ void store_half_row(uint8_t* panel, int row, int chun
         o.z = pack_bf16(v[ch * 8 + 4], v[ch * 8 + 5]);
         o.w = pack_bf16(v[ch * 8 + 6], v[ch * 8 + 7]);
         *reinterpret_cast<uint4*>(panel + sw128(row, chunk0 + ch)) = o;
+    }
+}
+
+// 32 fp32 state values of (row n, half hf) as 64 contiguous bytes of the [n][p] bf16 state tile `slot`.
+__device__ __forceinline__ void store_state_slot(__nv_bfloat16* slot, int row, int hf, const float (&H)[32]) {
+    uint4* o = reinterpret_cast<uint4*>(slot + (size_t)row * HP + hf * 32);
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+        uint4 v;
+        v.x = pack_bf16(H[ch * 8 + 0], H[ch * 8 + 1]);
+        v.y = pack_bf16(H[ch * 8 + 2], H[ch * 8 + 3]);
+        v.z = pack_bf16(H[ch * 8 + 4], H[ch * 8 + 5]);
+        v.w = pack_bf16(H[ch * 8 + 6], H[ch * 8 + 7]);
+        o[ch] = v;
     }
 }
 
@@ -62,7 +87,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
     uint8_t* sY = sH + PANEL;                              // y staging (mode 0 only)
     float* scum2 = reinterpret_cast<float*>(sH + PANEL + (MODE == 0 ? PANEL : 0));  // [2][128]
     float* sf = scum2 + 2 * LT;                            // [2][128] column factors dt_j 2^(cend - c_j)
-    __shared__ uint64_t bar_ld[3], bar_s, bar_g, bar_m2, bar_h;
+    __shared__ uint64_t bar_ld[3], bar_s, bar_u, bar_g, bar_m2, bar_h;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
 
@@ -76,6 +101,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
         failed = 0;
         for (int s = 0; s < NST; ++s) mbar_init(&bar_ld[s], 1);
         mbar_init(&bar_s, 1);
+        mbar_init(&bar_u, 256);
         mbar_init(&bar_g, 256);
         mbar_init(&bar_m2, 1);
         mbar_init(&bar_h, 256);
@@ -138,7 +164,15 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 }
                 mma_commit(&bar_s);
             };
+            auto state_row = [&](int it) {  // row of tile `it` of this walk in the [b*nt*h*128][64] state tensor
+                const int k = REV ? nt - 1 - it : it;
+                return (int)((((size_t)bb * nt + k) * P.h + hh) * DN);
+            };
             for (int it = 0; it < NST - 1 && it < nt; ++it) issue_loads(it);
+            if (P.save_states) {  // the seed is the state entering the first tile
+                tma_store_2d(&P.mS, sH, 0, state_row(0));
+                tma_store_commit();
+            }
             for (int it = 0; it < nt; ++it) {
                 const int s = it % NST;
                 const uint32_t ph = it & 1;
@@ -147,7 +181,12 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 const uint32_t st = smem_u32(sStage + (size_t)s * Cfg::STAGE_BYTES);
                 const uint32_t v0 = st, u0 = st + 2 * PANEL, c0 = st + 3 * PANEL;
                 if (MODE == 0 && it == 0) issue_S(0);
-                if (it > 0) mbar_wait(&bar_h, (it - 1) & 1, &failed);  // new state in sH, accumulators free
+                if (it > 0) {
+                    mbar_wait(&bar_h, (it - 1) & 1, &failed);  // new state in sH, y staged, accumulators free
+                    if (MODE == 0) tma_store_2d(&P.mY, sY, hh * HP, bb * P.T + (it - 1) * LT);
+                    if (P.save_states) tma_store_2d(&P.mS, sH, 0, state_row(it));
+                    tma_store_commit();
+                }
                 tc_fence_after();
                 if (MODE == 0 || MODE == 2) {
                     // Yo = C H^T : A = C K-major, B = state [n][p] MN-major.  Forward: the running state in
@@ -160,19 +199,22 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                         mma_ss(tYo, smem_desc(a0 + off, 16, 1024), smem_desc(h0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
                     }
                 }
-                mbar_wait(&bar_g, ph, &failed);
+                mbar_wait(&bar_u, ph, &failed);
                 tc_fence_after();
-                if (MODE == 0) {
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)  // Yd = G' x : A in TMEM (K = j), B = x [j][p] MN-major
-                        mma_ts(tYd, tG + kk * 8, smem_desc(u0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
-                }
                 {
                     const uint32_t ud0 = smem_u32(sUd);
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)  // Hl = V^T Ud : both MN-major, K = position
                         mma_ss(tHl, smem_desc(v0 + kk * 2048, PANEL, 1024), smem_desc(ud0 + kk * 2048, PANEL, 1024), kIdescMM, kk > 0);
                 }
+                if (MODE == 0) {
+                    mbar_wait(&bar_g, ph, &failed);
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)  // Yd = G' x : A in TMEM (K = j), B = x [j][p] MN-major
+                        mma_ts(tYd, tG + kk * 8, smem_desc(u0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
+                }
+                tma_store_wait_read();  // the stores issued above have read sH / sY before the row warps rewrite them
                 mma_commit(&bar_m2);
                 if (MODE == 0 && it + 1 < nt) {
                     mbar_wait(&bar_ld[(it + 1) % NST], ((it + 1) / NST) & 1, &failed);
@@ -181,6 +223,12 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 }
                 mbar_wait(&bar_m2, ph, &failed);  // stage s and sUd may be overwritten from here on
             }
+            if (MODE == 0) {
+                mbar_wait(&bar_h, (nt - 1) & 1, &failed);
+                tma_store_2d(&P.mY, sY, hh * HP, bb * P.T + (nt - 1) * LT);
+                tma_store_commit();
+            }
+            tma_store_wait_all();
         }
         __syncwarp();
     } else {
@@ -210,17 +258,12 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 scum2[buf * LT + row] = c_i;
                 sf[buf * LT + row] = dtv * exp2f(cend - c_i);
             }
-            if (tid == 0) tma_store_wait_read();  // the previous tile's y / state store has read its staging
             mbar_wait(&bar_ld[s], (it / NST) & 1, &failed);
             named_barrier(1, 256);
+
             const float Sk = scum2[buf * LT + LT - 1];
             uint8_t* st = sStage + (size_t)s * Cfg::STAGE_BYTES;
             uint8_t* sU = st + 2 * PANEL;
-            if (MODE != 0 && tid == 0) {
-                // sH holds the state entering this tile (or the state gradient leaving it, reverse walk)
-                tma_store_2d(&P.mS, sH, 0, (int)((((size_t)bb * nt + k) * P.h + hh) * DN));
-                tma_store_commit();
-            }
             // this thread's half row of U: keep x for the D skip, write the weighted copy
             uint32_t xrow[16];
             {
@@ -238,6 +281,8 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     *reinterpret_cast<uint4*>(sUd + sw128(row, hf * 4 + ch)) = v;
                 }
             }
+            fence_async_smem();
+            mbar_arrive(&bar_u);
             if (MODE == 0) {
                 mbar_wait(&bar_s, ph, &failed);
                 tc_fence_after();
@@ -280,12 +325,13 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 tmem_st32(tG + lanes + hf * 32, packed);
                 tmem_st_wait();
             }
-            if (MODE != 0 && tid == 0) tma_store_wait_read();  // the state store has read sH before E2 rewrites it
-            tc_fence_before();
-            fence_async_smem();
-            mbar_arrive(&bar_g);
+            if (MODE == 0) {
+                tc_fence_before();
+                mbar_arrive(&bar_g);
+            }
 
             mbar_wait(&bar_m2, ph, &failed);
+
             tc_fence_after();
             if (MODE == 0) {
                 uint32_t a[32], o[32];
@@ -333,20 +379,12 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
             tc_fence_before();
             fence_async_smem();
             mbar_arrive(&bar_h);
-            if (MODE == 0) {
-                named_barrier(2, 256);
-                if (tid == 0) {
-                    tma_store_2d(&P.mY, sY, hh * HP, bb * P.T + k * LT);
-                    tma_store_commit();
-                }
-            }
         }
         if (P.out_state) {
             float* o = P.out_state + bh * (size_t)HP * DN;
 #pragma unroll
             for (int q = 0; q < 32; ++q) o[(size_t)(hf * 32 + q) * DN + row] = H[q];
         }
-        if (tid == 0) tma_store_wait_all();
     }
     tc_fence_before();
     __syncthreads();

@@ -39,6 +39,15 @@ from . import _cabi
 _EAGER_CACHE = False
 _FORCE_PATH = _cabi.PATH_AUTO
 _CHECK_STATUS = os.environ.get("SSD_B200_CHECK_STATUS", "0") == "1"
+_SAVE_STATES = os.environ.get("SSD_B200_SAVE_STATES", "1") == "1"
+
+
+def set_save_states(flag: bool) -> None:
+    """Keep the per-tile recurrent states of the forward for the backward (default on: one bf16 buffer of
+    b*T*h*64 elements, the size of x at d_state 128) instead of recomputing them in the backward, which is
+    what the reference's input-only checkpointing corresponds to (src/kernels/ssd_scan.py:458)."""
+    global _SAVE_STATES
+    _SAVE_STATES = bool(flag)
 
 
 def set_check_status(flag: bool) -> None:
@@ -151,8 +160,8 @@ class LazySSDCache(dict):
         return dict.get(self, key)
 
 
-def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in):
-    """Common forward launcher.  Returns (y, final_state fp32 (b,h,p,n), a_cumsum, shape)."""
+def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=False):
+    """Common forward launcher.  Returns (y, final_state fp32 (b,h,p,n), a_cumsum, shape, states or None)."""
     lib = _cabi.load()
     b, T, h, p = x.shape
     n = B.shape[3]
@@ -172,12 +181,17 @@ def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in):
         else:
             cum = torch.empty(b, h, T // chunk, chunk, dtype=torch.float32, device=dev)
         ws = _workspace(lib, shape, _cabi.PASS_FWD, dev)
+        states = None
+        if want_states and _SAVE_STATES:
+            nbytes = lib.ssd_b200_states_bytes(C.byref(shape))
+            if nbytes:
+                states = torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
         args = _cabi.FwdArgs(shape, _ptr(x), _ptr(a), _ptr(dt), _ptr(A_head), _ptr(D), _ptr(B), _ptr(Cm), _ptr(init4),
                              _ptr(y), _ptr(final), _ptr(cum), 1 if a_cumsum_in is not None else 0, 0, _ptr(ws),
-                             ws.numel())
+                             ws.numel(), _ptr(states))
         _cabi.check(lib.ssd_b200_fwd(C.byref(args), _stream(dev)))
         _status(lib, shape, ws, dev)
-    return y, final, cum, shape
+    return y, final, cum, shape, states
 
 
 class FusedSSDScan(torch.autograd.Function):
@@ -197,8 +211,10 @@ class FusedSSDScan(torch.autograd.Function):
         if initial_states is not None:
             init4 = initial_states.reshape(b, h, p, n).float().contiguous()
         cached = A_cumsum_cache_in is not None
-        y, final, cum, shape = _run_fwd(xc, Ac, None, None, None, Bc, Cc, chunk, init4,
-                                        A_cumsum_cache_in if cached else None)
+        y, final, cum, shape, states = _run_fwd(xc, Ac, None, None, None, Bc, Cc, chunk, init4,
+                                                A_cumsum_cache_in if cached else None,
+                                                want_states=any(ctx.needs_input_grad))
+        ctx.states = states
         ctx.save_for_backward(xc, Ac, Bc, Cc, init4 if init4 is not None else torch.empty(0, device=x.device), cum)
         ctx.chunk = chunk
         ctx.has_init = initial_states is not None
@@ -238,7 +254,7 @@ class FusedSSDScan(torch.autograd.Function):
             args = _cabi.BwdArgs(shape, _ptr(x), _ptr(A), None, None, None, _ptr(B), _ptr(Cm),
                                  _ptr(init4) if ctx.has_init else None, _ptr(cum), _ptr(dy), _ptr(dfin), _ptr(dx),
                                  _ptr(dB), _ptr(dC), _ptr(da), None, None, None, _ptr(dinit),
-                                 1 if ctx.cached else 0, 0, _ptr(ws), ws.numel())
+                                 1 if ctx.cached else 0, 0, _ptr(ws), ws.numel(), _ptr(ctx.states))
             _cabi.check(lib.ssd_b200_bwd(C.byref(args), _stream(dev)))
             _status(lib, shape, ws, dev)
         dA = None if da is None else da.to(A.dtype)
@@ -285,7 +301,9 @@ class _SSDMamba2(torch.autograd.Function):
         b, T, h, p = xc.shape
         n = Bc.shape[3]
         init4 = None if initial_states is None else initial_states.reshape(b, h, p, n).float().contiguous()
-        y, final, cum, shape = _run_fwd(xc, None, dtc, Ah, Dc, Bc, Cc, chunk, init4, None)
+        y, final, cum, shape, states = _run_fwd(xc, None, dtc, Ah, Dc, Bc, Cc, chunk, init4, None,
+                                                want_states=any(ctx.needs_input_grad))
+        ctx.states = states
         ctx.save_for_backward(xc, dtc, Ah, Bc, Cc, cum,
                               Dc if Dc is not None else torch.empty(0, device=x.device),
                               init4 if init4 is not None else torch.empty(0, device=x.device))
@@ -317,7 +335,7 @@ class _SSDMamba2(torch.autograd.Function):
             args = _cabi.BwdArgs(shape, _ptr(x), None, _ptr(dt), _ptr(Ah), _ptr(D) if ctx.has_D else None, _ptr(B),
                                  _ptr(Cm), _ptr(init4) if ctx.has_init else None, _ptr(cum), _ptr(dy), _ptr(dfin),
                                  _ptr(dx), _ptr(dB), _ptr(dC), None, _ptr(ddt), _ptr(dAh), _ptr(dD), _ptr(dinit),
-                                 0, 0, _ptr(ws), ws.numel())
+                                 0, 0, _ptr(ws), ws.numel(), _ptr(ctx.states))
             _cabi.check(lib.ssd_b200_bwd(C.byref(args), _stream(dev)))
             _status(lib, shape, ws, dev)
         dtd, ahd, dd = ctx.in_dtypes

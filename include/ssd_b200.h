@@ -96,6 +96,9 @@ typedef struct ssd_b200_fwd_args {
     int32_t reserved;
     void *workspace;
     size_t workspace_bytes;
+    void *states; /* optional output, ssd_b200_states_bytes() bytes: the recurrent state entering every
+                     128-position tile, in the layout the backward wants.  Passing the same buffer to
+                     ssd_b200_bwd saves it one recomputation pass; NULL = do not save. */
 } ssd_b200_fwd_args;
 
 /*
@@ -133,6 +136,7 @@ typedef struct ssd_b200_bwd_args {
     int32_t reserved;
     void *workspace;
     size_t workspace_bytes;
+    const void *states; /* optional: what the forward wrote into its `states`; NULL = recompute */
 } ssd_b200_bwd_args;
 
 /* ABI version of the loaded library (compare with SSD_B200_ABI_VERSION). */
@@ -144,6 +148,10 @@ const char *ssd_b200_last_error(void);
 
 /* Bytes of workspace one call of the given pass needs for this shape (0 on a bad shape). */
 size_t ssd_b200_workspace_bytes(const ssd_b200_shape *shape, int pass);
+
+/* Bytes of the optional `states` buffer for this shape; 0 when the resolved path does not use one
+ * (then `states` must be NULL). */
+size_t ssd_b200_states_bytes(const ssd_b200_shape *shape);
 
 /* Which path AUTO resolves to for this shape: SSD_B200_PATH_SIMT or SSD_B200_PATH_TC
  * (negative code on a bad shape).  Host-only, needs no GPU. */

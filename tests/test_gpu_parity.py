@@ -244,3 +244,20 @@ def test_tensor_core_path_is_deterministic_and_selected(pkg, cabi):
     b = mamba2_gpu(pkg, inp, cfg.chunk)
     for k in a:
         assert torch.equal(a[k], b[k]), k
+
+
+def test_saved_states_equal_recomputed_states(pkg, cabi):
+    """The backward gives the same gradients whether the forward kept its per-tile states or the
+    backward recomputes them (the reference's input-only checkpointing)."""
+    cfg = pkg.shrink(pkg.CONFIGS[2], 2, 512)
+    inp = pkg.make_inputs(cfg)
+    g = torch.Generator().manual_seed(9)
+    init = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g) * 0.2
+    kept = mamba2_gpu(pkg, inp, cfg.chunk, init)
+    pkg.set_save_states(False)
+    try:
+        redone = mamba2_gpu(pkg, inp, cfg.chunk, init)
+    finally:
+        pkg.set_save_states(True)
+    for k in kept:
+        assert torch.equal(kept[k], redone[k]), k

@@ -33,7 +33,7 @@ def _forward(cabi, pkg, entry, cfg, inp, use_workspace):
     if use_workspace:
         ws = torch.empty(lib.ssd_b200_workspace_bytes(C.byref(shape), cabi.PASS_FWD), dtype=torch.uint8, device=dev)
     args = cabi.FwdArgs(shape, _ptr(x), None, _ptr(dt), _ptr(Ah), _ptr(D), _ptr(B), _ptr(Cm), None, _ptr(y),
-                        _ptr(final), _ptr(cum), 0, 0, _ptr(ws), 0 if ws is None else ws.numel())
+                        _ptr(final), _ptr(cum), 0, 0, _ptr(ws), 0 if ws is None else ws.numel(), None)
     stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
     cabi.check(getattr(lib, entry)(C.byref(args), stream))
     torch.cuda.synchronize(dev)
