@@ -47,21 +47,22 @@ struct BwdParams {
 };
 
 
-constexpr size_t kBwdSmem = 12 * PANEL + 6 * LT * 4 + 1024;
+constexpr size_t kBwdSmem = 13 * PANEL + 6 * LT * 4 + 1024;
 
 __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant__ BwdParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sC = sm;                  // 2 panels [pos][n]
     uint8_t* sB = sC + 2 * PANEL;      // 2 panels [pos][n]
-    uint8_t* sG = sB + 2 * PANEL;      // 2 panels [i][j]; panel 0 doubles as dx staging, both as dC staging
+    uint8_t* sG = sB + 2 * PANEL;      // 2 panels [i][j]; at the end dC staging
     uint8_t* sXY = sG + 2 * PANEL;     // 4 panels: x0, dy0, x1, dy1; at the end sum_h dS (2) and dB staging (2)
     uint8_t* sH = sXY + 4 * PANEL;     // [n][p]
     uint8_t* sQ = sH + PANEL;          // [n][p]
-    float* scum2 = reinterpret_cast<float*>(sQ + PANEL);  // [2][128] each:
+    uint8_t* sdX = sQ + PANEL;         // dx staging
+    float* scum2 = reinterpret_cast<float*>(sdX + PANEL);  // [2][128] each:
     float* sfL = scum2 + 2 * LT;       //   2^(cend - c_j)
     float* sdt = sfL + 2 * LT;         //   dt_j
-    __shared__ uint64_t bar_cb, bar_xy[2], bar_hq, bar_m1, bar_m2, bar_m3;
+    __shared__ uint64_t bar_cb, bar_xy[2], bar_hq, bar_m1, bar_m2, bar_m2b, bar_m3;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
 
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         mbar_init(&bar_hq, 1);
         mbar_init(&bar_m1, 1);
         mbar_init(&bar_m2, 1);
+        mbar_init(&bar_m2b, 1);
         mbar_init(&bar_m3, 1);
         mbar_fence_init();
     }
@@ -102,6 +104,22 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         tma_load_2d(sH, &P.mH, &bar_hq, 0, srow);
         tma_load_2d(sQ, &P.mQ, &bar_hq, 0, srow);
     };
+    const size_t bhT = (size_t)P.b * P.h * P.T;
+    auto pos_of = [&](int hl) { return ((size_t)bb * P.h + gg * hpg + hl) * P.T + (size_t)k * LT; };
+    // per-head row scalars are fetched one head ahead; the shared per-column arrays of head hl + 1 are
+    // written before the last block-wide barrier of head hl
+    float c_n = P.tcum[pos_of(0) + row], cend_n = P.tcum[pos_of(0) + (row | 31)];
+    float dt_n = P.dtT ? P.dtT[pos_of(0) + row] : 1.f;
+    float r0_n = P.rterm[pos_of(0) + row], r1_n = P.rterm[bhT + pos_of(0) + row];
+    float D_n = P.D ? P.D[gg * hpg] : 0.f;
+    auto publish_columns = [&](int buf) {
+        if (hf == 0) {
+            scum2[buf * LT + row] = c_n;
+            sfL[buf * LT + row] = exp2f(cend_n - c_n);
+            sdt[buf * LT + row] = dt_n;
+        }
+    };
+    publish_columns(0);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -121,7 +139,6 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     const uint32_t tS = tm, tdG = tm + 128, tX1 = tm, tX2 = tm + 64, tdC = tm + 256, tdB = tm + 384;
     const uint32_t lanes = lane_base(warp);
     const uint32_t c0a = smem_u32(sC), b0a = smem_u32(sB), g0a = smem_u32(sG), h0a = smem_u32(sH), q0a = smem_u32(sQ);
-    const size_t bhT = (size_t)P.b * P.h * P.T;
     auto issue_phase1 = [&](int hl) {  // S = C B^T (K = n) and dG = dY x^T (K = p) of head hl
         const uint32_t x0 = smem_u32(sXY + (2 * (hl & 1)) * PANEL), y0 = x0 + PANEL;
 #pragma unroll
@@ -135,13 +152,9 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         mma_commit(&bar_m1);
     };
 
-    float dSsum[64];
+    float2 dS2[32];  // sum over heads of dS for this thread's 64 columns, as fp32 pairs
 #pragma unroll
-    for (int q = 0; q < 64; ++q) dSsum[q] = 0.f;
-    auto pos_of = [&](int hl) { return ((size_t)bb * P.h + gg * hpg + hl) * P.T + (size_t)k * LT; };
-    float c_n = P.tcum[pos_of(0) + row], cend_n = P.tcum[pos_of(0) + (row | 31)];
-    float dt_n = P.dtT ? P.dtT[pos_of(0) + row] : 1.f;
-    float r0_n = P.rterm[pos_of(0) + row], r1_n = P.rterm[bhT + pos_of(0) + row];
+    for (int q = 0; q < 32; ++q) dS2[q] = make_float2(0.f, 0.f);
     mbar_wait(&bar_cb, 0, &failed);
     if (tid == CTL) {
         mbar_wait(&bar_xy[0], 0, &failed);
@@ -154,7 +167,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         const int hh = gg * hpg + hl, xb = hl & 1, buf = hl & 1;
         const uint32_t ph = hl & 1;
         const size_t tpos = pos_of(hl) + row;
-        const float c_i = c_n, cend = cend_n, dtv = dt_n, rt0 = r0_n, rt1 = r1_n;
+        const float c_i = c_n, dtv = dt_n, rt0 = r0_n, rt1 = r1_n, Dh = D_n;
         if (hl + 1 < hpg) {
             const size_t o = pos_of(hl + 1);
             c_n = P.tcum[o + row];
@@ -162,16 +175,9 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             dt_n = P.dtT ? P.dtT[o + row] : 1.f;
             r0_n = P.rterm[o + row];
             r1_n = P.rterm[bhT + o + row];
+            D_n = P.D ? P.D[hh + 1] : 0.f;
         }
-        if (hf == 0) {
-            scum2[buf * LT + row] = c_i;
-            sfL[buf * LT + row] = exp2f(cend - c_i);
-            sdt[buf * LT + row] = dtv;
-        }
-        if (tid == CTL) tma_store_wait_read();  // the previous head's dx store has read its staging (sG panel 0)
         mbar_wait(&bar_xy[xb], (hl >> 1) & 1, &failed);
-        tc_fence_before();
-        __syncthreads();  // (A) previous head fully retired by every thread
         uint8_t* sX = sXY + (2 * xb) * PANEL;
         uint8_t* sdY = sX + PANEL;
         const uint32_t x0 = smem_u32(sX), y0 = x0 + PANEL;  // phase 1 of this head was issued one step earlier
@@ -196,47 +202,74 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         const float dj = exp2f(Sk - c_i);
         mbar_wait(&bar_m1, ph, &failed);
         tc_fence_after();
-        float rowacc = 0.f;
-#pragma unroll
-        for (int sub = 0; sub < 4; ++sub) {  // 16 columns at a time keeps the register footprint small
-            const int c0 = hf * 64 + sub * 16, cb = c0 & ~31;
-            uint32_t gp[8];
-            if (cb > rowblk) {
-#pragma unroll
-                for (int q = 0; q < 8; ++q) gp[q] = 0u;
-            } else {
-                uint32_t rs[16], rg[16];
-                tmem_ld16(tS + lanes + c0, rs);
-                tmem_ld16(tdG + lanes + c0, rg);
-                const float rf = exp2f(c_i - scum2[buf * LT + cb + 31]);
-                const float4* fl4 = reinterpret_cast<const float4*>(sfL + buf * LT + c0);
-                const float4* dt4 = reinterpret_cast<const float4*>(sdt + buf * LT + c0);
-                tmem_ld_wait();
-                const bool diag = (cb == rowblk);
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const float4 fl = fl4[q4], d4 = dt4[q4];
-                    const float lf[4] = {rf * fl.x, rf * fl.y, rf * fl.z, rf * fl.w};
-                    const float dd[4] = {d4.x, d4.y, d4.z, d4.w};
-                    float gq[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int q = q4 * 4 + e;
-                        const bool ok = !diag || (c0 + q <= row);
-                        const float l = ok ? lf[e] : 0.f;
-                        const float dg = __uint_as_float(rg[q]) * dd[e];
-                        gq[e] = __uint_as_float(rs[q]) * l;
-                        dSsum[sub * 16 + q] += dg * l;
-                        // the bf16-rounded G that the dX product uses, so row and column sums of dG o G cancel
-                        rowacc += dg * __bfloat162float(__float2bfloat16_rn(gq[e]));
-                    }
-                    gp[q4 * 2] = pack_bf16(gq[0], gq[1]);
-                    gp[q4 * 2 + 1] = pack_bf16(gq[2], gq[3]);
-                }
+        float2 rowacc2 = make_float2(0.f, 0.f);
+        {
+            // 16 columns at a time; the TMEM loads of the next 16 are in flight while these are processed
+            uint32_t rs[2][16], rg[2][16];
+            auto active = [&](int sub) { return ((hf * 64 + sub * 16) & ~31) <= rowblk; };
+            if (active(0)) {
+                tmem_ld16(tS + lanes + hf * 64, rs[0]);
+                tmem_ld16(tdG + lanes + hf * 64, rg[0]);
             }
-            *reinterpret_cast<uint4*>(sG + hf * PANEL + sw128(row, sub * 2)) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
-            *reinterpret_cast<uint4*>(sG + hf * PANEL + sw128(row, sub * 2 + 1)) = make_uint4(gp[4], gp[5], gp[6], gp[7]);
+#pragma unroll
+            for (int sub = 0; sub < 4; ++sub) {
+                const int c0 = hf * 64 + sub * 16, cb = c0 & ~31;
+                uint32_t gp[8];
+                if (!active(sub)) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) gp[q] = 0u;
+                } else {
+                    const float rf = exp2f(c_i - scum2[buf * LT + cb + 31]);
+                    const float4* fl4 = reinterpret_cast<const float4*>(sfL + buf * LT + c0);
+                    const float4* dt4 = reinterpret_cast<const float4*>(sdt + buf * LT + c0);
+                    tmem_ld_wait();
+                    if (sub < 3 && active(sub + 1)) {
+                        tmem_ld16(tS + lanes + c0 + 16, rs[(sub + 1) & 1]);
+                        tmem_ld16(tdG + lanes + c0 + 16, rg[(sub + 1) & 1]);
+                    }
+                    // rowacc uses the bf16-rounded G that the dX product reads (unpacked from the packed pair),
+                    // so that the row and column sums of dG o G cancel exactly
+                    auto pair = [&](float s0, float s1, float g0, float g1, float l0, float l1, float t0, float t1, int q) {
+                        const float2 l = make_float2(l0, l1);
+                        const float2 dg = mul2(make_float2(g0, g1), make_float2(t0, t1));
+                        const float2 gl = mul2(make_float2(s0, s1), l);
+                        const uint32_t pk = pack_bf16(gl.x, gl.y);
+                        dS2[sub * 8 + q / 2] = fma2(dg, l, dS2[sub * 8 + q / 2]);
+                        rowacc2 = fma2(dg, make_float2(__uint_as_float(pk << 16), __uint_as_float(pk & 0xffff0000u)), rowacc2);
+                        return pk;
+                    };
+                    if (cb == rowblk) {  // diagonal block: columns beyond the row are masked
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const float4 fl = fl4[q4], d4 = dt4[q4];
+                            const int j = c0 + q4 * 4;
+                            const float l0 = (j + 0 <= row) ? rf * fl.x : 0.f, l1 = (j + 1 <= row) ? rf * fl.y : 0.f;
+                            const float l2 = (j + 2 <= row) ? rf * fl.z : 0.f, l3 = (j + 3 <= row) ? rf * fl.w : 0.f;
+                            const uint32_t* S4 = &rs[sub & 1][q4 * 4];
+                            const uint32_t* G4 = &rg[sub & 1][q4 * 4];
+                            gp[q4 * 2] = pair(__uint_as_float(S4[0]), __uint_as_float(S4[1]), __uint_as_float(G4[0]),
+                                              __uint_as_float(G4[1]), l0, l1, d4.x, d4.y, q4 * 4);
+                            gp[q4 * 2 + 1] = pair(__uint_as_float(S4[2]), __uint_as_float(S4[3]), __uint_as_float(G4[2]),
+                                                  __uint_as_float(G4[3]), l2, l3, d4.z, d4.w, q4 * 4 + 2);
+                        }
+                    } else {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const float4 fl = fl4[q4], d4 = dt4[q4];
+                            const uint32_t* S4 = &rs[sub & 1][q4 * 4];
+                            const uint32_t* G4 = &rg[sub & 1][q4 * 4];
+                            gp[q4 * 2] = pair(__uint_as_float(S4[0]), __uint_as_float(S4[1]), __uint_as_float(G4[0]),
+                                              __uint_as_float(G4[1]), rf * fl.x, rf * fl.y, d4.x, d4.y, q4 * 4);
+                            gp[q4 * 2 + 1] = pair(__uint_as_float(S4[2]), __uint_as_float(S4[3]), __uint_as_float(G4[2]),
+                                                  __uint_as_float(G4[3]), rf * fl.z, rf * fl.w, d4.z, d4.w, q4 * 4 + 2);
+                        }
+                    }
+                }
+                *reinterpret_cast<uint4*>(sG + hf * PANEL + sw128(row, sub * 2)) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
+                *reinterpret_cast<uint4*>(sG + hf * PANEL + sw128(row, sub * 2 + 1)) = make_uint4(gp[4], gp[5], gp[6], gp[7]);
+            }
         }
+        const float rowacc = rowacc2.x + rowacc2.y;
         {   // Xd = d dt x in place (A operand of dB += Xd Q); dYe = e dY as bf16 pairs in TMEM
             uint32_t a[16];
             const float wx = dj * dtv;
@@ -272,6 +305,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
                 qh += fh.x * fq.x + fh.y * fq.y;
             }
         }
+        if (tid == CTL) tma_store_wait_read();  // the previous head's dx store has read sdX
         tc_fence_before();
         fence_async_smem();
         __syncthreads();  // (B) G, Xd, dYe complete; H / Q read by everyone
@@ -285,6 +319,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
                 const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
                 mma_ss(tX2, smem_desc(b0a + off, 16, 1024), smem_desc(q0a + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
             }
+            mma_commit(&bar_m2);  // the row epilogue only needs dX1 and dX2
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // dC += dYe H : A in TMEM (K = p), B = H^T [n][p] K-major, N = 128
                 mma_ts(tdC, tdG + (kk >> 1) * 64 + (kk & 1) * 8, smem_desc(h0a + kk * 32, 16, 1024), kIdescKK128,
@@ -292,14 +327,12 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // dB += Xd Q : A = Xd K-major (in place of x), B = Q^T [n][p] K-major
                 mma_ss(tdB, smem_desc(x0 + kk * 32, 16, 1024), smem_desc(q0a + kk * 32, 16, 1024), kIdescKK128, hl > 0 || kk > 0);
-            mma_commit(&bar_m2);
+            mma_commit(&bar_m2b);  // releases H, Q, Xd and the dYe columns
         }
         mbar_wait(&bar_m2, ph, &failed);
         tc_fence_after();
-        if (tid == CTL && hl + 1 < hpg) load_hq(hl + 1);
         float ddt_acc = 0.f, st_acc = 0.f;
         {
-            const float Dh = P.D ? P.D[hh] : 0.f;
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t a[16], b2[16];
@@ -318,8 +351,8 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
                     st_acc += s0v * fx.x + s1v * fx.y;
                     dxp[q] = pack_bf16(e0 * dtv + Dh * fy.x, e1 * dtv + Dh * fy.y);
                 }
-                *reinterpret_cast<uint4*>(sG + sw128(row, hf * 4 + sub * 2)) = make_uint4(dxp[0], dxp[1], dxp[2], dxp[3]);
-                *reinterpret_cast<uint4*>(sG + sw128(row, hf * 4 + sub * 2 + 1)) = make_uint4(dxp[4], dxp[5], dxp[6], dxp[7]);
+                *reinterpret_cast<uint4*>(sdX + sw128(row, hf * 4 + sub * 2)) = make_uint4(dxp[0], dxp[1], dxp[2], dxp[3]);
+                *reinterpret_cast<uint4*>(sdX + sw128(row, hf * 4 + sub * 2 + 1)) = make_uint4(dxp[4], dxp[5], dxp[6], dxp[7]);
             }
         }
         {
@@ -335,13 +368,16 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             for (int of = 16; of > 0; of >>= 1) red += __shfl_xor_sync(0xffffffffu, red, of);
             if (lane == 0) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + warp] = red;
         }
+        if (hl + 1 < hpg) publish_columns((hl + 1) & 1);
         tc_fence_before();
         fence_async_smem();
-        __syncthreads();  // (C) dx staged, TMEM reads done
+        __syncthreads();  // (C) dx staged, TMEM reads done, next head's column arrays visible
         if (tid == CTL) {
-            tma_store_2d(&P.mdX, sG, hh * HP, row0);
+            tma_store_2d(&P.mdX, sdX, hh * HP, row0);
             tma_store_commit();
+            mbar_wait(&bar_m2b, ph, &failed);  // dC / dB products of this head done
             if (hl + 1 < hpg) {
+                load_hq(hl + 1);
                 // everyone has read dX1 / dX2, so S and dG of the next head may overwrite them now; its x / dy
                 // tiles were prefetched during this head, and this head's buffer is free for head hl + 2
                 mbar_wait(&bar_xy[xb ^ 1], ((hl + 1) >> 1) & 1, &failed);
@@ -352,13 +388,16 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         }
     }
     // ---- group terms: stage sum_h dS as bf16 [i][j] (panel = column half) for the two closing products
-    if (tid == CTL) tma_store_wait_read();  // last dx store has read sG panel 0
+    mbar_wait(&bar_m2b, (hpg - 1) & 1, &failed);  // the last head's products have read Xd / dY
     {
         float v[32];
 #pragma unroll
         for (int blk = 0; blk < 2; ++blk) {
 #pragma unroll
-            for (int q = 0; q < 32; ++q) v[q] = dSsum[blk * 32 + q];
+            for (int q = 0; q < 16; ++q) {
+                v[2 * q] = dS2[blk * 16 + q].x;
+                v[2 * q + 1] = dS2[blk * 16 + q].y;
+            }
             store_half_row(sXY + hf * PANEL, row, blk * 4, v);
         }
     }
