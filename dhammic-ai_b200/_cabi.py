@@ -12,6 +12,8 @@ F32, BF16 = 0, 1
 PASS_FWD, PASS_BWD = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA, EDEVICE = 0, -1, -2, -3, -4, -5
+FWD_STATES_ONLY = 1
+BWD_DINIT_ONLY = 1
 
 EXPORTS = (
     "ssd_b200_abi_version", "ssd_b200_last_error", "ssd_b200_workspace_bytes", "ssd_b200_states_bytes",
@@ -33,7 +35,7 @@ class FwdArgs(C.Structure):
     _fields_ = [("shape", Shape), ("x", C.c_void_p), ("a", C.c_void_p), ("dt", C.c_void_p), ("A_head", C.c_void_p),
                 ("D", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("init", C.c_void_p), ("y", C.c_void_p),
                 ("final_state", C.c_void_p), ("a_cumsum", C.c_void_p), ("cumsum_is_input", C.c_int32),
-                ("reserved", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+                ("flags", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
                 ("states", C.c_void_p)]
 
 
@@ -43,7 +45,7 @@ class BwdArgs(C.Structure):
                 ("a_cumsum", C.c_void_p), ("dy", C.c_void_p), ("dfinal", C.c_void_p), ("dx", C.c_void_p),
                 ("dB", C.c_void_p), ("dC", C.c_void_p), ("da", C.c_void_p), ("ddt", C.c_void_p),
                 ("dA_head", C.c_void_p), ("dD", C.c_void_p), ("dinit", C.c_void_p),
-                ("cumsum_is_input", C.c_int32), ("reserved", C.c_int32), ("workspace", C.c_void_p),
+                ("cumsum_is_input", C.c_int32), ("flags", C.c_int32), ("workspace", C.c_void_p),
                 ("workspace_bytes", C.c_size_t), ("states", C.c_void_p)]
 
 

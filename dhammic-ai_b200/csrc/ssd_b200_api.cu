@@ -213,6 +213,7 @@ int simt_fwd(const ssd_b200_fwd_args* a, cudaStream_t st) {
     if (!a->cumsum_is_input)
         if (int rc = launch_cumsum(P, st)) return rc;
     if (int rc = simt_forward_states<T>(P, st)) return rc;
+    if (a->flags & SSD_B200_FWD_STATES_ONLY) return 0;
     const int PT = (d.p + TS - 1) / TS;
     const int hrows = d.p > TS ? d.p : TS;
     size_t sm = ((size_t)TS * (d.n + 1) + (size_t)hrows * (d.n + 1) + (size_t)TS * (PT * TS + 1) + TS * (TS + 1) + 2 * TS) * 4;
@@ -272,8 +273,10 @@ int simt_bwd(const ssd_b200_bwd_args* a, cudaStream_t st) {
     P.da = a->cumsum_is_input ? nullptr : a->da;
     P.ddt = a->ddt; P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = (float*)(ws + w.dD_part);
     P.a_is_bf16 = a->shape.a_dtype == SSD_B200_BF16;
+    const bool dinit_only = (a->flags & SSD_B200_BWD_DINIT_ONLY) != 0;
     // states entering each chunk (recomputed) and the final state
-    if (int rc = simt_forward_states<T>(P, st)) return rc;
+    if (!dinit_only)
+        if (int rc = simt_forward_states<T>(P, st)) return rc;
     // local state gradients and the reverse recurrence
     dim3 gs((d.n + TS - 1) / TS, (d.p + TS - 1) / TS, d.b * d.c * d.h);
     SSD_LAUNCH(ssd::prof::K_CHUNK_DSTATE, st, chunk_state_kernel<T><<<gs, NTHR, 0, st>>>(P, 1));
@@ -281,6 +284,7 @@ int simt_bwd(const ssd_b200_bwd_args* a, cudaStream_t st) {
     const size_t pn = (size_t)d.p * d.n;
     SSD_LAUNCH(ssd::prof::K_STATE_PASS_REV, st, state_passing_kernel<<<dim3((unsigned)((pn + NTHR - 1) / NTHR), d.h, d.b), NTHR, 0, st>>>(P, 1));
     CUDA_LAUNCH_CHECK("state_passing_rev");
+    if (dinit_only) return 0;
     const int NTN = (d.n + TS - 1) / TS, PT = (d.p + TS - 1) / TS;
     int rc = 0;
     if (NTN <= 1) rc = launch_bwd_row<T, 1>(P, st);
@@ -379,7 +383,9 @@ int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
     if (!a) return fail(SSD_B200_EINVAL, "args is null");
     if (int rc = check_shape(&a->shape)) return rc;
     if (int rc = check_forms(a->a, a->dt, a->A_head, a->D)) return rc;
-    if (!a->x || !a->B || !a->C || !a->y || !a->a_cumsum) return fail(SSD_B200_EINVAL, "null tensor pointer");
+    const bool states_only = (a->flags & SSD_B200_FWD_STATES_ONLY) != 0;
+    if (!a->x || !a->B || !a->C || !a->a_cumsum || (!a->y && !states_only)) return fail(SSD_B200_EINVAL, "null tensor pointer");
+    if (states_only && !a->final_state) return fail(SSD_B200_EINVAL, "STATES_ONLY needs final_state");
     int path = resolve_path(a->shape);
     if (path < 0) return path;
     if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(SSD_B200_EWORKSPACE, "workspace null or not 256-byte aligned");
@@ -392,11 +398,17 @@ int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
 int ssd_b200_bwd(const ssd_b200_bwd_args* a, void* stream) {
     if (!a) return fail(SSD_B200_EINVAL, "args is null");
     if (int rc = check_shape(&a->shape)) return rc;
-    if (int rc = check_forms(a->a, a->dt, a->A_head, a->D)) return rc;
-    if (!a->x || !a->B || !a->C || !a->dy || !a->a_cumsum || !a->dx || !a->dB || !a->dC)
-        return fail(SSD_B200_EINVAL, "null tensor pointer");
-    if (a->dt && (!a->ddt || !a->dA_head || (a->D && !a->dD))) return fail(SSD_B200_EINVAL, "Mamba-2 form needs ddt, dA_head (and dD)");
-    if (a->a && !a->cumsum_is_input && !a->da) return fail(SSD_B200_EINVAL, "operator form needs da");
+    if (!(a->flags & SSD_B200_BWD_DINIT_ONLY))
+        if (int rc = check_forms(a->a, a->dt, a->A_head, a->D)) return rc;
+    const bool dinit_only = (a->flags & SSD_B200_BWD_DINIT_ONLY) != 0;
+    if (dinit_only) {
+        if (!a->C || !a->dy || !a->a_cumsum || !a->dinit) return fail(SSD_B200_EINVAL, "DINIT_ONLY needs C, dy, a_cumsum and dinit");
+    } else {
+        if (!a->x || !a->B || !a->C || !a->dy || !a->a_cumsum || !a->dx || !a->dB || !a->dC)
+            return fail(SSD_B200_EINVAL, "null tensor pointer");
+        if (a->dt && (!a->ddt || !a->dA_head || (a->D && !a->dD))) return fail(SSD_B200_EINVAL, "Mamba-2 form needs ddt, dA_head (and dD)");
+        if (a->a && !a->cumsum_is_input && !a->da) return fail(SSD_B200_EINVAL, "operator form needs da");
+    }
     int path = resolve_path(a->shape);
     if (path < 0) return path;
     if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(SSD_B200_EWORKSPACE, "workspace null or not 256-byte aligned");

@@ -91,6 +91,7 @@ inline int set_walk_attrs(char* err, size_t errn) {
     cudaError_t e = cudaFuncSetAttribute(walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<0>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<1>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<2>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<3>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem);
     if (e != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "set shared memory size: %s", cudaGetErrorString(e));
     return 0;
@@ -108,6 +109,7 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     Ws w = ws_layout(d, SSD_B200_PASS_FWD);
     if (a->workspace_bytes < w.total) SSD_TC_FAIL(SSD_B200_EWORKSPACE, "workspace %zu < %zu", a->workspace_bytes, w.total);
     if (!encode_fn()) SSD_TC_FAIL(SSD_B200_ECUDA, "cuTensorMapEncodeTiled is not available");
+    const bool states_only = (a->flags & SSD_B200_FWD_STATES_ONLY) != 0;
     for (const void* p : {a->x, a->B, a->C, (const void*)a->y})
         if ((uintptr_t)p & 15) SSD_TC_FAIL(SSD_B200_EINVAL, "tensor-core path needs 16-byte aligned tensors");
     char* ws = (char*)a->workspace;
@@ -131,7 +133,8 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     WalkParams P{};
     const uint64_t rows = (uint64_t)d.b * d.T;
     bool ok = make_map(&P.mU, a->x, rows, (uint64_t)d.h * HP) && make_map(&P.mV, a->B, rows, (uint64_t)d.g * DN) &&
-              make_map(&P.mC, a->C, rows, (uint64_t)d.g * DN) && make_map(&P.mY, a->y, rows, (uint64_t)d.h * HP);
+              make_map(&P.mC, a->C, rows, (uint64_t)d.g * DN) &&
+              make_map(&P.mY, states_only ? a->x : (const void*)a->y, rows, (uint64_t)d.h * HP);
     if (a->states && ((uintptr_t)a->states & 15)) SSD_TC_FAIL(SSD_B200_EINVAL, "`states` must be 16-byte aligned");
     if (ok && a->states) {
         ok = make_map(&P.mS, a->states, (uint64_t)d.b * (d.T / LT) * d.h * DN, HP);
@@ -142,6 +145,13 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     if (!ok) SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
     P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.seed = a->init; P.out_state = a->final_state; P.status = status;
     P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = d.T / LT;
+    if (states_only) {  // the recurrence alone: final state of this slice of the sequence
+        P.save_states = 0;
+        P.D = nullptr;
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<1><<<dim3(d.h, d.b), 288, WalkCfg<1>::SMEM, st>>>(P));
+        SSD_TC_CHECK("tc_states_walk");
+        return 0;
+    }
     SSD_LAUNCH(prof::K_TC_FWD, st, walk_kernel<0><<<dim3(d.h, d.b), 288, WalkCfg<0>::SMEM, st>>>(P));
     SSD_TC_CHECK("tc_fwd_walk");
     return 0;
@@ -167,6 +177,17 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     if (int rc = set_walk_attrs(err, errn)) return rc;
     const int nt = d.T / LT;
     const uint64_t rows = (uint64_t)d.b * d.T, srows = (uint64_t)d.b * nt * d.h * DN;
+    if (a->flags & SSD_B200_BWD_DINIT_ONLY) {  // reverse recurrence alone: d(initial state) of this slice
+        WalkParams P{};
+        if (!(make_map(&P.mU, a->dy, rows, (uint64_t)d.h * HP) && make_map(&P.mV, a->C, rows, (uint64_t)d.g * DN)))
+            SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
+        P.mC = P.mV; P.mY = P.mU; P.mS = P.mU;
+        P.tcum = tcum; P.seed = a->dfinal; P.out_state = a->dinit; P.status = status;
+        P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<3><<<dim3(d.h, d.b), 288, WalkCfg<3>::SMEM, st>>>(P));
+        SSD_TC_CHECK("tc_dinit_walk");
+        return 0;
+    }
     CUtensorMap mX, mdY, mB, mC, mH, mQ, mdX, mdB, mdC;
     bool ok = make_map(&mX, a->x, rows, (uint64_t)d.h * HP) && make_map(&mdY, a->dy, rows, (uint64_t)d.h * HP) &&
               make_map(&mB, a->B, rows, (uint64_t)d.g * DN) && make_map(&mC, a->C, rows, (uint64_t)d.g * DN) &&

@@ -18,7 +18,8 @@
 //   bar_h      accumulators read, new state written, 256 arrive   (row warps -> control)
 //
 // MODE 0 forward (writes y), MODE 1 states only (stores the state entering every tile, bf16),
-// MODE 2 reverse walk over dy and C (stores the state gradient leaving every tile).
+// MODE 2 reverse walk over dy and C (stores the state gradient leaving every tile, and the state part of
+// the decay gradient of every row), MODE 3 the same reverse recurrence alone (for d initial-state only).
 #pragma once
 
 namespace ssd {
@@ -67,7 +68,7 @@ __device__ __forceinline__ void store_state_slot(__nv_bfloat16* slot, int row, i
 
 template <int MODE>
 struct WalkCfg {
-    static constexpr int NST = (MODE == 1) ? 3 : 2;                           // load stages
+    static constexpr int NST = (MODE == 1 || MODE == 3) ? 3 : 2;              // load stages
     static constexpr int STAGE_PANELS = (MODE == 0) ? 5 : (MODE == 2 ? 4 : 3);  // V(2) U(1) [C(2) | H_k(1)]
     static constexpr uint32_t STAGE_BYTES = STAGE_PANELS * PANEL;
     // stages | sUd | sH | sY (mode 0) | scum2[2][128] sf[2][128] | alignment slack
@@ -78,7 +79,7 @@ template <int MODE>
 __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ WalkParams P) {
     using Cfg = WalkCfg<MODE>;
     constexpr int NST = Cfg::NST;
-    constexpr bool REV = (MODE == 2);
+    constexpr bool REV = (MODE == 2 || MODE == 3);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sStage = sm;                                  // per stage: V panels 0,1 | U | C panels 0,1
@@ -234,7 +235,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
     } else {
         // ------------------------------------------------------------------ row warps
         const float* tcum = P.tcum + bh * P.T;
-        const float* dtT = (MODE != 2 && P.dtT) ? P.dtT + bh * P.T : nullptr;
+        const float* dtT = (!REV && P.dtT) ? P.dtT + bh * P.T : nullptr;
         const uint32_t lanes = lane_base(warp);
         const float Dh = (MODE == 0 && P.D) ? P.D[hh] : 0.f;
         // per-tile scalars are fetched one tile ahead

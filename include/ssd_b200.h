@@ -56,6 +56,14 @@ enum { SSD_B200_PASS_FWD = 0, SSD_B200_PASS_BWD = 1 };
  * fp32 SIMT path otherwise; the other two force a path (for tests). */
 enum { SSD_B200_PATH_AUTO = 0, SSD_B200_PATH_SIMT = 1, SSD_B200_PATH_TC = 2 };
 
+/* Partial passes used by the sequence-parallel schedule (each rank holds a contiguous slice of the
+ * sequence and only per-rank states cross NVLink):
+ *   SSD_B200_FWD_STATES_ONLY  forward: write final_state (and a_cumsum) only; y may be NULL.
+ *   SSD_B200_BWD_DINIT_ONLY   backward: from dy, C and a_cumsum alone write dinit, the gradient of the
+ *                             initial state for a zero dfinal; every other output may be NULL. */
+enum { SSD_B200_FWD_STATES_ONLY = 1 };
+enum { SSD_B200_BWD_DINIT_ONLY = 1 };
+
 typedef struct ssd_b200_shape {
     int32_t abi_version; /* SSD_B200_ABI_VERSION                                      */
     int32_t dtype;       /* storage of x, B, C, y, dy, dx, dB, dC                      */
@@ -93,7 +101,7 @@ typedef struct ssd_b200_fwd_args {
     float *final_state;
     float *a_cumsum;
     int32_t cumsum_is_input;
-    int32_t reserved;
+    int32_t flags;       /* SSD_B200_FWD_* */
     void *workspace;
     size_t workspace_bytes;
     void *states; /* optional output, ssd_b200_states_bytes() bytes: the recurrent state entering every
@@ -133,7 +141,7 @@ typedef struct ssd_b200_bwd_args {
     float *dD;
     float *dinit;
     int32_t cumsum_is_input;
-    int32_t reserved;
+    int32_t flags;       /* SSD_B200_BWD_* */
     void *workspace;
     size_t workspace_bytes;
     const void *states; /* optional: what the forward wrote into its `states`; NULL = recompute */

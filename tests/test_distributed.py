@@ -1,0 +1,217 @@
+"""Sequence-parallel schedule of the scan: the communication/prefix logic with two gloo processes on the
+CPU (a CPU backend built on the oracle stands in for the CUDA passes), and the CUDA passes themselves on one
+GPU with the ranks emulated by threads.  Both compare against the scan of the whole sequence."""
+import importlib
+import os
+import socket
+import sys
+from dataclasses import replace
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from conftest import TOL_BF16, TOL_FP32, rel_err  # noqa: E402
+
+
+class OracleBackend:
+    """The per-rank passes on the CPU, from the oracle (test infrastructure)."""
+
+    def __init__(self):
+        from oracle import ssd_oracle
+        self.O = ssd_oracle
+
+    def _run(self, s, init):
+        return self.O.mamba2_operator(s.x, s.dt, s.A_head, s.B, s.C, s.D, s.chunk,
+                                      None if init is None else init.unsqueeze(1))
+
+    def states_only(self, s):
+        with torch.no_grad():
+            _, final = self._run(s, None)
+        return final, (s.dt * s.A_head).sum(1), None
+
+    def forward(self, s, init, cum):
+        with torch.no_grad():
+            y, final = self._run(s, init)
+        return y, final, {}
+
+    def dinit_only(self, s, saved, dy):
+        init0 = torch.zeros(s.x.shape[0], s.x.shape[2], s.x.shape[3], s.B.shape[3], dtype=s.x.dtype, requires_grad=True)
+        with torch.enable_grad():
+            y, _ = self._run(s, init0)
+        return torch.autograd.grad([y], [init0], [dy])[0]
+
+    def backward(self, s, saved, init, dy, dfinal):
+        lv = {k: getattr(s, k).detach().clone().requires_grad_(True) for k in ("x", "dt", "A_head", "B", "C", "D")}
+        il = init.detach().clone().requires_grad_(True)
+        s2 = replace(s, **lv)
+        with torch.enable_grad():
+            y, final = self._run(s2, il)
+        g = torch.autograd.grad([y, final], list(lv.values()) + [il], [dy, dfinal])
+        out = {"d" + k: v for k, v in zip(lv, g[:-1])}
+        out["dinit"] = g[-1]
+        return out
+
+    def prefix(self, states, logp, index, reverse):
+        acc = torch.zeros_like(states[0])
+        rng = range(states.shape[0] - 1, index, -1) if reverse else range(index)
+        for q in rng:
+            acc = torch.exp(logp[q])[..., None, None] * acc + states[q]
+        return acc
+
+
+def _small_cfg(pkg):
+    return replace(pkg.CONFIGS[0], batch=2, seqlen=256, nheads=4, headdim=8, d_state=16, ngroups=2, chunk=32)
+
+
+def _free_port():
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
+def _gloo_worker(rank, world, port, result_file):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        pkg = importlib.import_module("dhammic-ai_b200")
+        D = importlib.import_module("dhammic-ai_b200.distributed")
+        from oracle import ssd_oracle as O
+        torch.set_num_threads(2)
+        cfg = _small_cfg(pkg)
+        inp = pkg.make_inputs(cfg)  # same seed on every rank: the full sequence
+        g = torch.Generator().manual_seed(5)
+        init = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g) * 0.3
+        dfin = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g)
+        Tl = cfg.seqlen // world
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        lv = {"x": inp["x"][:, sl], "dt": inp["dt"][:, sl], "A_head": inp["A_head"], "B": inp["B"][:, sl],
+              "C": inp["C"][:, sl], "D": inp["D"]}
+        lv = {k: v.clone().requires_grad_(True) for k, v in lv.items()}
+        il = init.clone().requires_grad_(True)
+        y, final = D.ssd_mamba2_sequence_parallel(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk,
+                                                  il, backend=OracleBackend())
+        # the caller's d final_state acts on the last rank's final state only
+        outs, gouts = [y], [inp["dy"][:, sl]]
+        if rank == world - 1:
+            outs.append(final)
+            gouts.append(dfin)
+        grads = torch.autograd.grad(outs, list(lv.values()) + [il], gouts)
+        got = {"y": y.detach(), "final": final.detach()}
+        got.update({"d" + k: v for k, v in zip(list(lv) + ["init"], grads)})
+        want = O.mamba2_fwd_bwd(inp, cfg.chunk, torch.float32, init.unsqueeze(1), dfin)
+        errs = {}
+        for k in ("y", "dx", "ddt", "dB", "dC"):
+            errs[k] = rel_err(got[k], want[k][:, sl])
+        for k in ("dA_head", "dD"):
+            errs[k] = rel_err(got[k], want[k])       # summed over the group by the operator
+        errs["dinit"] = rel_err(got["dinit"], want["dinit"].reshape(got["dinit"].shape))
+        if rank == world - 1:
+            errs["final"] = rel_err(got["final"], want["final_state"])
+        bad = {k: v for k, v in errs.items() if not v < TOL_FP32}
+        with open(f"{result_file}.{rank}", "w") as f:
+            f.write("ok" if not bad else f"bad {errs}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sequence_parallel_schedule_gloo(tmp_path, world):
+    port = _free_port()
+    res = str(tmp_path / "res")
+    mp.spawn(_gloo_worker, args=(world, port, res), nprocs=world, join=True)
+    for r in range(world):
+        assert Path(f"{res}.{r}").read_text() == "ok", Path(f"{res}.{r}").read_text()
+
+
+def test_head_grad_allreduce_gloo(tmp_path):
+    port = _free_port()
+    res = str(tmp_path / "res")
+    mp.spawn(_allreduce_worker, args=(2, port, res), nprocs=2, join=True)
+    for r in range(2):
+        assert Path(f"{res}.{r}").read_text() == "ok"
+
+
+def _allreduce_worker(rank, world, port, result_file):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        D = importlib.import_module("dhammic-ai_b200.distributed")
+        a = torch.full((4,), float(rank + 1))
+        d = torch.full((4,), 10.0 * (rank + 1))
+        D.allreduce_head_grads(a, d)
+        ok = torch.equal(a, torch.full((4,), 3.0)) and torch.equal(d, torch.full((4,), 30.0))
+        with open(f"{result_file}.{rank}", "w") as f:
+            f.write("ok" if ok else "bad")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("idx,world,seqlen,tol", [(0, 2, 512, TOL_FP32), (2, 2, 512, TOL_BF16), (2, 4, 1024, TOL_BF16)])
+def test_sequence_parallel_cuda_passes(pkg, cabi, idx, world, seqlen, tol):
+    """States-only / dinit-only passes, the prefix kernel and the chained full passes on the GPU (the ranks
+    emulated phase by phase in this process), against one call over the whole sequence."""
+    D = importlib.import_module("dhammic-ai_b200.distributed")
+    cfg = pkg.shrink(pkg.CONFIGS[idx], 1, seqlen)
+    inp = {k: v.cuda() for k, v in pkg.make_inputs(cfg).items()}
+    g = torch.Generator().manual_seed(5)
+    init = (torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g) * 0.3).cuda()
+    dfin = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g).cuda()
+    names = ("x", "dt", "A_head", "B", "C", "D")
+    full = {k: inp[k].clone().requires_grad_(True) for k in names}
+    il = init.clone().requires_grad_(True)
+    y, fs = pkg.ssd_mamba2(full["x"], full["dt"], full["A_head"], full["B"], full["C"], full["D"], cfg.chunk, il)
+    gw = torch.autograd.grad([y, fs], list(full.values()) + [il], [inp["dy"], dfin])
+    want = {"y": y.detach(), "final": fs.detach()}
+    want.update({"d" + k: v for k, v in zip(list(names) + ["init"], gw)})
+
+    Tl = seqlen // world
+    slices, dys = [], []
+    for r in range(world):
+        sl = slice(r * Tl, (r + 1) * Tl)
+        slices.append(D.Slice(inp["x"][:, sl].contiguous(), inp["dt"][:, sl].contiguous(), inp["A_head"],
+                              inp["B"][:, sl].contiguous(), inp["C"][:, sl].contiguous(), inp["D"], cfg.chunk))
+        dys.append(inp["dy"][:, sl].contiguous())
+    res = D.emulate_sequence_parallel(slices, dys, init, dfin)
+    torch.cuda.synchronize()
+    errs = {}
+    for k in ("y", "dx", "ddt", "dB", "dC"):
+        errs[k] = rel_err(torch.cat([res[r][k] for r in range(world)], 1), want[k])
+    for k in ("dA_head", "dD", "dinit"):
+        errs[k] = rel_err(res[0][k], want[k])
+    errs["final"] = rel_err(res[world - 1]["final"], want["final"])
+    bad = {k: v for k, v in errs.items() if not v < tol}
+    assert not bad, errs
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_emulated_schedule_cpu(pkg, oracle, world):
+    """The single-process emulation of the schedule (same phases, same prefix arithmetic) on the CPU backend."""
+    D = importlib.import_module("dhammic-ai_b200.distributed")
+    cfg = _small_cfg(pkg)
+    inp = pkg.make_inputs(cfg)
+    g = torch.Generator().manual_seed(5)
+    init = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g) * 0.3
+    dfin = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g)
+    Tl = cfg.seqlen // world
+    slices = [D.Slice(inp["x"][:, r * Tl:(r + 1) * Tl], inp["dt"][:, r * Tl:(r + 1) * Tl], inp["A_head"],
+                      inp["B"][:, r * Tl:(r + 1) * Tl], inp["C"][:, r * Tl:(r + 1) * Tl], inp["D"], cfg.chunk)
+              for r in range(world)]
+    dys = [inp["dy"][:, r * Tl:(r + 1) * Tl] for r in range(world)]
+    res = D.emulate_sequence_parallel(slices, dys, init, dfin, backend=OracleBackend())
+    want = oracle.mamba2_fwd_bwd(inp, cfg.chunk, torch.float32, init.unsqueeze(1), dfin)
+    for k in ("y", "dx", "ddt", "dB", "dC"):
+        assert rel_err(torch.cat([res[r][k] for r in range(world)], 1), want[k]) < TOL_FP32, k
+    assert rel_err(res[0]["dA_head"], want["dA_head"]) < TOL_FP32
+    assert rel_err(res[0]["dD"], want["dD"]) < TOL_FP32
+    assert rel_err(res[0]["dinit"], want["dinit"].reshape(res[0]["dinit"].shape)) < TOL_FP32
+    assert rel_err(res[world - 1]["final"], want["final_state"]) < TOL_FP32
