@@ -171,15 +171,25 @@ def main():
             dist.barrier(device_ids=[local_rank])
         torch.cuda.synchronize(dev)
 
+    seq_par = cfg.seq_parallel and world > 1
+    if cfg.seq_parallel:
+        if cfg.seqlen % (world * 128) != 0:
+            raise SystemExit("sequence length must split into multiples of 128 per rank")
+        cfg = pkg.shrink(cfg, cfg.batch, cfg.seqlen // world)  # this rank's contiguous slice
+    dmod = importlib.import_module("dhammic-ai_b200.distributed")
     host = pkg.make_inputs(cfg, rank=rank)
     names = ("x", "dt", "A_head", "B", "C", "D", "dy")
     pinned = {k: host[k].pin_memory() for k in names}
     devin = {k: pinned[k].to(dev, non_blocking=True) for k in names}
     leaves = {k: devin[k].detach().requires_grad_(True) for k in names if k != "dy"}
 
+    def scan(lv):
+        if seq_par:  # contiguous sequence split: per-rank states cross NVLink through NCCL
+            return dmod.ssd_mamba2_sequence_parallel(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
+        return pkg.ssd_mamba2(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
+
     def step_device():
-        y, _ = pkg.ssd_mamba2(leaves["x"], leaves["dt"], leaves["A_head"], leaves["B"], leaves["C"], leaves["D"],
-                              cfg.chunk)
+        y, _ = scan(leaves)
         return y, torch.autograd.grad([y], list(leaves.values()), [devin["dy"]])
 
     for _ in range(args.warmup):
@@ -244,7 +254,7 @@ def main():
             nonlocal out_host
             d = {k: pinned[k].to(dev, non_blocking=True) for k in names}
             lv = {k: d[k].requires_grad_(True) for k in names if k != "dy"}
-            y, _ = pkg.ssd_mamba2(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
+            y, _ = scan(lv)
             grads = torch.autograd.grad([y], list(lv.values()), [d["dy"]])
             outs = [y.detach(), *grads]
             if out_host is None:
@@ -278,11 +288,13 @@ def main():
         line = {
             "metric": "ssd_scan_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cfg.dtype == "bf16" else "f32",
+            "scaling": "strong" if cfg.seq_parallel else "weak", "vs_baseline": None,
+            "dtype": "bf16" if cfg.dtype == "bf16" else "f32",
             "data": "synthetic",
             "config": {"workload": cfg.name, "batch_per_gpu": cfg.batch, "seqlen": cfg.seqlen, "nheads": cfg.nheads,
                        "headdim": cfg.headdim, "d_state": cfg.d_state, "ngroups": cfg.ngroups, "chunk": cfg.chunk,
-                       "parallelism": f"batch-sharded x{world}, no data-path collective",
+                       "parallelism": (f"sequence split x{world}, all_gather of per-rank states (NCCL)" if cfg.seq_parallel
+                                       else f"batch-sharded x{world}, no data-path collective"),
                        "kernel_path": pkg.resolved_path_name(cfg), "accumulate": "fp32",
                        "l2": "inputs larger than L2 (x alone %.0f MB per GPU)" % (cfg.tokens * cfg.nheads * cfg.headdim * 2 / 1e6)},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_base,
