@@ -185,7 +185,10 @@ def main():
 
     def scan(lv):
         if seq_par:  # contiguous sequence split: per-rank states cross NVLink through NCCL
-            return dmod.ssd_mamba2_sequence_parallel(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
+            return dmod.ssd_mamba2_sequence_parallel(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk,
+                                                     segments=0)
+        if cfg.seq_parallel:  # one GPU: the same schedule with the segments as extra batch entries
+            return dmod.ssd_mamba2_segmented(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
         return pkg.ssd_mamba2(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
 
     def step_device():

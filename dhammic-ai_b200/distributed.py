@@ -167,59 +167,86 @@ class CudaBackend:
 _DEFAULT_BACKEND = CudaBackend()
 
 
-def _gather_with_virtual(comm, local_state: Tensor, logp: Tensor, extra: Tensor | None, extra_first: bool):
-    """all_gather (state, logp) over the ranks and add one virtual rank carrying `extra` (the caller's
-    initial state in front, or the caller's d final at the back) with log-decay 0."""
-    states = comm.all_gather(local_state)
-    lps = comm.all_gather(logp)
-    if extra is None:
-        extra = torch.zeros_like(local_state)
-    z = torch.zeros_like(logp)
-    if extra_first:
-        return torch.cat([extra.unsqueeze(0), states]), torch.cat([z.unsqueeze(0), lps])
-    return torch.cat([states, extra.unsqueeze(0)]), torch.cat([lps, z.unsqueeze(0)])
+class LoopbackComm:
+    """A group of one: used when the sequence is only cut into segments inside a single GPU."""
+    rank, world = 0, 1
+
+    def all_gather(self, t: Tensor) -> Tensor:
+        return t.unsqueeze(0)
+
+    def all_reduce_sum(self, t: Tensor) -> Tensor:
+        return t
 
 
-class _SeqParallelSSD(torch.autograd.Function):
+class _SeqSplitSSD(torch.autograd.Function):
+    """The scan over a sequence cut into world * S contiguous pieces: `world` ranks (one per GPU, each holding
+    a contiguous slice) times S segments per rank.  The S segments of a rank run as extra batch entries of one
+    launch, (b, T_rank) viewed as (b*S, T_rank/S), so that the per-(batch, head) walk kernels have enough
+    blocks when b*h is small; all pieces are linked by the state prefix.  S = 1 is the plain multi-GPU
+    schedule, world = 1 the split inside one GPU."""
+
     @staticmethod
-    def forward(ctx, x, dt, A_head, B, C_, D, chunk, initial_state, comm, backend):
-        s = Slice(x.contiguous(), dt.float().contiguous(), A_head.float().contiguous(), B.contiguous(), C_.contiguous(),
-                  None if D is None else D.float().contiguous(), int(chunk))
-        F_loc, logp, cum = backend.states_only(s)
-        init_g = None if initial_state is None else initial_state.reshape(F_loc.shape).float()
-        states, lps = _gather_with_virtual(comm, F_loc, logp, init_g, extra_first=True)
-        # virtual rank 0 holds the caller's initial state, so this rank sits at index rank + 1
-        init = backend.prefix(states, lps, comm.rank + 1, reverse=False)
-        y, final, saved = backend.forward(s, init, cum)
-        ctx.s, ctx.saved, ctx.init, ctx.logp = s, saved, init, logp
-        ctx.comm, ctx.backend = comm, backend
+    def forward(ctx, x, dt, A_head, B, C_, D, chunk, initial_state, S, comm, backend):
+        b, T, h, p = x.shape
+        n, g = B.shape[3], B.shape[2]
+        Ts = T // S
+        seg = Slice(x.contiguous().view(b * S, Ts, h, p), dt.float().contiguous().view(b * S, Ts, h),
+                    A_head.float().contiguous(), B.contiguous().view(b * S, Ts, g, n),
+                    C_.contiguous().view(b * S, Ts, g, n), None if D is None else D.float().contiguous(), int(chunk))
+        F_loc, logp, cum = backend.states_only(seg)                              # (b*S,h,p,n), (b*S,h)
+        Fs = F_loc.view(b, S, h, p, n).transpose(0, 1).contiguous()              # (S,b,h,p,n)
+        lps = logp.view(b, S, h).transpose(0, 1).contiguous()                    # (S,b,h)
+        allF = comm.all_gather(Fs).reshape(comm.world * S, b, h, p, n)           # piece index = rank*S + segment
+        allP = comm.all_gather(lps).reshape(comm.world * S, b, h)
+        init_g = torch.zeros_like(Fs[0]) if initial_state is None else initial_state.reshape(b, h, p, n).float()
+        # a virtual piece in front carries the caller's initial state, so piece q sits at index q + 1
+        states = torch.cat([init_g.unsqueeze(0), allF])
+        lpv = torch.cat([torch.zeros_like(allP[:1]), allP])
+        base = comm.rank * S
+        inits = torch.stack([backend.prefix(states, lpv, base + s + 1, reverse=False) for s in range(S)], dim=1)
+        inits = inits.reshape(b * S, h, p, n).contiguous()
+        y, final, saved = backend.forward(seg, inits, cum)
+        ctx.seg, ctx.saved, ctx.inits, ctx.allP = seg, saved, inits, allP
+        ctx.comm, ctx.backend, ctx.S, ctx.dims = comm, backend, S, (b, T, h, p, n, g)
         ctx.has_init = initial_state is not None
         ctx.init_shape = None if initial_state is None else tuple(initial_state.shape)
-        return y, final
+        return y.view(b, T, h, p), final.view(b, S, h, p, n)[:, -1].contiguous()
 
     @staticmethod
     def backward(ctx, dy, dfinal_global):
-        s, comm, backend = ctx.s, ctx.comm, ctx.backend
-        dy = dy.contiguous().to(s.x.dtype)
-        D_loc = backend.dinit_only(s, ctx.saved, dy)
-        # the caller's d final_state belongs to the last rank's final state: a virtual rank behind the last
-        extra = None
+        seg, comm, backend, S = ctx.seg, ctx.comm, ctx.backend, ctx.S
+        b, T, h, p, n, g = ctx.dims
+        dys = dy.contiguous().to(seg.x.dtype).view(b * S, T // S, h, p)
+        Dl = backend.dinit_only(seg, ctx.saved, dys).view(b, S, h, p, n).transpose(0, 1).contiguous()
+        allD = comm.all_gather(Dl).reshape(comm.world * S, b, h, p, n)
+        # the caller's d final_state belongs to the last piece of the last rank: a virtual piece behind it
+        extra = torch.zeros_like(Dl[0])
         if dfinal_global is not None and comm.rank == comm.world - 1:
             extra = dfinal_global.float().contiguous()
-        if extra is None:
-            extra = torch.zeros_like(D_loc)
-        extra = comm.all_reduce_sum(extra.clone())  # every rank needs it for its suffix combination
-        states, lps = _gather_with_virtual(comm, D_loc, ctx.logp, extra, extra_first=False)
-        dfinal = backend.prefix(states, lps, comm.rank, reverse=True)
-        g = backend.backward(s, ctx.saved, ctx.init, dy, dfinal)
-        dAh = comm.all_reduce_sum(g["dA_head"])
-        dD = None if g["dD"] is None else comm.all_reduce_sum(g["dD"])
+        extra = comm.all_reduce_sum(extra.clone())
+        dstates = torch.cat([allD, extra.unsqueeze(0)])
+        dlp = torch.cat([ctx.allP, torch.zeros_like(ctx.allP[:1])])
+        base = comm.rank * S
+        dfin = torch.stack([backend.prefix(dstates, dlp, base + s, reverse=True) for s in range(S)], dim=1)
+        gr = backend.backward(seg, ctx.saved, ctx.inits, dys, dfin.reshape(b * S, h, p, n).contiguous())
+        dAh = comm.all_reduce_sum(gr["dA_head"])
+        dD = None if gr["dD"] is None else comm.all_reduce_sum(gr["dD"])
         dinit = None
         if ctx.has_init:
-            # d(initial state of the whole sequence) = d init of rank 0; hand it to every rank
-            d0 = g["dinit"] if comm.rank == 0 else torch.zeros_like(g["dinit"])
+            d0 = gr["dinit"].view(b, S, h, p, n)[:, 0].contiguous()
+            if comm.rank != 0:
+                d0 = torch.zeros_like(d0)
             dinit = comm.all_reduce_sum(d0).reshape(ctx.init_shape)
-        return g["dx"], g["ddt"], dAh, g["dB"], g["dC"], dD, None, dinit, None, None
+        return (gr["dx"].view(b, T, h, p), gr["ddt"].view(b, T, h), dAh, gr["dB"].view(b, T, g, n),
+                gr["dC"].view(b, T, g, n), dD, None, dinit, None, None, None)
+
+
+def pick_segments(batch: int, nheads: int, seqlen: int, n_sm: int = 148) -> int:
+    """Segments per rank so that batch*heads*segments covers the SMs about twice; 1 = no split."""
+    S = 1
+    while batch * nheads * S < 2 * n_sm and seqlen % (2 * S * 1024) == 0 and S < 16:
+        S *= 2
+    return S
 
 
 def emulate_sequence_parallel(slices: list[Slice], dys: list[Tensor], initial_state: Tensor | None = None,
@@ -257,14 +284,25 @@ def emulate_sequence_parallel(slices: list[Slice], dys: list[Tensor], initial_st
 
 def ssd_mamba2_sequence_parallel(x: Tensor, dt: Tensor, A_head: Tensor, B: Tensor, C: Tensor, D: Tensor | None,
                                  chunk_size: int, initial_state: Tensor | None = None, group=None, comm=None,
-                                 backend=None):
+                                 backend=None, segments: int = 1):
     """Y = SSD(x*dt, dt*A_head, B, C) + D*x for a sequence split contiguously over the ranks of `group`.
 
     Every rank passes its own slice (b, T/R, ...) and the replicated per-head parameters; it gets its slice
     of Y and the final state of its slice (the last rank's is the final state of the whole sequence).
     ``initial_state`` (b,h,p,n), if given, is the state before position 0 (same tensor on every rank).
-    ``dA_head`` and ``dD`` come back summed over the group.
+    ``dA_head`` and ``dD`` come back summed over the group.  ``segments`` > 1 additionally cuts the rank's
+    slice into that many pieces run as extra batch entries (0 = choose from the shape).
     """
     comm = comm if comm is not None else TorchDistComm(group)
     backend = backend if backend is not None else _DEFAULT_BACKEND
-    return _SeqParallelSSD.apply(x, dt, A_head, B, C, D, int(chunk_size), initial_state, comm, backend)
+    b, T, h, _ = x.shape
+    S = segments if segments > 0 else pick_segments(b, h, T)
+    if T % (S * int(chunk_size)) != 0:
+        raise ValueError(f"a slice of {T} positions does not split into {S} segments of whole chunks")
+    return _SeqSplitSSD.apply(x, dt, A_head, B, C, D, int(chunk_size), initial_state, S, comm, backend)
+
+
+def ssd_mamba2_segmented(x, dt, A_head, B, C, D, chunk_size, initial_state=None, segments: int = 0, backend=None):
+    """ssd_mamba2 with the sequence cut into `segments` pieces inside this GPU (0 = choose from the shape)."""
+    return ssd_mamba2_sequence_parallel(x, dt, A_head, B, C, D, chunk_size, initial_state, comm=LoopbackComm(),
+                                        backend=backend, segments=segments)

@@ -215,3 +215,33 @@ def test_emulated_schedule_cpu(pkg, oracle, world):
     assert rel_err(res[0]["dD"], want["dD"]) < TOL_FP32
     assert rel_err(res[0]["dinit"], want["dinit"].reshape(res[0]["dinit"].shape)) < TOL_FP32
     assert rel_err(res[world - 1]["final"], want["final_state"]) < TOL_FP32
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("idx,segments,tol", [(0, 2, TOL_FP32), (2, 4, TOL_BF16)])
+def test_segmented_scan_inside_one_gpu(pkg, cabi, idx, segments, tol):
+    """Cutting the sequence into segments that run as extra batch entries gives the result of the plain call."""
+    D = importlib.import_module("dhammic-ai_b200.distributed")
+    cfg = pkg.shrink(pkg.CONFIGS[idx], 2, 1024)
+    inp = {k: v.cuda() for k, v in pkg.make_inputs(cfg).items()}
+    g = torch.Generator().manual_seed(6)
+    init = (torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g) * 0.3).cuda()
+    dfin = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g).cuda()
+    names = ("x", "dt", "A_head", "B", "C", "D")
+
+    def run(fn, **kw):
+        lv = {k: inp[k].clone().requires_grad_(True) for k in names}
+        il = init.clone().requires_grad_(True)
+        y, fs = fn(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk, il, **kw)
+        gr = torch.autograd.grad([y, fs], list(lv.values()) + [il], [inp["dy"], dfin])
+        out = {"y": y.detach(), "final": fs.detach()}
+        out.update({"d" + k: v for k, v in zip(list(names) + ["init"], gr)})
+        return out
+
+    want = run(pkg.ssd_mamba2)
+    got = run(D.ssd_mamba2_segmented, segments=segments)
+    torch.cuda.synchronize()
+    errs = {k: rel_err(got[k], want[k]) for k in want}
+    bad = {k: v for k, v in errs.items() if not v < tol}
+    assert not bad, errs
+    assert D.pick_segments(1, 64, 131072) == 8 and D.pick_segments(16, 64, 4096) == 1

@@ -261,3 +261,24 @@ def test_saved_states_equal_recomputed_states(pkg, cabi):
         pkg.set_save_states(True)
     for k in kept:
         assert torch.equal(kept[k], redone[k]), k
+
+
+@pytest.mark.parametrize("dtype,tol", [("fp32", TOL_FP32), ("bf16", TOL_BF16)])
+def test_mamba3_variant(pkg, cabi, oracle, dtype, tol):
+    """Rotary state angles + trapezoidal two-term form (config 3 per-token shape, reduced batch / sequence)
+    against the oracle's two-call composition under plain autograd, all gradients including d raw_angles, d lam."""
+    cfg = replace(pkg.shrink(pkg.CONFIGS[3], 1, 256), dtype=dtype)
+    inp = pkg.make_inputs(cfg)
+    names = ("x", "dt", "A_head", "B", "C", "D", "raw_angles", "lam")
+    lv = {k: inp[k].to(DEV).requires_grad_(True) for k in names}
+    y = pkg.ssd_mamba3(*[lv[k] for k in names], cfg.chunk)
+    grads = torch.autograd.grad([y], list(lv.values()), [inp["dy"].to(DEV)])
+    torch.cuda.synchronize()
+    ol = {k: inp[k].float().requires_grad_(True) for k in names}
+    yo = oracle.mamba3_operator(*[ol[k] for k in names], cfg.chunk)
+    go = torch.autograd.grad([yo], list(ol.values()), [inp["dy"].float()])
+    errs = {"y": rel_err(y, yo)}
+    for k, a, b in zip(names, grads, go):
+        errs["d" + k] = rel_err(a, b)
+    bad = {k: v for k, v in errs.items() if not v < tol}
+    assert not bad, errs
