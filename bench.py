@@ -178,12 +178,15 @@ def main():
         cfg = pkg.shrink(cfg, cfg.batch, cfg.seqlen // world)  # this rank's contiguous slice
     dmod = importlib.import_module("dhammic-ai_b200.distributed")
     host = pkg.make_inputs(cfg, rank=rank)
-    names = ("x", "dt", "A_head", "B", "C", "D", "dy")
+    names = ("x", "dt", "A_head", "B", "C", "D", "dy") + (("raw_angles", "lam") if cfg.mamba3 else ())
     pinned = {k: host[k].pin_memory() for k in names}
     devin = {k: pinned[k].to(dev, non_blocking=True) for k in names}
     leaves = {k: devin[k].detach().requires_grad_(True) for k in names if k != "dy"}
 
     def scan(lv):
+        if cfg.mamba3:  # rotary state angles + trapezoidal two-term form: two scans behind an element-wise prologue
+            return pkg.ssd_mamba3(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], lv["raw_angles"], lv["lam"],
+                                  cfg.chunk), None
         if seq_par:  # contiguous sequence split: per-rank states cross NVLink through NCCL
             return dmod.ssd_mamba2_sequence_parallel(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk,
                                                      segments=0)
