@@ -74,6 +74,7 @@ struct WalkParams {
     CUtensorMap mY;   // y store (mode 0)
     CUtensorMap mS;   // state store: 2D [b*nt*h*128][64]
     int save_states;  // store the state entering every tile of the walk through mS
+    float* gS;           // mode 2: (b,h,nt,8) per warp exp(S_k) <Q_k, H_k>
     float* rterm;        // mode 2: (2,b,h,T) halves of e_i * sum_p dY[i,p] (C_i . H_k[p,:])
     int* status;
     int T, h, hpg, nt;

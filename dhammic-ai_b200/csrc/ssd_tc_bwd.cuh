@@ -41,7 +41,8 @@ struct BwdParams {
     float* g;                      // (2,b,h,T) per column half: gradient w.r.t. the tile-cumulative log-decay
     float* ddtx;                   // (2,b,h,T) per column half: sum_p dX * x
     float* dyx;                    // (2,b,h,T) per column half: sum_p dy * x
-    float* gS;                     // (b,h,nt,8) per warp: terms that act through S = cum[127] of the tile
+    float* gS;                     // (b,h,nt,8) per warp: terms that act through S = cum[127] of the tile; the
+                                   // reverse walk initialises it, this kernel adds to it
     int* status;
     int T, h, hpg, nt, b;
 };
@@ -51,7 +52,9 @@ constexpr size_t kBwdSmem = 13 * PANEL + 6 * LT * 4 + 1024;
 
 __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant__ BwdParams P) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // 1024-byte alignment by an offset on the __shared__ array itself, so that every access below stays a
+    // shared-memory instruction (a pointer rebuilt from an integer would be a generic-address access)
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sC = sm;                  // 2 panels [pos][n]
     uint8_t* sB = sC + 2 * PANEL;      // 2 panels [pos][n]
     uint8_t* sG = sB + 2 * PANEL;      // 2 panels [i][j]; at the end dC staging
@@ -184,7 +187,6 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         const float Sk = scum2[buf * LT + LT - 1];
         // this thread's half rows of x and dy (raw)
         uint32_t xr[16], yr[16];
-        float dyx = 0.f;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
             uint4 v = *reinterpret_cast<const uint4*>(sX + sw128(row, hf * 4 + ch));
@@ -192,12 +194,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             xr[ch * 4 + 0] = v.x; xr[ch * 4 + 1] = v.y; xr[ch * 4 + 2] = v.z; xr[ch * 4 + 3] = v.w;
             yr[ch * 4 + 0] = u.x; yr[ch * 4 + 1] = u.y; yr[ch * 4 + 2] = u.z; yr[ch * 4 + 3] = u.w;
         }
-#pragma unroll
-        for (int q = 0; q < 16; ++q) {
-            float2 fx = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xr[q]));
-            float2 fy = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&yr[q]));
-            dyx += fx.x * fy.x + fx.y * fy.y;
-        }
+        float dyx = 0.f;  // sum_p dy[i,p] x[i,p] is the diagonal entry of dG = dY x^T: picked up in the mask loop
         const float ei = exp2f(c_i);
         const float dj = exp2f(Sk - c_i);
         mbar_wait(&bar_m1, ph, &failed);
@@ -239,6 +236,9 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
                         return pk;
                     };
                     if (cb == rowblk) {  // diagonal block: columns beyond the row are masked
+#pragma unroll
+                        for (int q = 0; q < 16; ++q)
+                            if (c0 + q == row) dyx = __uint_as_float(rg[sub & 1][q]);
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {
                             const float4 fl = fl4[q4], d4 = dt4[q4];
@@ -289,27 +289,12 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             tmem_st16(tdG + lanes + hf * 64, a);
             tmem_st_wait();
         }
-        // <Q, H> over this thread's half of state row n = row: gradient of the inter-tile decay exp(S)
-        float qh = 0.f;
-        mbar_wait(&bar_hq, ph, &failed);
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-            uint4 hv = *reinterpret_cast<const uint4*>(sH + sw128(row, hf * 4 + ch));
-            uint4 qv = *reinterpret_cast<const uint4*>(sQ + sw128(row, hf * 4 + ch));
-            const uint32_t* hu = reinterpret_cast<const uint32_t*>(&hv);
-            const uint32_t* qu = reinterpret_cast<const uint32_t*>(&qv);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float2 fh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hu[q]));
-                float2 fq = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu[q]));
-                qh += fh.x * fq.x + fh.y * fq.y;
-            }
-        }
         if (tid == CTL) tma_store_wait_read();  // the previous head's dx store has read sdX
         tc_fence_before();
         fence_async_smem();
         __syncthreads();  // (B) G, Xd, dYe complete; H / Q read by everyone
         if (tid == CTL) {
+            mbar_wait(&bar_hq, ph, &failed);  // H and Q of this head have landed
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk)  // dX1 = G^T dY : A = G MN-major (M = j, K = i), B = dY MN-major
@@ -363,10 +348,11 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             P.g[o] = rowacc - dtv * ddt_acc + (hf == 0 ? rt0 + rt1 : 0.f);
             P.ddtx[o] = ddt_acc;
             P.dyx[o] = dyx;
-            float red = dj * dtv * st_acc + exp2f(Sk) * qh;
+            float red = dj * dtv * st_acc;
 #pragma unroll
             for (int of = 16; of > 0; of >>= 1) red += __shfl_xor_sync(0xffffffffu, red, of);
-            if (lane == 0) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + warp] = red;
+            // the reverse walk already left exp(S) <Q_k, H_k> (the inter-tile decay term) in this slot
+            if (lane == 0) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + warp] += red;
         }
         if (hl + 1 < hpg) publish_columns((hl + 1) & 1);
         tc_fence_before();

@@ -206,7 +206,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     {   // reverse walk: gradient of the state leaving every tile, and d(initial state)
         WalkParams P{};
         P.mU = mdY; P.mV = mC; P.mC = mH; P.mY = mdX; P.mS = mQ; P.save_states = 1;
-        P.rterm = (float*)(ws + w.rterm);
+        P.rterm = (float*)(ws + w.rterm); P.gS = (float*)(ws + w.gS);
         P.tcum = tcum; P.dtT = nullptr; P.D = nullptr; P.seed = a->dfinal; P.out_state = dinit; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
         SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<2><<<dim3(d.h, d.b), 288, WalkCfg<2>::SMEM, st>>>(P));

@@ -81,7 +81,9 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
     constexpr int NST = Cfg::NST;
     constexpr bool REV = (MODE == 2 || MODE == 3);
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // 1024-byte alignment by an offset on the __shared__ array itself, so that every access below stays a
+    // shared-memory instruction (a pointer rebuilt from an integer would be a generic-address access)
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sStage = sm;                                  // per stage: V panels 0,1 | U | C panels 0,1
     uint8_t* sUd = sStage + (size_t)NST * Cfg::STAGE_BYTES;  // weighted copy of U
     uint8_t* sH = sUd + PANEL;                             // state, bf16, [n][p]
@@ -281,6 +283,26 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     }
                     *reinterpret_cast<uint4*>(sUd + sw128(row, hf * 4 + ch)) = v;
                 }
+            }
+            if (MODE == 2) {
+                // exp(S_k) <Q_k, H_k>: gradient of the inter-tile decay; Q_k is this thread's state row (fp32, not yet
+                // updated), H_k the stored forward state of the tile (rows n of the loaded panel)
+                const uint8_t* sHk = st + 3 * PANEL;
+                float qh = 0.f;
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint4 hv = *reinterpret_cast<const uint4*>(sHk + sw128(row, hf * 4 + ch));
+                    const uint32_t* hu = reinterpret_cast<const uint32_t*>(&hv);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float2 fh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hu[q]));
+                        qh += fh.x * H[ch * 8 + 2 * q] + fh.y * H[ch * 8 + 2 * q + 1];
+                    }
+                }
+                qh *= exp2f(Sk);
+#pragma unroll
+                for (int of = 16; of > 0; of >>= 1) qh += __shfl_xor_sync(0xffffffffu, qh, of);
+                if (lane == 0) P.gS[((bh * (size_t)nt) + k) * 8 + warp] = qh;
             }
             fence_async_smem();
             mbar_arrive(&bar_u);
