@@ -241,9 +241,15 @@ def main():
     step_bytes = cfg.bytes_per_token() * cfg.tokens
     step_flops = cfg.flops_per_token() * cfg.tokens
     ms_step = ms_max / args.steps
+    # dram read + write of one launch, from the committed ncu capture of the same per-token shape at batch 4
+    # (profiles/), scaled by tokens; None for kernels / shapes without a capture
+    ncu_bytes_per_token = {"tc_bwd_walk": 823.7e6 / 16384, "tc_fwd_walk": 443.5e6 / 16384, "tc_bwd_state": 438.2e6 / 16384}
+    traffic = None
+    if cfg.index == 2 and top in ncu_bytes_per_token:
+        traffic = ncu_bytes_per_token[top] * cfg.tokens
     roofline = {
         "bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-        "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+        "frac": achieved / hbm_peak, "traffic": traffic, "peak_kind": peak_kind,
         "whole_step": {"algorithmic_GB": step_bytes / 1e9, "algorithmic_TFLOP": step_flops / 1e12,
                        "hbm_frac": step_bytes / (ms_step * 1e-3) / 1e9 / hbm_peak,
                        "tensor_frac": step_flops / (ms_step * 1e-3) / 1e12 / tc_peak if tc_peak else None},
@@ -253,23 +259,31 @@ def main():
     # end to end: host buffers in, host buffers out, through the public operator
     e2e = None
     if not args.no_e2e:
-        out_host = None
         h2d = sum(pinned[k].numel() * pinned[k].element_size() for k in names)
-
-        def step_e2e():
-            nonlocal out_host
-            d = {k: pinned[k].to(dev, non_blocking=True) for k in names}
-            lv = {k: d[k].requires_grad_(True) for k in names if k != "dy"}
-            y, _ = scan(lv)
-            grads = torch.autograd.grad([y], list(lv.values()), [d["dy"]])
-            outs = [y.detach(), *grads]
-            if out_host is None:
-                out_host = [torch.empty(o.shape, dtype=o.dtype, pin_memory=True) for o in outs]
-            for o, hbuf in zip(outs, out_host):
-                hbuf.copy_(o, non_blocking=True)
-            return outs
-
         e2e_steps = max(2, min(args.steps, 5))
+        plain = cfg.mamba3 or cfg.seq_parallel
+        if not plain:
+            # the package's host-buffer entry: micro-batches, copies overlapped with the kernels on three streams
+            pipe = pkg.HostPipeline(dev, micro_batches=4)
+            out_host = pkg.HostPipeline.alloc_outputs(pinned)
+
+            def step_e2e():
+                pipe.run(pinned, out_host, cfg.chunk)
+        else:
+            out_host = None
+
+            def step_e2e():
+                nonlocal out_host
+                d = {k: pinned[k].to(dev, non_blocking=True) for k in names}
+                lv = {k: d[k].requires_grad_(True) for k in names if k != "dy"}
+                y, _ = scan(lv)
+                grads = torch.autograd.grad([y], list(lv.values()), [d["dy"]])
+                outs = [y.detach(), *grads]
+                if out_host is None:
+                    out_host = [torch.empty(o.shape, dtype=o.dtype, pin_memory=True) for o in outs]
+                for o, hbuf in zip(outs, out_host):
+                    hbuf.copy_(o, non_blocking=True)
+
         step_e2e()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -281,9 +295,11 @@ def main():
         t2 = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-        d2h = sum(o.numel() * o.element_size() for o in out_host)
+        outs_iter = out_host.values() if isinstance(out_host, dict) else out_host
+        d2h = sum(o.numel() * o.element_size() for o in outs_iter)
         e2e = {"value": tokens_all * e2e_steps / (float(t2.item()) * 1e-3), "unit": "tokens/s",
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "api": "HostPipeline.run (4 micro-batches, 3 streams)" if not plain else "operator call on pinned buffers"}
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
