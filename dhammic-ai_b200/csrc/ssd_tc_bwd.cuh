@@ -271,18 +271,19 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         }
         const float rowacc = rowacc2.x + rowacc2.y;
         {   // Xd = d dt x in place (A operand of dB += Xd Q); dYe = e dY as bf16 pairs in TMEM
+            // row weights as bf16 pairs: one packed multiply per two elements
             uint32_t a[16];
-            const float wx = dj * dtv;
+            const __nv_bfloat162 wx2 = __float2bfloat162_rn(dj * dtv), we2 = __float2bfloat162_rn(ei);
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
                 uint4 v;
                 uint32_t* u = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    float2 fx = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xr[ch * 4 + q]));
-                    float2 fy = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&yr[ch * 4 + q]));
-                    u[q] = pack_bf16(fx.x * wx, fx.y * wx);
-                    a[ch * 4 + q] = pack_bf16(fy.x * ei, fy.y * ei);
+                    __nv_bfloat162 rx = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&xr[ch * 4 + q]), wx2);
+                    __nv_bfloat162 ry = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&yr[ch * 4 + q]), we2);
+                    u[q] = *reinterpret_cast<uint32_t*>(&rx);
+                    a[ch * 4 + q] = *reinterpret_cast<uint32_t*>(&ry);
                 }
                 *reinterpret_cast<uint4*>(sX + sw128(row, hf * 4 + ch)) = v;
             }

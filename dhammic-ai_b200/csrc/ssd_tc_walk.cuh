@@ -270,7 +270,10 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
             // this thread's half row of U: keep x for the D skip, write the weighted copy
             uint32_t xrow[16];
             {
+                // the row weight as a bf16 pair: one packed multiply per two elements (the product is rounded to
+                // bf16 for the MMA anyway; rounding the weight first costs at most one more ulp of bf16)
                 const float w = REV ? exp2f(c_i) : exp2f(Sk - c_i) * dtv;
+                const __nv_bfloat162 w2 = __float2bfloat162_rn(w);
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     uint4 v = *reinterpret_cast<const uint4*>(sU + sw128(row, hf * 4 + ch));
@@ -278,8 +281,8 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         xrow[ch * 4 + q] = u[q];
-                        float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u[q]));
-                        u[q] = pack_bf16(f.x * w, f.y * w);
+                        __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&u[q]), w2);
+                        u[q] = *reinterpret_cast<uint32_t*>(&r);
                     }
                     *reinterpret_cast<uint4*>(sUd + sw128(row, hf * 4 + ch)) = v;
                 }
