@@ -224,45 +224,33 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
                         tmem_ld16(tS + lanes + c0 + 16, rs[(sub + 1) & 1]);
                         tmem_ld16(tdG + lanes + c0 + 16, rg[(sub + 1) & 1]);
                     }
-                    // rowacc uses the bf16-rounded G that the dX product reads (unpacked from the packed pair),
-                    // so that the row and column sums of dG o G cancel exactly
-                    auto pair = [&](float s0, float s1, float g0, float g1, float l0, float l1, float t0, float t1, int q) {
-                        const float2 l = make_float2(l0, l1);
-                        const float2 dg = mul2(make_float2(g0, g1), make_float2(t0, t1));
-                        const float2 gl = mul2(make_float2(s0, s1), l);
+                    // Everything in fp32 pairs (one instruction, two columns).  rowacc uses the bf16-rounded G that
+                    // the dX product reads (unpacked from the packed pair), so that the row and column sums of
+                    // dG o G cancel exactly.
+                    const float2* S2 = reinterpret_cast<const float2*>(rs[sub & 1]);
+                    const float2* G2 = reinterpret_cast<const float2*>(rg[sub & 1]);
+                    const float2* F2 = reinterpret_cast<const float2*>(fl4);
+                    const float2* T2 = reinterpret_cast<const float2*>(dt4);
+                    const float2 rf2 = make_float2(rf, rf);
+                    const bool diag = (cb == rowblk);
+#pragma unroll
+                    for (int q2 = 0; q2 < 8; ++q2) {
+                        float2 l = mul2(rf2, F2[q2]);
+                        if (diag) {  // columns beyond the row are masked
+                            if (c0 + 2 * q2 > row) l.x = 0.f;
+                            if (c0 + 2 * q2 + 1 > row) l.y = 0.f;
+                        }
+                        const float2 dg = mul2(G2[q2], T2[q2]);
+                        const float2 gl = mul2(S2[q2], l);
                         const uint32_t pk = pack_bf16(gl.x, gl.y);
-                        dS2[sub * 8 + q / 2] = fma2(dg, l, dS2[sub * 8 + q / 2]);
+                        dS2[sub * 8 + q2] = fma2(dg, l, dS2[sub * 8 + q2]);
                         rowacc2 = fma2(dg, make_float2(__uint_as_float(pk << 16), __uint_as_float(pk & 0xffff0000u)), rowacc2);
-                        return pk;
-                    };
-                    if (cb == rowblk) {  // diagonal block: columns beyond the row are masked
+                        gp[q2] = pk;
+                    }
+                    if (diag) {
 #pragma unroll
                         for (int q = 0; q < 16; ++q)
                             if (c0 + q == row) dyx = __uint_as_float(rg[sub & 1][q]);
-#pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            const float4 fl = fl4[q4], d4 = dt4[q4];
-                            const int j = c0 + q4 * 4;
-                            const float l0 = (j + 0 <= row) ? rf * fl.x : 0.f, l1 = (j + 1 <= row) ? rf * fl.y : 0.f;
-                            const float l2 = (j + 2 <= row) ? rf * fl.z : 0.f, l3 = (j + 3 <= row) ? rf * fl.w : 0.f;
-                            const uint32_t* S4 = &rs[sub & 1][q4 * 4];
-                            const uint32_t* G4 = &rg[sub & 1][q4 * 4];
-                            gp[q4 * 2] = pair(__uint_as_float(S4[0]), __uint_as_float(S4[1]), __uint_as_float(G4[0]),
-                                              __uint_as_float(G4[1]), l0, l1, d4.x, d4.y, q4 * 4);
-                            gp[q4 * 2 + 1] = pair(__uint_as_float(S4[2]), __uint_as_float(S4[3]), __uint_as_float(G4[2]),
-                                                  __uint_as_float(G4[3]), l2, l3, d4.z, d4.w, q4 * 4 + 2);
-                        }
-                    } else {
-#pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            const float4 fl = fl4[q4], d4 = dt4[q4];
-                            const uint32_t* S4 = &rs[sub & 1][q4 * 4];
-                            const uint32_t* G4 = &rg[sub & 1][q4 * 4];
-                            gp[q4 * 2] = pair(__uint_as_float(S4[0]), __uint_as_float(S4[1]), __uint_as_float(G4[0]),
-                                              __uint_as_float(G4[1]), rf * fl.x, rf * fl.y, d4.x, d4.y, q4 * 4);
-                            gp[q4 * 2 + 1] = pair(__uint_as_float(S4[2]), __uint_as_float(S4[3]), __uint_as_float(G4[2]),
-                                                  __uint_as_float(G4[3]), rf * fl.z, rf * fl.w, d4.z, d4.w, q4 * 4 + 2);
-                        }
                     }
                 }
                 *reinterpret_cast<uint4*>(sG + hf * PANEL + sw128(row, sub * 2)) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
