@@ -329,22 +329,18 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                         const float4* f4 = reinterpret_cast<const float4*>(sf + buf * LT + c0);
                         tmem_ld_wait();
                         const bool diag = (c0 == rowblk);
+                        const float2* S2 = reinterpret_cast<const float2*>(r);
+                        const float2* F2 = reinterpret_cast<const float2*>(f4);
+                        const float2 rf2 = make_float2(rf, rf);
 #pragma unroll
-                        for (int q4 = 0; q4 < 8; ++q4) {
-                            const float4 f = f4[q4];
-                            float v0 = __uint_as_float(r[q4 * 4 + 0]) * (rf * f.x);
-                            float v1 = __uint_as_float(r[q4 * 4 + 1]) * (rf * f.y);
-                            float v2 = __uint_as_float(r[q4 * 4 + 2]) * (rf * f.z);
-                            float v3 = __uint_as_float(r[q4 * 4 + 3]) * (rf * f.w);
+                        for (int q2 = 0; q2 < 16; ++q2) {  // fp32 pairs: one instruction, two columns
+                            float2 l = mul2(rf2, F2[q2]);
                             if (diag) {
-                                const int j = c0 + q4 * 4;
-                                if (j + 0 > row) v0 = 0.f;
-                                if (j + 1 > row) v1 = 0.f;
-                                if (j + 2 > row) v2 = 0.f;
-                                if (j + 3 > row) v3 = 0.f;
+                                if (c0 + 2 * q2 > row) l.x = 0.f;
+                                if (c0 + 2 * q2 + 1 > row) l.y = 0.f;
                             }
-                            packed[blk * 16 + q4 * 2] = pack_bf16(v0, v1);
-                            packed[blk * 16 + q4 * 2 + 1] = pack_bf16(v2, v3);
+                            const float2 v = mul2(S2[q2], l);
+                            packed[blk * 16 + q2] = pack_bf16(v.x, v.y);
                         }
                     }
                 }
@@ -366,14 +362,16 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 const float e = exp2f(c_i);
                 tmem_ld_wait();
                 float y[32];
-#pragma unroll
-                for (int q = 0; q < 32; ++q) y[q] = __uint_as_float(a[q]) + e * __uint_as_float(o[q]);
-                if (P.D) {
+                {
+                    const float2* A2 = reinterpret_cast<const float2*>(a);
+                    const float2* O2 = reinterpret_cast<const float2*>(o);
+                    float2* Y2 = reinterpret_cast<float2*>(y);
+                    const float2 e2 = make_float2(e, e), D2 = make_float2(Dh, Dh);
 #pragma unroll
                     for (int q = 0; q < 16; ++q) {
-                        float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xrow[q]));
-                        y[2 * q] += Dh * f.x;
-                        y[2 * q + 1] += Dh * f.y;
+                        float2 v = fma2(e2, O2[q], A2[q]);
+                        if (P.D) v = fma2(D2, __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xrow[q])), v);
+                        Y2[q] = v;
                     }
                 }
                 store_half_row(sY, row, hf * 4, y);
@@ -399,7 +397,10 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 const float dec = exp2f(Sk);
                 tmem_ld_wait();
 #pragma unroll
-                for (int q = 0; q < 32; ++q) H[q] = dec * H[q] + __uint_as_float(r[q]);
+                for (int q = 0; q < 16; ++q) {
+                    float2* H2 = reinterpret_cast<float2*>(H);
+                    H2[q] = fma2(make_float2(dec, dec), H2[q], reinterpret_cast<const float2*>(r)[q]);
+                }
                 store_half_row(sH, row, hf * 4, H);
             }
             tc_fence_before();
