@@ -264,7 +264,7 @@ def main():
         plain = cfg.mamba3 or cfg.seq_parallel
         if not plain:
             # the package's host-buffer entry: micro-batches, copies overlapped with the kernels on three streams
-            pipe = pkg.HostPipeline(dev, micro_batches=4)
+            pipe = pkg.HostPipeline(dev, micro_batches=8)
             out_host = pkg.HostPipeline.alloc_outputs(pinned)
 
             def step_e2e():
@@ -299,7 +299,7 @@ def main():
         d2h = sum(o.numel() * o.element_size() for o in outs_iter)
         e2e = {"value": tokens_all * e2e_steps / (float(t2.item()) * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-               "api": "HostPipeline.run (4 micro-batches, 3 streams)" if not plain else "operator call on pinned buffers"}
+               "api": "HostPipeline.run (8 micro-batches, 3 streams)" if not plain else "operator call on pinned buffers"}
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -62,6 +62,117 @@ __global__ void tile_cumsum_kernel(const float* __restrict__ cum, const float* _
 }
 
 // ------------------------------------------------------------------------------------------
+// Decay gradient of the tensor-core backward, one block per (128-tile, 32 heads, batch).
+// Inputs in (b,h,T) layout (coalesced along t): the per-row gradients g w.r.t. the tile-cumulative
+// log-decay (two column-half partials), ddtx = sum_p dX x (two partials), dyx = sum_p dy x (two
+// partials), and gS, the terms that act through the tile's last row.  Within a tile
+//   dA[t] = sum_{t' >= t} g[t']      (a suffix sum, four 32-lane segments per warp and head)
+// and  ddt = ddtx + dA A_head,  dA_head += dA dt,  dD += dyx.  dt is read and ddt / da written in the
+// caller's (b,T,h) layout through a shared-memory transpose, so both sides are 128-byte rows.
+struct DecayTileParams {
+    const float* g;      // (2,b,h,T)
+    const float* ddtx;   // (2,b,h,T)
+    const float* dyx;    // (2,b,h,T) or null
+    const float* gS;     // (b,h,nt,8)
+    const float* dt;     // (b,T,h) or null (operator form)
+    const float* A_head; // (h) or null
+    float* ddt;          // (b,T,h) or null
+    float* da;           // (b,T,h) or null
+    float* dAh_part;     // (b*nt, h)
+    float* dD_part;      // (b*nt, h) or null
+    int b, T, h, nt;
+};
+
+__global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
+    __shared__ float sdt[LT][33];
+    __shared__ float sout[LT][33];
+    const int k = blockIdx.x, hg = blockIdx.y, bb = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h0 = hg * 32;
+    const size_t half = (size_t)P.b * P.h * P.T;
+    const bool head_ok = h0 + lane < P.h;
+    if (P.dt) {
+        for (int t = warp; t < LT; t += 8)
+            sdt[t][lane] = head_ok ? P.dt[((size_t)bb * P.T + (size_t)k * LT + t) * P.h + h0 + lane] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int i = 0; i < 4; ++i) {
+        const int hl = warp * 4 + i, hh = h0 + hl;
+        if (hh >= P.h) break;  // warp-uniform
+        const size_t base = ((size_t)bb * P.h + hh) * P.T + (size_t)k * LT;
+        float v[4], dx[4], yx = 0.f;
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+            const int t = s4 * 32 + lane;
+            v[s4] = P.g[base + t] + P.g[half + base + t];
+            dx[s4] = P.ddtx[base + t] + P.ddtx[half + base + t];
+            if (P.dyx) yx += P.dyx[base + t] + P.dyx[half + base + t];
+        }
+        if (lane == 31) {
+            const float* q = P.gS + ((((size_t)bb * P.h + hh) * P.nt) + k) * 8;
+            v[3] += ((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]));
+        }
+        // suffix sums: inside each 32-lane segment by shuffles, then the totals of the later segments
+        float tot[4];
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+            float incl = v[s4];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float u = __shfl_down_sync(0xffffffffu, incl, o);
+                if (lane + o < 32) incl += u;
+            }
+            v[s4] = incl;
+            tot[s4] = __shfl_sync(0xffffffffu, incl, 0);
+        }
+        v[2] += tot[3];
+        v[1] += tot[3] + tot[2];
+        v[0] += (tot[3] + tot[2]) + tot[1];
+        float dAh = 0.f;
+        const float Ah = P.A_head ? P.A_head[hh] : 0.f;
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+            const int t = s4 * 32 + lane;
+            if (P.dt) {
+                sout[t][hl] = dx[s4] + v[s4] * Ah;
+                dAh += v[s4] * sdt[t][hl];
+            } else {
+                sout[t][hl] = v[s4];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            dAh += __shfl_xor_sync(0xffffffffu, dAh, o);
+            yx += __shfl_xor_sync(0xffffffffu, yx, o);
+        }
+        if (lane == 0) {
+            const size_t po = ((size_t)bb * P.nt + k) * P.h + hh;
+            if (P.dt) P.dAh_part[po] = dAh;
+            if (P.dD_part) P.dD_part[po] = yx;
+        }
+    }
+    __syncthreads();
+    float* out = P.dt ? P.ddt : P.da;
+    if (out && head_ok) {
+        for (int t = warp; t < LT; t += 8) out[((size_t)bb * P.T + (size_t)k * LT + t) * P.h + h0 + lane] = sout[t][lane];
+    }
+}
+
+// out[hh] = sum_r part[r, hh] over `rows` rows, one block per head, fixed summation tree (deterministic).
+__global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restrict__ part, float* __restrict__ out, int rows, int h) {
+    __shared__ float red[8];
+    const int hh = blockIdx.x;
+    float s = 0.f;
+    for (int r = threadIdx.x; r < rows; r += 256) s += part[(size_t)r * h + hh];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) out[hh] = ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+}
+
+// ------------------------------------------------------------------------------------------
 struct WalkParams {
     CUtensorMap mU;   // x (modes 0,1) or dy (mode 2): 2D [b*T][h*64]
     CUtensorMap mV;   // B (modes 0,1) or C (mode 2):  2D [b*T][g*128]

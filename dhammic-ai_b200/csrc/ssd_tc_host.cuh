@@ -65,8 +65,8 @@ inline Ws ws_layout(const Dims& d, int pass) {
         w.dyx = take(2 * bht);
         w.rterm = take(2 * bht);
         w.gS = take((size_t)d.b * d.h * (d.T / LT) * 8 * 4);
-        w.dAh_part = take((size_t)d.b * d.h * 4);
-        w.dD_part = take((size_t)d.b * d.h * 4);
+        w.dAh_part = take((size_t)d.b * (d.T / LT) * d.h * 4);
+        w.dD_part = take((size_t)d.b * (d.T / LT) * d.h * 4);
     }
     w.total = off;
     return w;
@@ -222,19 +222,17 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         SSD_TC_CHECK("tc_bwd_walk");
     }
     {
-        simt::Params P{};
-        P.d = d; P.x = a->x; P.dy = a->dy; P.dt = a->dt; P.A_head = a->A_head; P.D = a->D; P.dfinal = a->dfinal;
-        P.final_state = fin; P.g_row = (float*)(ws + w.g); P.g_col = nullptr; P.ddtx = (float*)(ws + w.ddtx);
-        P.dyx = (float*)(ws + w.dyx); P.da = a->cumsum_is_input ? nullptr : a->da; P.ddt = a->ddt;
-        P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = (float*)(ws + w.dD_part);
-        P.scan_len = LT;
-        const size_t half = (size_t)d.b * d.h * d.T;
-        P.g_row2 = P.g_row + half; P.ddtx2 = P.ddtx + half; P.dyx2 = P.dyx + half; P.gS = (const float*)(ws + w.gS);
-        SSD_LAUNCH(prof::K_DECAY, st, simt::decay_grad_kernel<__nv_bfloat16><<<dim3(d.h, d.b), simt::NTHR, 0, st>>>(P));
+        DecayTileParams P{};
+        P.g = (const float*)(ws + w.g); P.ddtx = (const float*)(ws + w.ddtx); P.gS = (const float*)(ws + w.gS);
+        P.dyx = (a->dt && a->D) ? (const float*)(ws + w.dyx) : nullptr;
+        P.dt = a->dt; P.A_head = a->A_head; P.ddt = a->ddt; P.da = a->cumsum_is_input ? nullptr : a->da;
+        P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = P.dyx ? (float*)(ws + w.dD_part) : nullptr;
+        P.b = d.b; P.T = d.T; P.h = d.h; P.nt = nt;
+        SSD_LAUNCH(prof::K_DECAY, st, decay_tile_kernel<<<dim3(nt, (d.h + 31) / 32, d.b), 256, 0, st>>>(P));
         SSD_TC_CHECK("decay_grad");
         if (a->dt) {
-            SSD_LAUNCH(prof::K_REDUCE, st, simt::reduce_batch_kernel<<<(d.h + 127) / 128, 128, 0, st>>>(P.dAh_part, a->dA_head, d.b, d.h));
-            if (a->D) SSD_LAUNCH(prof::K_REDUCE, st, simt::reduce_batch_kernel<<<(d.h + 127) / 128, 128, 0, st>>>(P.dD_part, a->dD, d.b, d.h));
+            SSD_LAUNCH(prof::K_REDUCE, st, reduce_rows_kernel<<<d.h, 256, 0, st>>>(P.dAh_part, a->dA_head, d.b * nt, d.h));
+            if (a->D) SSD_LAUNCH(prof::K_REDUCE, st, reduce_rows_kernel<<<d.h, 256, 0, st>>>(P.dD_part, a->dD, d.b * nt, d.h));
             SSD_TC_CHECK("reduce_batch");
         }
     }

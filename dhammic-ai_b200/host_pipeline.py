@@ -22,7 +22,7 @@ _OUT = ("y", "dx", "ddt", "dB", "dC")
 
 
 class HostPipeline:
-    def __init__(self, device: torch.device | str = "cuda", micro_batches: int = 4):
+    def __init__(self, device: torch.device | str = "cuda", micro_batches: int = 8):
         self.dev = torch.device(device)
         self.nmb = int(micro_batches)
         self.s_in = torch.cuda.Stream(self.dev)
