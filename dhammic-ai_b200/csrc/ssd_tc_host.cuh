@@ -73,7 +73,11 @@ inline Ws ws_layout(const Dims& d, int pass) {
 }
 
 inline size_t workspace_bytes(const Dims& d, int pass) { return ws_layout(d, pass).total; }
-inline size_t states_bytes(const Dims& d) { return (size_t)d.b * (d.T / LT) * d.h * DN * HP * 2; }
+// The `states` buffer a forward call may fill for the backward call of the same inputs: the bf16 state entering
+// every tile, followed by the two (b,h,T) fp32 arrays the tile kernels read (tile-cumulative log2 decay, dt in
+// (b,h,T) order), so that the backward neither walks the states nor rebuilds those arrays.
+inline size_t tile_states_bytes(const Dims& d) { return (size_t)d.b * (d.T / LT) * d.h * DN * HP * 2; }
+inline size_t states_bytes(const Dims& d) { return tile_states_bytes(d) + 2 * ((size_t)d.b * d.h * d.T * 4); }
 
 #define SSD_TC_FAIL(code, ...)              \
     do {                                    \
@@ -116,6 +120,10 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     int* status = (int*)(ws + w.status);
     float* tcum = (float*)(ws + w.tcum);
     float* dtT = a->dt ? (float*)(ws + w.dtT) : nullptr;
+    if (a->states && !states_only) {  // kept for the backward call, behind the tile states
+        tcum = (float*)((char*)a->states + tile_states_bytes(d));
+        if (a->dt) dtT = tcum + (size_t)d.b * d.h * d.T;
+    }
     if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     if (!a->cumsum_is_input) {
         simt::Params P{};
@@ -173,7 +181,12 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     float* fin = (float*)(ws + w.final_state);
     float* dinit = a->dinit ? a->dinit : (float*)(ws + w.dinit);
     if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
-    if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, st, err, errn)) return rc;
+    if (a->states && !(a->flags & SSD_B200_BWD_DINIT_ONLY)) {  // the forward left both arrays behind the tile states
+        tcum = (float*)((uintptr_t)a->states + tile_states_bytes(d));
+        dtT = a->dt ? tcum + (size_t)d.b * d.h * d.T : nullptr;
+    } else if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, st, err, errn)) {
+        return rc;
+    }
     if (int rc = set_walk_attrs(err, errn)) return rc;
     const int nt = d.T / LT;
     const uint64_t rows = (uint64_t)d.b * d.T, srows = (uint64_t)d.b * nt * d.h * DN;

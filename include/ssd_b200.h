@@ -105,8 +105,9 @@ typedef struct ssd_b200_fwd_args {
     void *workspace;
     size_t workspace_bytes;
     void *states; /* optional output, ssd_b200_states_bytes() bytes: the recurrent state entering every
-                     128-position tile, in the layout the backward wants.  Passing the same buffer to
-                     ssd_b200_bwd saves it one recomputation pass; NULL = do not save. */
+                     128-position tile and the per-position decay arrays of the tile kernels, in the layout
+                     the backward wants.  Passing the same buffer to ssd_b200_bwd (same inputs) saves it the
+                     state walk and the rebuild of those arrays; NULL = do not save. */
 } ssd_b200_fwd_args;
 
 /*
