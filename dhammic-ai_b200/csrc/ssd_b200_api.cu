@@ -326,36 +326,47 @@ int check_forms(const void* a, const float* dt, const float* A_head, const float
 namespace {
 template <class T>
 int m3_fwd_impl(const ssd::Dims& d, const void* x, const float* dt, const float* lam, const float* A_head, const void* B,
-                const void* C, const void* ang, void* xg, void* xb, float* dA, void* Br, void* Cr, void* Bprev, float* cum,
+                const void* C, const void* ang, void* xw, float* dA, void* Br, void* Cr, float* sdot, float* cum,
                 float* segsum, cudaStream_t st) {
     using namespace ssd::m3;
     const int E = d.h * (d.n / 2), nseg = (d.T + SEG - 1) / SEG;
     dim3 gs(nseg, (E + 255) / 256, d.b);
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<T><<<gs, 256, 0, st>>>((const T*)ang, segsum, d.T, E));
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<T, float><<<gs, 256, 0, st>>>((const T*)ang, segsum, cum, d.T, E, 0, -1.f)));
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, rope_fwd_kernel<T><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, (T*)Bprev, d.T, d.h, d.g, d.n));
-    const size_t rows = (size_t)d.b * d.T * d.h;
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, xprod_fwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)x, dt, lam, A_head, (T*)xg, (T*)xb, dA, d.T, d.h, d.p, rows));
+    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, rope_fwd_kernel<T><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n));
+    const size_t grows = (size_t)d.b * d.T * d.g, rows = (size_t)d.b * d.T * d.h;
+    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, bc_dot_kernel<T><<<(unsigned)((grows + 7) / 8), 256, 0, st>>>((const T*)B, (const T*)C, sdot, d.n, grows));
+    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, xw_fwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)x, dt, lam, A_head, (T*)xw, dA, d.T, d.h, d.p, rows));
     CUDA_LAUNCH_CHECK("mamba3 prologue forward");
     return 0;
 }
 
 template <class T>
-int m3_bwd_impl(const ssd::Dims& d, const void* x, const void* dy, const float* dt, const float* lam, const float* A_head,
-                const float* D, const void* B, const void* C, const float* cum, const void* dxg, const void* dxb,
-                const void* dBr, const void* dBprev, const void* dCr1, const void* dCr2, void* dx, float* dgam, float* dbet,
-                float* dyx, void* dB, void* dC, void* dang, float* dcum, float* segsum, cudaStream_t st) {
+int m3_skip_impl(const ssd::Dims& d, const void* y_scan, const void* x, const float* D, const float* dt, const float* lam,
+                 const float* sdot, void* y, cudaStream_t st) {
+    using namespace ssd::m3;
+    const size_t rows = (size_t)d.b * d.T * d.h;
+    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, skip_fwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)y_scan, (const T*)x, D, dt, lam, sdot, (T*)y, d.T, d.h, d.hpg, d.p, rows));
+    CUDA_LAUNCH_CHECK("mamba3 skip forward");
+    return 0;
+}
+
+template <class T>
+int m3_bwd_impl(const ssd::Dims& d, const void* x, const void* dy, const float* dt, const float* lam, const float* D,
+                const void* B, const void* C, const float* cum, const float* sdot, const void* dxw, const void* dBr,
+                const void* dCr, void* dx, float* dw, float* dyx, void* dB, void* dC, void* dang, float* dcum, float* segsum,
+                cudaStream_t st) {
     using namespace ssd::m3;
     const int E = d.h * (d.n / 2), nseg = (d.T + SEG - 1) / SEG;
-    const size_t sm = (size_t)2 * d.h * d.n * sizeof(float);
+    const size_t rows = (size_t)d.b * d.T * d.h;
+    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, xw_bwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)x, (const T*)dy, (const T*)dxw, dt, lam, D, sdot, (T*)dx, dw, dyx, d.T, d.h, d.hpg, d.p, rows));
+    const size_t sm = ((size_t)2 * d.h * d.n + d.h) * sizeof(float);
     if (int rc = set_smem(rope_bwd_kernel<T>, sm, "rope_bwd")) return rc;
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, rope_bwd_kernel<T><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dBprev, (const T*)dCr1, (const T*)dCr2, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n));
+    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, rope_bwd_kernel<T><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n));
     dim3 gs(nseg, (E + 255) / 256, d.b);
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<float><<<gs, 256, 0, st>>>(dcum, segsum, d.T, E));
     // d raw_angles[t] = - sum_{s >= t} d cum[s]
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<float, T><<<gs, 256, 0, st>>>(dcum, segsum, (T*)dang, d.T, E, 1, -1.f)));
-    const size_t rows = (size_t)d.b * d.T * d.h;
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, xprod_bwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)x, (const T*)dy, (const T*)dxg, (const T*)dxb, dt, lam, A_head, D, (T*)dx, dgam, dbet, dyx, d.T, d.h, d.p, rows));
     CUDA_LAUNCH_CHECK("mamba3 prologue backward");
     return 0;
 }
@@ -543,36 +554,45 @@ int ssd_b200_device_status(const ssd_b200_shape* shape, const void* workspace, v
 }
 
 int ssd_b200_m3_prologue_fwd(const ssd_b200_shape* shape, const void* x, const float* dt, const float* lam,
-                             const float* A_head, const void* B, const void* C, const void* raw_angles, void* xg, void* xb,
-                             float* dA, void* Br, void* Cr, void* Bprev, float* cum, float* segsum_ws, void* stream) {
+                             const float* A_head, const void* B, const void* C, const void* raw_angles, void* xw,
+                             float* dA, void* Br, void* Cr, float* sdot, float* cum, float* segsum_ws, void* stream) {
     if (int rc = check_shape(shape)) return rc;
-    if (!x || !dt || !lam || !A_head || !B || !C || !raw_angles || !xg || !xb || !dA || !Br || !Cr || !Bprev || !cum || !segsum_ws)
+    if (!x || !dt || !lam || !A_head || !B || !C || !raw_angles || !xw || !dA || !Br || !Cr || !sdot || !cum || !segsum_ws)
         return fail(SSD_B200_EINVAL, "null pointer");
     if (shape->dstate % 2) return fail(SSD_B200_EINVAL, "d_state must be even for the pairwise rotation");
     ssd::Dims d = dims_of(*shape);
     if (d.T > 65535 || d.b > 65535) return fail(SSD_B200_EUNSUPPORTED, "grid dimension too large");
     cudaStream_t st = (cudaStream_t)stream;
     return shape->dtype == SSD_B200_BF16
-               ? m3_fwd_impl<__nv_bfloat16>(d, x, dt, lam, A_head, B, C, raw_angles, xg, xb, dA, Br, Cr, Bprev, cum, segsum_ws, st)
-               : m3_fwd_impl<float>(d, x, dt, lam, A_head, B, C, raw_angles, xg, xb, dA, Br, Cr, Bprev, cum, segsum_ws, st);
+               ? m3_fwd_impl<__nv_bfloat16>(d, x, dt, lam, A_head, B, C, raw_angles, xw, dA, Br, Cr, sdot, cum, segsum_ws, st)
+               : m3_fwd_impl<float>(d, x, dt, lam, A_head, B, C, raw_angles, xw, dA, Br, Cr, sdot, cum, segsum_ws, st);
+}
+
+int ssd_b200_m3_skip_fwd(const ssd_b200_shape* shape, const void* y_scan, const void* x, const float* D, const float* dt,
+                         const float* lam, const float* sdot, void* y, void* stream) {
+    if (int rc = check_shape(shape)) return rc;
+    if (!y_scan || !x || !dt || !lam || !sdot || !y) return fail(SSD_B200_EINVAL, "null pointer");
+    ssd::Dims d = dims_of(*shape);
+    cudaStream_t st = (cudaStream_t)stream;
+    return shape->dtype == SSD_B200_BF16 ? m3_skip_impl<__nv_bfloat16>(d, y_scan, x, D, dt, lam, sdot, y, st)
+                                         : m3_skip_impl<float>(d, y_scan, x, D, dt, lam, sdot, y, st);
 }
 
 int ssd_b200_m3_prologue_bwd(const ssd_b200_shape* shape, const void* x, const void* dy, const float* dt, const float* lam,
-                             const float* A_head, const float* D, const void* B, const void* C, const float* cum,
-                             const void* dxg, const void* dxb, const void* dBr, const void* dBprev, const void* dCr1,
-                             const void* dCr2, void* dx, float* dgam, float* dbet, float* dyx, void* dB, void* dC,
-                             void* d_raw_angles, float* dcum_ws, float* segsum_ws, void* stream) {
+                             const float* D, const void* B, const void* C, const float* cum, const float* sdot,
+                             const void* dxw, const void* dBr, const void* dCr, void* dx, float* dw, float* dyx, void* dB,
+                             void* dC, void* d_raw_angles, float* dcum_ws, float* segsum_ws, void* stream) {
     if (int rc = check_shape(shape)) return rc;
-    if (!x || !dy || !dt || !lam || !A_head || !B || !C || !cum || !dxg || !dxb || !dBr || !dBprev || !dCr1 || !dCr2 || !dx ||
-        !dgam || !dbet || !dyx || !dB || !dC || !d_raw_angles || !dcum_ws || !segsum_ws)
+    if (!x || !dy || !dt || !lam || !B || !C || !cum || !sdot || !dxw || !dBr || !dCr || !dx || !dw || !dyx || !dB || !dC ||
+        !d_raw_angles || !dcum_ws || !segsum_ws)
         return fail(SSD_B200_EINVAL, "null pointer");
     if (shape->dstate % 2) return fail(SSD_B200_EINVAL, "d_state must be even for the pairwise rotation");
     ssd::Dims d = dims_of(*shape);
     if (d.T > 65535 || d.b > 65535) return fail(SSD_B200_EUNSUPPORTED, "grid dimension too large");
     cudaStream_t st = (cudaStream_t)stream;
     return shape->dtype == SSD_B200_BF16
-               ? m3_bwd_impl<__nv_bfloat16>(d, x, dy, dt, lam, A_head, D, B, C, cum, dxg, dxb, dBr, dBprev, dCr1, dCr2, dx, dgam, dbet, dyx, dB, dC, d_raw_angles, dcum_ws, segsum_ws, st)
-               : m3_bwd_impl<float>(d, x, dy, dt, lam, A_head, D, B, C, cum, dxg, dxb, dBr, dBprev, dCr1, dCr2, dx, dgam, dbet, dyx, dB, dC, d_raw_angles, dcum_ws, segsum_ws, st);
+               ? m3_bwd_impl<__nv_bfloat16>(d, x, dy, dt, lam, D, B, C, cum, sdot, dxw, dBr, dCr, dx, dw, dyx, dB, dC, d_raw_angles, dcum_ws, segsum_ws, st)
+               : m3_bwd_impl<float>(d, x, dy, dt, lam, D, B, C, cum, sdot, dxw, dBr, dCr, dx, dw, dyx, dB, dC, d_raw_angles, dcum_ws, segsum_ws, st);
 }
 
 int ssd_b200_materialize_cache(const ssd_b200_shape* shape, const float* a_cumsum, void* L, void* decay_chunk,

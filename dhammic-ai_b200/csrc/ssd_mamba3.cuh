@@ -1,13 +1,22 @@
-// Element-wise prologue of the Mamba-3 style variant: data-dependent rotary state angles and the
-// trapezoidal two-term products, forward and backward.  These are the steps the reference's block
-// runs before its two scan calls (src/mamba_base_engine.py:128-181; rotation as in
-// tests/kernels/test_rope.py:31-43; gamma / beta as in src/kernels/trapezoidal.py:6-12):
+// Element-wise kernels of the Mamba-3 style variant: data-dependent rotary state angles and the
+// trapezoidal two-term discretisation, forward and backward (the block math of
+// src/mamba_base_engine.py:128-187; rotation as in tests/kernels/test_rope.py:31-43; gamma / beta as in
+// src/kernels/trapezoidal.py:6-12).
 //
-//   cum      = -cumsum_T(raw_angles)                                   (b,T,h,n/2)   scan_T kernels
-//   Br, Cr   = rope(B_group(h), cum), rope(C_group(h), cum)            (b,T,h,n)     rope_fwd_kernel
-//   Bprev[t] = Br[t-1]  (zero at t = 0)
-//   dA = dt A_head,  gamma = lam dt,  beta = (1-lam) dt exp(dA)        (b,T,h)
-//   xg = x gamma,  xb[t] = x[t-1] beta[t]                              (b,T,h,p)     xprod_fwd_kernel
+// The reference evaluates  Y = SSD(x gamma, a, Br, Cr) + SSD(shift(x) beta, a, shift(Br), Cr) + D x  with
+// gamma = lam dt, beta = (1-lam) dt exp(a), a = dt A_head.  The shifted term at position j+1 decays to row i
+// exactly like an input at position j scaled by exp(-a[j+1]), and beta[j+1] exp(-a[j+1]) = (1-lam[j+1]) dt[j+1]
+// =: u[j], so for every i > j both terms share one decay mask; only i = j has no shifted term.  Hence
+//
+//   Y = SSD(x w, a, Br, Cr) + (D - u <Br, Cr>) x ,   w = lam dt + u ,   u[T-1] = 0
+//
+// one scan instead of two, and <Br, Cr> = <B, C> because both are rotated by the same angles.  Steps:
+//
+//   cum    = -cumsum_T(raw_angles)                                  (b,T,h,n/2)   scanT kernels
+//   Br, Cr = rope(B_group(h), cum), rope(C_group(h), cum)           (b,T,h,n)     rope_fwd_kernel
+//   s      = <B, C> per group                                       (b,T,g)       bc_dot_kernel
+//   xw = x w,  a = dt A_head                                                      xw_fwd_kernel
+//   y  = y_scan + (D - u s) x                                                     skip_fwd_kernel
 //
 // All of them are HBM-bound streaming kernels; the scans along T are two-pass (per-segment sums, then a
 // segment-local scan seeded by the prefix of the earlier segments).
@@ -79,8 +88,7 @@ __device__ __forceinline__ void sincos_reduced(float a, float* s, float* c) {
 template <class T>
 __global__ void __launch_bounds__(256) rope_fwd_kernel(const T* __restrict__ B, const T* __restrict__ C,
                                                        const float* __restrict__ cum, T* __restrict__ Br,
-                                                       T* __restrict__ Cr, T* __restrict__ Bprev, int Tlen, int h, int g,
-                                                       int n) {
+                                                       T* __restrict__ Cr, int Tlen, int h, int g, int n) {
     const int t = blockIdx.x, bb = blockIdx.y;
     const int half = n / 2, hpg = h / g;
     const size_t row = (size_t)bb * Tlen + t;
@@ -93,37 +101,37 @@ __global__ void __launch_bounds__(256) rope_fwd_kernel(const T* __restrict__ B, 
         const float b1 = to_f(B[ib]), b2 = to_f(B[ib + half]);
         const float c1 = to_f(C[ib]), c2 = to_f(C[ib + half]);
         const size_t o = (row * h + hh) * n + m;
-        const T br1 = from_f<T>(b1 * c - b2 * s), br2 = from_f<T>(b1 * s + b2 * c);
-        Br[o] = br1;
-        Br[o + half] = br2;
+        Br[o] = from_f<T>(b1 * c - b2 * s);
+        Br[o + half] = from_f<T>(b1 * s + b2 * c);
         Cr[o] = from_f<T>(c1 * c - c2 * s);
         Cr[o + half] = from_f<T>(c1 * s + c2 * c);
-        if (t + 1 < Tlen) {
-            Bprev[o + (size_t)h * n] = br1;
-            Bprev[o + (size_t)h * n + half] = br2;
-        }
-        if (t == 0) {
-            Bprev[o] = from_f<T>(0.f);
-            Bprev[o + half] = from_f<T>(0.f);
-        }
     }
 }
 
-// Backward of the rotation.  dBr_total[t] = dBr[t] + dBprev[t+1], dCr_total = dCr1 + dCr2.
+// u[t] = (1 - lam[t+1]) dt[t+1], zero at the last position; `w` indexes (b,t,h) flattened.
+__device__ __forceinline__ float u_of(const float* __restrict__ dt, const float* __restrict__ lam, size_t w, int t, int Tlen, int h) {
+    return t + 1 < Tlen ? (1.f - lam[w + h]) * dt[w + h] : 0.f;
+}
+
+// Backward of the rotation and of the diagonal term.
 //   d v = R(-theta) d out ;  d theta = -d out1 * out2 + d out2 * out1   (summed over B and C)
-// dB / dC are summed over the heads of a group through shared memory (fixed order, deterministic).
+// dB / dC are summed over the heads of a group through shared memory (fixed order, deterministic); the
+// diagonal term -u s x contributes d s = -u <dy, x> per head, i.e. (sum_h d s) C to dB and (sum_h d s) B to dC.
 template <class T>
 __global__ void __launch_bounds__(256) rope_bwd_kernel(const T* __restrict__ B, const T* __restrict__ C,
                                                        const float* __restrict__ cum, const T* __restrict__ dBr,
-                                                       const T* __restrict__ dBprev, const T* __restrict__ dCr1,
-                                                       const T* __restrict__ dCr2, T* __restrict__ dB, T* __restrict__ dC,
-                                                       float* __restrict__ dcum, int Tlen, int h, int g, int n) {
-    extern __shared__ float sm[];  // [2][h][n]: d(un-rotated) B and C per head
+                                                       const T* __restrict__ dCr, const float* __restrict__ dyx,
+                                                       const float* __restrict__ dt, const float* __restrict__ lam,
+                                                       T* __restrict__ dB, T* __restrict__ dC, float* __restrict__ dcum,
+                                                       int Tlen, int h, int g, int n) {
+    extern __shared__ float sm[];  // [2][h][n]: d(un-rotated) B and C per head, then [h] d s
     const int t = blockIdx.x, bb = blockIdx.y;
     const int half = n / 2, hpg = h / g;
     const size_t row = (size_t)bb * Tlen + t;
     float* sB = sm;
     float* sC = sm + (size_t)h * n;
+    float* sds = sC + (size_t)h * n;
+    for (int hh = threadIdx.x; hh < h; hh += 256) sds[hh] = -u_of(dt, lam, row * h + hh, t, Tlen, h) * dyx[row * h + hh];
     for (int e = threadIdx.x; e < h * half; e += 256) {
         const int hh = e / half, m = e - hh * half;
         const int gg = hh / hpg;
@@ -133,12 +141,8 @@ __global__ void __launch_bounds__(256) rope_bwd_kernel(const T* __restrict__ B, 
         const float b1 = to_f(B[ib]), b2 = to_f(B[ib + half]);
         const float c1 = to_f(C[ib]), c2 = to_f(C[ib + half]);
         const size_t o = (row * h + hh) * n + m;
-        float db1 = to_f(dBr[o]), db2 = to_f(dBr[o + half]);
-        if (t + 1 < Tlen) {
-            db1 += to_f(dBprev[o + (size_t)h * n]);
-            db2 += to_f(dBprev[o + (size_t)h * n + half]);
-        }
-        const float dc1 = to_f(dCr1[o]) + to_f(dCr2[o]), dc2 = to_f(dCr1[o + half]) + to_f(dCr2[o + half]);
+        const float db1 = to_f(dBr[o]), db2 = to_f(dBr[o + half]);
+        const float dc1 = to_f(dCr[o]), dc2 = to_f(dCr[o + half]);
         const float ob1 = b1 * c - b2 * s, ob2 = b1 * s + b2 * c;
         const float oc1 = c1 * c - c2 * s, oc2 = c1 * s + c2 * c;
         dcum[row * h * half + e] = (-db1 * ob2 + db2 * ob1) + (-dc1 * oc2 + dc2 * oc1);
@@ -150,83 +154,99 @@ __global__ void __launch_bounds__(256) rope_bwd_kernel(const T* __restrict__ B, 
     __syncthreads();
     for (int e = threadIdx.x; e < g * n; e += 256) {
         const int gg = e / n, nn = e - gg * n;
-        float ab = 0.f, ac = 0.f;
+        float ab = 0.f, ac = 0.f, ds = 0.f;
         for (int hl = 0; hl < hpg; ++hl) {
             ab += sB[(gg * hpg + hl) * n + nn];
             ac += sC[(gg * hpg + hl) * n + nn];
+            ds += sds[gg * hpg + hl];
         }
-        dB[(row * g + gg) * n + nn] = from_f<T>(ab);
-        dC[(row * g + gg) * n + nn] = from_f<T>(ac);
+        const size_t ib = (row * g + gg) * n + nn;
+        dB[ib] = from_f<T>(ab + ds * to_f(C[ib]));
+        dC[ib] = from_f<T>(ac + ds * to_f(B[ib]));
     }
 }
 
 // ------------------------------------------------------------------------------------------
-// Trapezoidal products.  One warp per (position, head): lanes over headdim.
+// Trapezoidal weights.  One warp per (position, head) (or per (position, group) for the dot): lanes over
+// headdim / d_state.
 // ------------------------------------------------------------------------------------------
 template <class T>
-__global__ void __launch_bounds__(256) xprod_fwd_kernel(const T* __restrict__ x, const float* __restrict__ dt,
-                                                        const float* __restrict__ lam, const float* __restrict__ A_head,
-                                                        T* __restrict__ xg, T* __restrict__ xb, float* __restrict__ dA,
-                                                        int Tlen, int h, int p, size_t rows) {
+__global__ void __launch_bounds__(256) bc_dot_kernel(const T* __restrict__ B, const T* __restrict__ C, float* __restrict__ sdot,
+                                                     int n, size_t rows) {
+    const size_t w = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // (b, t, g) flattened
+    if (w >= rows) return;
+    const int lane = threadIdx.x & 31;
+    float a = 0.f;
+    for (int nn = lane; nn < n; nn += 32) a += to_f(B[w * n + nn]) * to_f(C[w * n + nn]);
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) a += __shfl_xor_sync(0xffffffffu, a, of);
+    if (lane == 0) sdot[w] = a;
+}
+
+template <class T>
+__global__ void __launch_bounds__(256) xw_fwd_kernel(const T* __restrict__ x, const float* __restrict__ dt,
+                                                     const float* __restrict__ lam, const float* __restrict__ A_head,
+                                                     T* __restrict__ xw, float* __restrict__ dA, int Tlen, int h, int p,
+                                                     size_t rows) {
     const size_t w = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // (b, t, h) flattened
     if (w >= rows) return;
     const int lane = threadIdx.x & 31;
     const int hh = (int)(w % h);
     const int t = (int)((w / h) % Tlen);
-    const float d = dt[w], l = lam[w], a = d * A_head[hh];
-    const float gam = l * d, bet = (1.f - l) * d * __expf(a);
-    if (lane == 0) dA[w] = a;
-    const T* xr = x + w * p;
-    const T* xp = xr - (size_t)h * p;  // previous position, same head
-    for (int pp = lane; pp < p; pp += 32) {
-        xg[w * p + pp] = from_f<T>(to_f(xr[pp]) * gam);
-        xb[w * p + pp] = from_f<T>(t > 0 ? to_f(xp[pp]) * bet : 0.f);
-    }
+    const float d = dt[w];
+    const float wt = lam[w] * d + u_of(dt, lam, w, t, Tlen, h);
+    if (lane == 0) dA[w] = d * A_head[hh];
+    for (int pp = lane; pp < p; pp += 32) xw[w * p + pp] = from_f<T>(to_f(x[w * p + pp]) * wt);
 }
 
-// dx[t] = dxg[t] gamma[t] + dxb[t+1] beta[t+1] + D dy[t];  dgam = <dxg, x>,  dbet[t] = <dxb[t], x[t-1]>,  dyx = <dy, x>
+// y = y_scan + (D - u s) x   (y may be y_scan itself)
 template <class T>
-__global__ void __launch_bounds__(256) xprod_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
-                                                        const T* __restrict__ dxg, const T* __restrict__ dxb,
-                                                        const float* __restrict__ dt, const float* __restrict__ lam,
-                                                        const float* __restrict__ A_head, const float* __restrict__ D,
-                                                        T* __restrict__ dx, float* __restrict__ dgam,
-                                                        float* __restrict__ dbet, float* __restrict__ dyx, int Tlen, int h,
-                                                        int p, size_t rows) {
+__global__ void __launch_bounds__(256) skip_fwd_kernel(const T* y_scan, const T* __restrict__ x, const float* __restrict__ D,
+                                                       const float* __restrict__ dt, const float* __restrict__ lam,
+                                                       const float* __restrict__ sdot, T* y, int Tlen, int h, int hpg, int p,
+                                                       size_t rows) {
     const size_t w = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (w >= rows) return;
     const int lane = threadIdx.x & 31;
     const int hh = (int)(w % h);
     const int t = (int)((w / h) % Tlen);
-    const float d = dt[w], l = lam[w];
-    const float gam = l * d;
-    float bet_next = 0.f;
-    if (t + 1 < Tlen) {
-        const size_t wn = w + h;
-        const float dn = dt[wn], ln = lam[wn];
-        bet_next = (1.f - ln) * dn * __expf(dn * A_head[hh]);
-    }
-    const float Dh = D ? D[hh] : 0.f;
-    float ag = 0.f, ab = 0.f, ay = 0.f;
+    const int g = h / hpg;
+    const float coef = (D ? D[hh] : 0.f) - u_of(dt, lam, w, t, Tlen, h) * sdot[(w / h) * g + hh / hpg];
+    for (int pp = lane; pp < p; pp += 32) y[w * p + pp] = from_f<T>(to_f(y_scan[w * p + pp]) + coef * to_f(x[w * p + pp]));
+}
+
+// dx = dxw w + (D - u s) dy ;  dw = <dxw, x> ;  dyx = <dy, x>
+template <class T>
+__global__ void __launch_bounds__(256) xw_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                                     const T* __restrict__ dxw, const float* __restrict__ dt,
+                                                     const float* __restrict__ lam, const float* __restrict__ D,
+                                                     const float* __restrict__ sdot, T* __restrict__ dx,
+                                                     float* __restrict__ dw, float* __restrict__ dyx, int Tlen, int h, int hpg,
+                                                     int p, size_t rows) {
+    const size_t w = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (w >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const int hh = (int)(w % h);
+    const int t = (int)((w / h) % Tlen);
+    const int g = h / hpg;
+    const float u = u_of(dt, lam, w, t, Tlen, h);
+    const float wt = lam[w] * dt[w] + u;
+    const float coef = (D ? D[hh] : 0.f) - u * sdot[(w / h) * g + hh / hpg];
+    float aw = 0.f, ay = 0.f;
     for (int pp = lane; pp < p; pp += 32) {
         const size_t o = w * p + pp;
-        const float xv = to_f(x[o]), dyv = to_f(dy[o]), g1 = to_f(dxg[o]);
-        float v = g1 * gam + Dh * dyv;
-        if (t + 1 < Tlen) v += to_f(dxb[o + (size_t)h * p]) * bet_next;
-        dx[o] = from_f<T>(v);
-        ag += g1 * xv;
+        const float xv = to_f(x[o]), dyv = to_f(dy[o]), g1 = to_f(dxw[o]);
+        dx[o] = from_f<T>(g1 * wt + coef * dyv);
+        aw += g1 * xv;
         ay += dyv * xv;
-        if (t > 0) ab += to_f(dxb[o]) * to_f(x[o - (size_t)h * p]);
     }
 #pragma unroll
     for (int of = 16; of > 0; of >>= 1) {
-        ag += __shfl_xor_sync(0xffffffffu, ag, of);
-        ab += __shfl_xor_sync(0xffffffffu, ab, of);
+        aw += __shfl_xor_sync(0xffffffffu, aw, of);
         ay += __shfl_xor_sync(0xffffffffu, ay, of);
     }
     if (lane == 0) {
-        dgam[w] = ag;
-        dbet[w] = ab;
+        dw[w] = aw;
         dyx[w] = ay;
     }
 }

@@ -194,6 +194,31 @@ def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=
     return y, final, cum, shape, states
 
 
+def _run_bwd_operator(shape, x, A, B, Cm, cum, dY, states, init4=None, dfinal_state=None, cached=False):
+    """Backward launcher of the operator form (log-decay A given per position).  Returns
+    (dx, dA fp32 (b,T,h) or None when ``cached``, dB, dC, d initial state fp32 or None)."""
+    lib = _cabi.load()
+    dev = x.device
+    b, T, h, p = x.shape
+    with torch.cuda.device(dev):
+        dy = dY.contiguous()
+        if dy.dtype != x.dtype:
+            dy = dy.to(x.dtype)
+        dfin = None if dfinal_state is None else dfinal_state.float().contiguous()
+        dx = torch.empty_like(x)
+        dB = torch.empty_like(B)
+        dC = torch.empty_like(Cm)
+        da = None if cached else torch.empty(b, T, h, dtype=torch.float32, device=dev)
+        dinit = torch.empty(b, h, p, B.shape[3], dtype=torch.float32, device=dev) if init4 is not None else None
+        ws = _workspace(lib, shape, _cabi.PASS_BWD, dev)
+        args = _cabi.BwdArgs(shape, _ptr(x), _ptr(A), None, None, None, _ptr(B), _ptr(Cm), _ptr(init4), _ptr(cum),
+                             _ptr(dy), _ptr(dfin), _ptr(dx), _ptr(dB), _ptr(dC), _ptr(da), None, None, None, _ptr(dinit),
+                             1 if cached else 0, 0, _ptr(ws), ws.numel(), _ptr(states))
+        _cabi.check(lib.ssd_b200_bwd(C.byref(args), _stream(dev)))
+        _status(lib, shape, ws, dev)
+    return dx, da, dB, dC, dinit
+
+
 class FusedSSDScan(torch.autograd.Function):
     """Same call signature as the reference's FusedSSDScan (src/kernels/ssd_scan.py:441-465)."""
 
@@ -234,29 +259,8 @@ class FusedSSDScan(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dY, dfinal_state, dL_unused, ddecay_chunk_unused, dA_cumsum_unused):
         x, A, B, Cm, init4, cum = ctx.saved_tensors
-        lib = _cabi.load()
-        shape = ctx.shape_struct
-        dev = x.device
-        b, T, h, p = x.shape
-        with torch.cuda.device(dev):
-            dy = dY.contiguous()
-            if dy.dtype != x.dtype:
-                dy = dy.to(x.dtype)
-            dfin = None
-            if dfinal_state is not None:
-                dfin = dfinal_state.float().contiguous()
-            dx = torch.empty_like(x)
-            dB = torch.empty_like(B)
-            dC = torch.empty_like(Cm)
-            da = None if ctx.cached else torch.empty(b, T, h, dtype=torch.float32, device=dev)
-            dinit = torch.empty(b, h, p, B.shape[3], dtype=torch.float32, device=dev) if ctx.has_init else None
-            ws = _workspace(lib, shape, _cabi.PASS_BWD, dev)
-            args = _cabi.BwdArgs(shape, _ptr(x), _ptr(A), None, None, None, _ptr(B), _ptr(Cm),
-                                 _ptr(init4) if ctx.has_init else None, _ptr(cum), _ptr(dy), _ptr(dfin), _ptr(dx),
-                                 _ptr(dB), _ptr(dC), _ptr(da), None, None, None, _ptr(dinit),
-                                 1 if ctx.cached else 0, 0, _ptr(ws), ws.numel(), _ptr(ctx.states))
-            _cabi.check(lib.ssd_b200_bwd(C.byref(args), _stream(dev)))
-            _status(lib, shape, ws, dev)
+        dx, da, dB, dC, dinit = _run_bwd_operator(ctx.shape_struct, x, A, B, Cm, cum, dY, ctx.states,
+                                                  init4 if ctx.has_init else None, dfinal_state, ctx.cached)
         dA = None if da is None else da.to(A.dtype)
         dis = None
         if ctx.has_init:

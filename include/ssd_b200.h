@@ -225,26 +225,30 @@ int ssd_b200_state_prefix(const float *finals, const float *logp, float *out, in
                           int32_t reverse, void *stream);
 
 /*
- * Element-wise prologue of the Mamba-3 style variant, i.e. what the reference's block computes before
- * its two scan calls (src/mamba_base_engine.py:128-181; src/kernels/trapezoidal.py:6-12 for gamma / beta;
- * the rotation of src/kernels/rope.py:39-79 with cumulative per-head angles):
- *   cum = -cumsum_T(raw_angles) (b,T,h,n/2) fp32;  Br, Cr = rope(B, cum), rope(C, cum) (b,T,h,n);
- *   Bprev[t] = Br[t-1];  dA = dt*A_head;  xg = x*lam*dt;  xb[t] = x[t-1]*(1-lam[t])*dt[t]*exp(dA[t]).
- * x, B, C, raw_angles and the tensor outputs are in shape->dtype; dt, lam, A_head, dA, cum are fp32.
- * segsum_ws: b * ceil(T/128) * h * n/2 floats of scratch.  The backward takes the gradients of the six
- * outputs that reach it (dCr1 + dCr2 and dBr[t] + dBprev[t+1] are summed inside; pass a zero tensor for an
- * absent one) and writes dx (the xg / xb paths and, with D, the skip term), dgam = <dxg, x>, dbet = <dxb,
- * x_prev>, dyx = <dy, x> per (b,t,h), dB, dC (b,T,g,n) and d raw_angles; dcum_ws is (b,T,h,n/2) fp32 scratch.
+ * Element-wise kernels of the Mamba-3 style variant (no counterpart in the reference's operator file: its
+ * block does these steps with tensor arithmetic, src/mamba_base_engine.py:128-187).  The block's two scan
+ * calls  SSD(x gamma, a, Br, Cr) + SSD(shift(x) beta, a, shift(Br), Cr)  collapse into ONE scan
+ *     Y = SSD(x w, a, Br, Cr) + (D - u s) x,   w = lam dt + u,  u[t] = (1 - lam[t+1]) dt[t+1] (0 at the end),
+ * s = <B, C> per group (the rotation preserves it), a = dt A_head.
+ *   prologue_fwd: cum = -cumsum_T(raw_angles) (b,T,h,n/2); Br, Cr = rope(B, cum), rope(C, cum) (b,T,h,n);
+ *                 sdot = s (b,T,g); xw = x w; dA = a.
+ *   skip_fwd:     y = y_scan + (D - u s) x   (y may be y_scan; D may be NULL).
+ *   prologue_bwd: from dy, the scan's gradients dxw, dBr, dCr:  dx = dxw w + (D - u s) dy,  dw = <dxw, x>,
+ *                 dyx = <dy, x> per (b,t,h), dB, dC (b,T,g,n) (rotation undone, heads of a group summed, plus the
+ *                 s term) and d raw_angles.
+ * x, B, C, raw_angles and the tensor outputs are in shape->dtype; dt, lam, A_head, D, dA, sdot, cum, dw, dyx
+ * are fp32.  segsum_ws: b * ceil(T/128) * h * n/2 floats of scratch; dcum_ws: (b,T,h,n/2) fp32 scratch.
  */
 int ssd_b200_m3_prologue_fwd(const ssd_b200_shape *shape, const void *x, const float *dt, const float *lam,
-                             const float *A_head, const void *B, const void *C, const void *raw_angles, void *xg,
-                             void *xb, float *dA, void *Br, void *Cr, void *Bprev, float *cum, float *segsum_ws,
-                             void *stream);
+                             const float *A_head, const void *B, const void *C, const void *raw_angles, void *xw,
+                             float *dA, void *Br, void *Cr, float *sdot, float *cum, float *segsum_ws, void *stream);
+int ssd_b200_m3_skip_fwd(const ssd_b200_shape *shape, const void *y_scan, const void *x, const float *D, const float *dt,
+                         const float *lam, const float *sdot, void *y, void *stream);
 int ssd_b200_m3_prologue_bwd(const ssd_b200_shape *shape, const void *x, const void *dy, const float *dt,
-                             const float *lam, const float *A_head, const float *D, const void *B, const void *C,
-                             const float *cum, const void *dxg, const void *dxb, const void *dBr, const void *dBprev,
-                             const void *dCr1, const void *dCr2, void *dx, float *dgam, float *dbet, float *dyx,
-                             void *dB, void *dC, void *d_raw_angles, float *dcum_ws, float *segsum_ws, void *stream);
+                             const float *lam, const float *D, const void *B, const void *C, const float *cum,
+                             const float *sdot, const void *dxw, const void *dBr, const void *dCr, void *dx, float *dw,
+                             float *dyx, void *dB, void *dC, void *d_raw_angles, float *dcum_ws, float *segsum_ws,
+                             void *stream);
 
 /*
  * Measurement hooks (no counterpart in the reference).  ssd_b200_launch_count() is the number of
