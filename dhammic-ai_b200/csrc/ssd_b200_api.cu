@@ -324,6 +324,32 @@ int check_forms(const void* a, const float* dt, const float* A_head, const float
 }  // namespace
 
 namespace {
+// Threads per (b,t,h) row of the trapezoid kernels: p / V when that is a power of two <= 32 (16-byte accesses),
+// else 0 = scalar fallback with a full warp per row.
+template <class T>
+int m3_row_threads(int p) {
+    constexpr int V = ssd::m3::VecOf<T>::N;
+    if (p % V) return 0;
+    const int tpr = p / V;
+    return (tpr <= 32 && (tpr & (tpr - 1)) == 0) ? tpr : 0;
+}
+#define M3_ROW_DISPATCH(KERNEL, ...)                                                                              \
+    do {                                                                                                          \
+        constexpr int V = ssd::m3::VecOf<T>::N;                                                                   \
+        const int tpr = m3_row_threads<T>(d.p);                                                                   \
+        const size_t thr = rows * (size_t)(tpr ? tpr : 32);                                                       \
+        const unsigned blocks = (unsigned)((thr + 255) / 256);                                                    \
+        switch (tpr) {                                                                                            \
+            case 1: SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (KERNEL<T, V, 1><<<blocks, 256, 0, st>>>(__VA_ARGS__))); break;   \
+            case 2: SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (KERNEL<T, V, 2><<<blocks, 256, 0, st>>>(__VA_ARGS__))); break;   \
+            case 4: SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (KERNEL<T, V, 4><<<blocks, 256, 0, st>>>(__VA_ARGS__))); break;   \
+            case 8: SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (KERNEL<T, V, 8><<<blocks, 256, 0, st>>>(__VA_ARGS__))); break;   \
+            case 16: SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (KERNEL<T, V, 16><<<blocks, 256, 0, st>>>(__VA_ARGS__))); break; \
+            case 32: SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (KERNEL<T, V, 32><<<blocks, 256, 0, st>>>(__VA_ARGS__))); break; \
+            default: SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (KERNEL<T, 1, 32><<<blocks, 256, 0, st>>>(__VA_ARGS__))); break; \
+        }                                                                                                         \
+    } while (0)
+
 template <class T>
 int m3_fwd_impl(const ssd::Dims& d, const void* x, const float* dt, const float* lam, const float* A_head, const void* B,
                 const void* C, const void* ang, void* xw, float* dA, void* Br, void* Cr, float* sdot, float* cum,
@@ -333,10 +359,13 @@ int m3_fwd_impl(const ssd::Dims& d, const void* x, const float* dt, const float*
     dim3 gs(nseg, (E + 255) / 256, d.b);
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<T><<<gs, 256, 0, st>>>((const T*)ang, segsum, d.T, E));
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<T, float><<<gs, 256, 0, st>>>((const T*)ang, segsum, cum, d.T, E, 0, -1.f)));
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, rope_fwd_kernel<T><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n));
+    if ((d.n / 2) % VecOf<T>::N == 0)
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_fwd_kernel<T, VecOf<T>::N><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n)));
+    else
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_fwd_kernel<T, 1><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n)));
     const size_t grows = (size_t)d.b * d.T * d.g, rows = (size_t)d.b * d.T * d.h;
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, bc_dot_kernel<T><<<(unsigned)((grows + 7) / 8), 256, 0, st>>>((const T*)B, (const T*)C, sdot, d.n, grows));
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, xw_fwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)x, dt, lam, A_head, (T*)xw, dA, d.T, d.h, d.p, rows));
+    M3_ROW_DISPATCH(xw_fwd_kernel, (const T*)x, dt, lam, A_head, (T*)xw, dA, d.T, d.h, d.p, rows);
     CUDA_LAUNCH_CHECK("mamba3 prologue forward");
     return 0;
 }
@@ -346,7 +375,7 @@ int m3_skip_impl(const ssd::Dims& d, const void* y_scan, const void* x, const fl
                  const float* sdot, void* y, cudaStream_t st) {
     using namespace ssd::m3;
     const size_t rows = (size_t)d.b * d.T * d.h;
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, skip_fwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)y_scan, (const T*)x, D, dt, lam, sdot, (T*)y, d.T, d.h, d.hpg, d.p, rows));
+    M3_ROW_DISPATCH(skip_fwd_kernel, (const T*)y_scan, (const T*)x, D, dt, lam, sdot, (T*)y, d.T, d.h, d.hpg, d.p, rows);
     CUDA_LAUNCH_CHECK("mamba3 skip forward");
     return 0;
 }
@@ -359,10 +388,15 @@ int m3_bwd_impl(const ssd::Dims& d, const void* x, const void* dy, const float* 
     using namespace ssd::m3;
     const int E = d.h * (d.n / 2), nseg = (d.T + SEG - 1) / SEG;
     const size_t rows = (size_t)d.b * d.T * d.h;
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, xw_bwd_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)x, (const T*)dy, (const T*)dxw, dt, lam, D, sdot, (T*)dx, dw, dyx, d.T, d.h, d.hpg, d.p, rows));
+    M3_ROW_DISPATCH(xw_bwd_kernel, (const T*)x, (const T*)dy, (const T*)dxw, dt, lam, D, sdot, (T*)dx, dw, dyx, d.T, d.h, d.hpg, d.p, rows);
     const size_t sm = ((size_t)2 * d.h * d.n + d.h) * sizeof(float);
-    if (int rc = set_smem(rope_bwd_kernel<T>, sm, "rope_bwd")) return rc;
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, rope_bwd_kernel<T><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n));
+    if ((d.n / 2) % VecOf<T>::N == 0) {
+        if (int rc = set_smem(rope_bwd_kernel<T, VecOf<T>::N>, sm, "rope_bwd")) return rc;
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, VecOf<T>::N><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n)));
+    } else {
+        if (int rc = set_smem(rope_bwd_kernel<T, 1>, sm, "rope_bwd")) return rc;
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, 1><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n)));
+    }
     dim3 gs(nseg, (E + 255) / 256, d.b);
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<float><<<gs, 256, 0, st>>>(dcum, segsum, d.T, E));
     // d raw_angles[t] = - sum_{s >= t} d cum[s]

@@ -28,6 +28,32 @@ namespace m3 {
 
 constexpr int SEG = 128;  // positions per scan segment
 
+// 16-byte vector access: V elements of T (8 bf16 or 4 fp32) per thread, or V = 1 for shapes that do not divide.
+template <class T> struct VecOf { static constexpr int N = 16 / sizeof(T); };
+template <class T, int V>
+__device__ __forceinline__ void load_vec(const T* p, float (&f)[V]) {
+    if constexpr (V == 1) {
+        f[0] = to_f(*p);
+    } else {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+        for (int q = 0; q < V; ++q) f[q] = to_f(e[q]);
+    }
+}
+template <class T, int V>
+__device__ __forceinline__ void store_vec(T* p, const float (&f)[V]) {
+    if constexpr (V == 1) {
+        *p = from_f<T>(f[0]);
+    } else {
+        uint4 u;
+        T* e = reinterpret_cast<T*>(&u);
+#pragma unroll
+        for (int q = 0; q < V; ++q) e[q] = from_f<T>(f[q]);
+        *reinterpret_cast<uint4*>(p) = u;
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Scan along T of a (b, T, E) tensor.  Pass 1: per-segment sums.
 // ------------------------------------------------------------------------------------------
@@ -85,26 +111,37 @@ __device__ __forceinline__ void sincos_reduced(float a, float* s, float* c) {
     __sincosf(r, s, c);
 }
 
-template <class T>
+template <class T, int V>
 __global__ void __launch_bounds__(256) rope_fwd_kernel(const T* __restrict__ B, const T* __restrict__ C,
                                                        const float* __restrict__ cum, T* __restrict__ Br,
                                                        T* __restrict__ Cr, int Tlen, int h, int g, int n) {
     const int t = blockIdx.x, bb = blockIdx.y;
-    const int half = n / 2, hpg = h / g;
+    const int half = n / 2, hpg = h / g, upr = half / V;  // V pair indices per thread
     const size_t row = (size_t)bb * Tlen + t;
-    for (int e = threadIdx.x; e < h * half; e += 256) {
-        const int hh = e / half, m = e - hh * half;
+    for (int e = threadIdx.x; e < h * upr; e += 256) {
+        const int hh = e / upr, m = (e - hh * upr) * V;
         const int gg = hh / hpg;
-        float s, c;
-        sincos_reduced(cum[row * h * half + e], &s, &c);
+        float ang[V], b1[V], b2[V], c1[V], c2[V], o1[V], o2[V];
+        const float* cp = cum + (row * h + hh) * half + m;
+#pragma unroll
+        for (int q = 0; q < V; ++q) ang[q] = cp[q];
         const size_t ib = (row * g + gg) * n + m;
-        const float b1 = to_f(B[ib]), b2 = to_f(B[ib + half]);
-        const float c1 = to_f(C[ib]), c2 = to_f(C[ib + half]);
+        load_vec<T, V>(B + ib, b1);
+        load_vec<T, V>(B + ib + half, b2);
+        load_vec<T, V>(C + ib, c1);
+        load_vec<T, V>(C + ib + half, c2);
         const size_t o = (row * h + hh) * n + m;
-        Br[o] = from_f<T>(b1 * c - b2 * s);
-        Br[o + half] = from_f<T>(b1 * s + b2 * c);
-        Cr[o] = from_f<T>(c1 * c - c2 * s);
-        Cr[o + half] = from_f<T>(c1 * s + c2 * c);
+        float sn[V], cs[V];
+#pragma unroll
+        for (int q = 0; q < V; ++q) sincos_reduced(ang[q], &sn[q], &cs[q]);
+#pragma unroll
+        for (int q = 0; q < V; ++q) { o1[q] = b1[q] * cs[q] - b2[q] * sn[q]; o2[q] = b1[q] * sn[q] + b2[q] * cs[q]; }
+        store_vec<T, V>(Br + o, o1);
+        store_vec<T, V>(Br + o + half, o2);
+#pragma unroll
+        for (int q = 0; q < V; ++q) { o1[q] = c1[q] * cs[q] - c2[q] * sn[q]; o2[q] = c1[q] * sn[q] + c2[q] * cs[q]; }
+        store_vec<T, V>(Cr + o, o1);
+        store_vec<T, V>(Cr + o + half, o2);
     }
 }
 
@@ -117,7 +154,7 @@ __device__ __forceinline__ float u_of(const float* __restrict__ dt, const float*
 //   d v = R(-theta) d out ;  d theta = -d out1 * out2 + d out2 * out1   (summed over B and C)
 // dB / dC are summed over the heads of a group through shared memory (fixed order, deterministic); the
 // diagonal term -u s x contributes d s = -u <dy, x> per head, i.e. (sum_h d s) C to dB and (sum_h d s) B to dC.
-template <class T>
+template <class T, int V>
 __global__ void __launch_bounds__(256) rope_bwd_kernel(const T* __restrict__ B, const T* __restrict__ C,
                                                        const float* __restrict__ cum, const T* __restrict__ dBr,
                                                        const T* __restrict__ dCr, const float* __restrict__ dyx,
@@ -126,30 +163,40 @@ __global__ void __launch_bounds__(256) rope_bwd_kernel(const T* __restrict__ B, 
                                                        int Tlen, int h, int g, int n) {
     extern __shared__ float sm[];  // [2][h][n]: d(un-rotated) B and C per head, then [h] d s
     const int t = blockIdx.x, bb = blockIdx.y;
-    const int half = n / 2, hpg = h / g;
+    const int half = n / 2, hpg = h / g, upr = half / V;
     const size_t row = (size_t)bb * Tlen + t;
     float* sB = sm;
     float* sC = sm + (size_t)h * n;
     float* sds = sC + (size_t)h * n;
     for (int hh = threadIdx.x; hh < h; hh += 256) sds[hh] = -u_of(dt, lam, row * h + hh, t, Tlen, h) * dyx[row * h + hh];
-    for (int e = threadIdx.x; e < h * half; e += 256) {
-        const int hh = e / half, m = e - hh * half;
+    for (int e = threadIdx.x; e < h * upr; e += 256) {
+        const int hh = e / upr, m = (e - hh * upr) * V;
         const int gg = hh / hpg;
-        float s, c;
-        sincos_reduced(cum[row * h * half + e], &s, &c);
+        float b1[V], b2[V], c1[V], c2[V], db1[V], db2[V], dc1[V], dc2[V];
         const size_t ib = (row * g + gg) * n + m;
-        const float b1 = to_f(B[ib]), b2 = to_f(B[ib + half]);
-        const float c1 = to_f(C[ib]), c2 = to_f(C[ib + half]);
+        load_vec<T, V>(B + ib, b1);
+        load_vec<T, V>(B + ib + half, b2);
+        load_vec<T, V>(C + ib, c1);
+        load_vec<T, V>(C + ib + half, c2);
         const size_t o = (row * h + hh) * n + m;
-        const float db1 = to_f(dBr[o]), db2 = to_f(dBr[o + half]);
-        const float dc1 = to_f(dCr[o]), dc2 = to_f(dCr[o + half]);
-        const float ob1 = b1 * c - b2 * s, ob2 = b1 * s + b2 * c;
-        const float oc1 = c1 * c - c2 * s, oc2 = c1 * s + c2 * c;
-        dcum[row * h * half + e] = (-db1 * ob2 + db2 * ob1) + (-dc1 * oc2 + dc2 * oc1);
-        sB[hh * n + m] = c * db1 + s * db2;
-        sB[hh * n + m + half] = -s * db1 + c * db2;
-        sC[hh * n + m] = c * dc1 + s * dc2;
-        sC[hh * n + m + half] = -s * dc1 + c * dc2;
+        load_vec<T, V>(dBr + o, db1);
+        load_vec<T, V>(dBr + o + half, db2);
+        load_vec<T, V>(dCr + o, dc1);
+        load_vec<T, V>(dCr + o + half, dc2);
+        const float* cp = cum + (row * h + hh) * half + m;
+        float* dp = dcum + (row * h + hh) * half + m;
+#pragma unroll
+        for (int q = 0; q < V; ++q) {
+            float s, c;
+            sincos_reduced(cp[q], &s, &c);
+            const float ob1 = b1[q] * c - b2[q] * s, ob2 = b1[q] * s + b2[q] * c;
+            const float oc1 = c1[q] * c - c2[q] * s, oc2 = c1[q] * s + c2[q] * c;
+            dp[q] = (-db1[q] * ob2 + db2[q] * ob1) + (-dc1[q] * oc2 + dc2[q] * oc1);
+            sB[hh * n + m + q] = c * db1[q] + s * db2[q];
+            sB[hh * n + m + q + half] = -s * db1[q] + c * db2[q];
+            sC[hh * n + m + q] = c * dc1[q] + s * dc2[q];
+            sC[hh * n + m + q + half] = -s * dc1[q] + c * dc2[q];
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < g * n; e += 256) {
@@ -183,49 +230,65 @@ __global__ void __launch_bounds__(256) bc_dot_kernel(const T* __restrict__ B, co
     if (lane == 0) sdot[w] = a;
 }
 
-template <class T>
+// The three kernels below give TPR = 2^k <= 32 threads to one (b,t,h) row; each thread moves V elements per
+// step (16 bytes when V > 1), and row sums are reduced by shuffles inside the TPR group.
+template <class T, int V, int TPR>
 __global__ void __launch_bounds__(256) xw_fwd_kernel(const T* __restrict__ x, const float* __restrict__ dt,
                                                      const float* __restrict__ lam, const float* __restrict__ A_head,
                                                      T* __restrict__ xw, float* __restrict__ dA, int Tlen, int h, int p,
                                                      size_t rows) {
-    const size_t w = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // (b, t, h) flattened
+    const size_t w = ((size_t)blockIdx.x * 256 + threadIdx.x) / TPR;  // (b, t, h) flattened
     if (w >= rows) return;
-    const int lane = threadIdx.x & 31;
+    const int sub = threadIdx.x % TPR;
     const int hh = (int)(w % h);
     const int t = (int)((w / h) % Tlen);
     const float d = dt[w];
     const float wt = lam[w] * d + u_of(dt, lam, w, t, Tlen, h);
-    if (lane == 0) dA[w] = d * A_head[hh];
-    for (int pp = lane; pp < p; pp += 32) xw[w * p + pp] = from_f<T>(to_f(x[w * p + pp]) * wt);
+    if (sub == 0) dA[w] = d * A_head[hh];
+    for (int pp = sub * V; pp < p; pp += TPR * V) {
+        float f[V];
+        load_vec<T, V>(x + w * p + pp, f);
+#pragma unroll
+        for (int q = 0; q < V; ++q) f[q] *= wt;
+        store_vec<T, V>(xw + w * p + pp, f);
+    }
 }
 
 // y = y_scan + (D - u s) x   (y may be y_scan itself)
-template <class T>
+template <class T, int V, int TPR>
 __global__ void __launch_bounds__(256) skip_fwd_kernel(const T* y_scan, const T* __restrict__ x, const float* __restrict__ D,
                                                        const float* __restrict__ dt, const float* __restrict__ lam,
                                                        const float* __restrict__ sdot, T* y, int Tlen, int h, int hpg, int p,
                                                        size_t rows) {
-    const size_t w = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const size_t w = ((size_t)blockIdx.x * 256 + threadIdx.x) / TPR;
     if (w >= rows) return;
-    const int lane = threadIdx.x & 31;
+    const int sub = threadIdx.x % TPR;
     const int hh = (int)(w % h);
     const int t = (int)((w / h) % Tlen);
     const int g = h / hpg;
     const float coef = (D ? D[hh] : 0.f) - u_of(dt, lam, w, t, Tlen, h) * sdot[(w / h) * g + hh / hpg];
-    for (int pp = lane; pp < p; pp += 32) y[w * p + pp] = from_f<T>(to_f(y_scan[w * p + pp]) + coef * to_f(x[w * p + pp]));
+    for (int pp = sub * V; pp < p; pp += TPR * V) {
+        float a[V], f[V];
+        load_vec<T, V>(y_scan + w * p + pp, a);
+        load_vec<T, V>(x + w * p + pp, f);
+#pragma unroll
+        for (int q = 0; q < V; ++q) a[q] += coef * f[q];
+        store_vec<T, V>(y + w * p + pp, a);
+    }
 }
 
 // dx = dxw w + (D - u s) dy ;  dw = <dxw, x> ;  dyx = <dy, x>
-template <class T>
+template <class T, int V, int TPR>
 __global__ void __launch_bounds__(256) xw_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                                                      const T* __restrict__ dxw, const float* __restrict__ dt,
                                                      const float* __restrict__ lam, const float* __restrict__ D,
                                                      const float* __restrict__ sdot, T* __restrict__ dx,
                                                      float* __restrict__ dw, float* __restrict__ dyx, int Tlen, int h, int hpg,
                                                      int p, size_t rows) {
-    const size_t w = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (w >= rows) return;
-    const int lane = threadIdx.x & 31;
+    size_t w = ((size_t)blockIdx.x * 256 + threadIdx.x) / TPR;
+    const bool live = w < rows;
+    if (!live) w = rows - 1;  // keep the whole warp in the shuffles below
+    const int sub = threadIdx.x % TPR;
     const int hh = (int)(w % h);
     const int t = (int)((w / h) % Tlen);
     const int g = h / hpg;
@@ -233,19 +296,25 @@ __global__ void __launch_bounds__(256) xw_bwd_kernel(const T* __restrict__ x, co
     const float wt = lam[w] * dt[w] + u;
     const float coef = (D ? D[hh] : 0.f) - u * sdot[(w / h) * g + hh / hpg];
     float aw = 0.f, ay = 0.f;
-    for (int pp = lane; pp < p; pp += 32) {
-        const size_t o = w * p + pp;
-        const float xv = to_f(x[o]), dyv = to_f(dy[o]), g1 = to_f(dxw[o]);
-        dx[o] = from_f<T>(g1 * wt + coef * dyv);
-        aw += g1 * xv;
-        ay += dyv * xv;
+    for (int pp = sub * V; pp < p; pp += TPR * V) {
+        float xv[V], dyv[V], g1[V], o[V];
+        load_vec<T, V>(x + w * p + pp, xv);
+        load_vec<T, V>(dy + w * p + pp, dyv);
+        load_vec<T, V>(dxw + w * p + pp, g1);
+#pragma unroll
+        for (int q = 0; q < V; ++q) {
+            o[q] = g1[q] * wt + coef * dyv[q];
+            aw += g1[q] * xv[q];
+            ay += dyv[q] * xv[q];
+        }
+        if (live) store_vec<T, V>(dx + w * p + pp, o);
     }
 #pragma unroll
-    for (int of = 16; of > 0; of >>= 1) {
+    for (int of = TPR / 2; of > 0; of >>= 1) {
         aw += __shfl_xor_sync(0xffffffffu, aw, of);
         ay += __shfl_xor_sync(0xffffffffu, ay, of);
     }
-    if (lane == 0) {
+    if (live && sub == 0) {
         dw[w] = aw;
         dyx[w] = ay;
     }
