@@ -41,6 +41,28 @@ __device__ __forceinline__ void load_vec(const T* p, float (&f)[V]) {
         for (int q = 0; q < V; ++q) f[q] = to_f(e[q]);
     }
 }
+// V consecutive floats (V = 1, or a multiple of 4 at a 16-byte aligned address).
+template <int V>
+__device__ __forceinline__ void load_f32(const float* p, float (&f)[V]) {
+    if constexpr (V == 1) {
+        f[0] = *p;
+    } else {
+#pragma unroll
+        for (int q = 0; q < V; q += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(p + q);
+            f[q] = v.x; f[q + 1] = v.y; f[q + 2] = v.z; f[q + 3] = v.w;
+        }
+    }
+}
+template <int V>
+__device__ __forceinline__ void store_f32(float* p, const float (&f)[V]) {
+    if constexpr (V == 1) {
+        *p = f[0];
+    } else {
+#pragma unroll
+        for (int q = 0; q < V; q += 4) *reinterpret_cast<float4*>(p + q) = make_float4(f[q], f[q + 1], f[q + 2], f[q + 3]);
+    }
+}
 template <class T, int V>
 __device__ __forceinline__ void store_vec(T* p, const float (&f)[V]) {
     if constexpr (V == 1) {
@@ -122,9 +144,7 @@ __global__ void __launch_bounds__(256) rope_fwd_kernel(const T* __restrict__ B, 
         const int hh = e / upr, m = (e - hh * upr) * V;
         const int gg = hh / hpg;
         float ang[V], b1[V], b2[V], c1[V], c2[V], o1[V], o2[V];
-        const float* cp = cum + (row * h + hh) * half + m;
-#pragma unroll
-        for (int q = 0; q < V; ++q) ang[q] = cp[q];
+        load_f32<V>(cum + (row * h + hh) * half + m, ang);
         const size_t ib = (row * g + gg) * n + m;
         load_vec<T, V>(B + ib, b1);
         load_vec<T, V>(B + ib + half, b2);
@@ -183,20 +203,25 @@ __global__ void __launch_bounds__(256) rope_bwd_kernel(const T* __restrict__ B, 
         load_vec<T, V>(dBr + o + half, db2);
         load_vec<T, V>(dCr + o, dc1);
         load_vec<T, V>(dCr + o + half, dc2);
-        const float* cp = cum + (row * h + hh) * half + m;
-        float* dp = dcum + (row * h + hh) * half + m;
+        float ang[V], dth[V], ub1[V], ub2[V], uc1[V], uc2[V];
+        load_f32<V>(cum + (row * h + hh) * half + m, ang);
 #pragma unroll
         for (int q = 0; q < V; ++q) {
             float s, c;
-            sincos_reduced(cp[q], &s, &c);
+            sincos_reduced(ang[q], &s, &c);
             const float ob1 = b1[q] * c - b2[q] * s, ob2 = b1[q] * s + b2[q] * c;
             const float oc1 = c1[q] * c - c2[q] * s, oc2 = c1[q] * s + c2[q] * c;
-            dp[q] = (-db1[q] * ob2 + db2[q] * ob1) + (-dc1[q] * oc2 + dc2[q] * oc1);
-            sB[hh * n + m + q] = c * db1[q] + s * db2[q];
-            sB[hh * n + m + q + half] = -s * db1[q] + c * db2[q];
-            sC[hh * n + m + q] = c * dc1[q] + s * dc2[q];
-            sC[hh * n + m + q + half] = -s * dc1[q] + c * dc2[q];
+            dth[q] = (-db1[q] * ob2 + db2[q] * ob1) + (-dc1[q] * oc2 + dc2[q] * oc1);
+            ub1[q] = c * db1[q] + s * db2[q];
+            ub2[q] = -s * db1[q] + c * db2[q];
+            uc1[q] = c * dc1[q] + s * dc2[q];
+            uc2[q] = -s * dc1[q] + c * dc2[q];
         }
+        store_f32<V>(dcum + (row * h + hh) * half + m, dth);
+        store_f32<V>(sB + hh * n + m, ub1);
+        store_f32<V>(sB + hh * n + m + half, ub2);
+        store_f32<V>(sC + hh * n + m, uc1);
+        store_f32<V>(sC + hh * n + m + half, uc2);
     }
     __syncthreads();
     for (int e = threadIdx.x; e < g * n; e += 256) {
