@@ -73,7 +73,8 @@ struct DecayTileParams {
     const float* g;      // (2,b,h,T)
     const float* ddtx;   // (2,b,h,T)
     const float* dyx;    // (2,b,h,T) or null
-    const float* gS;     // (b,h,nt,8)
+    const float* gS;     // (b,h,nt,8) from the reverse walk
+    const float* gS2;    // (b,h,nt,8) from the backward tile kernel
     const float* dt;     // (b,T,h) or null (operator form)
     const float* A_head; // (h) or null
     float* ddt;          // (b,T,h) or null
@@ -110,8 +111,11 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
             if (P.dyx) yx += P.dyx[base + t] + P.dyx[half + base + t];
         }
         if (lane == 31) {
-            const float* q = P.gS + ((((size_t)bb * P.h + hh) * P.nt) + k) * 8;
-            v[3] += ((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]));
+            const size_t so = ((((size_t)bb * P.h + hh) * P.nt) + k) * 8;
+            const float* q = P.gS + so;
+            const float* r = P.gS2 + so;
+            v[3] += (((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]))) +
+                    (((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7])));
         }
         // suffix sums: inside each 32-lane segment by shuffles, then the totals of the later segments
         float tot[4];

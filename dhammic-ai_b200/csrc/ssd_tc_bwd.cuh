@@ -41,8 +41,8 @@ struct BwdParams {
     float* g;                      // (2,b,h,T) per column half: gradient w.r.t. the tile-cumulative log-decay
     float* ddtx;                   // (2,b,h,T) per column half: sum_p dX * x
     float* dyx;                    // (2,b,h,T) per column half: sum_p dy * x
-    float* gS;                     // (b,h,nt,8) per warp: terms that act through S = cum[127] of the tile; the
-                                   // reverse walk initialises it, this kernel adds to it
+    float* gS;                     // (b,h,nt,8) per warp: this kernel's terms that act through S = cum[127] of the
+                                   // tile (the reverse walk writes its own array of the same shape)
     int* status;
     int T, h, hpg, nt, b;
 };
@@ -258,6 +258,23 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             }
         }
         const float rowacc = rowacc2.x + rowacc2.y;
+        if (tid == CTL) tma_store_wait_read();  // the previous head's dx store has read sdX
+        tc_fence_before();
+        fence_async_smem();
+        __syncthreads();  // (A) G complete, S and dG read by everyone
+        if (tid == CTL) {
+            mbar_wait(&bar_hq, ph, &failed);  // H and Q of this head have landed
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)  // dX1 = G^T dY : A = G MN-major (M = j, K = i), B = dY MN-major
+                mma_ss(tX1, smem_desc(g0a + kk * 2048, PANEL, 1024), smem_desc(y0 + kk * 2048, PANEL, 1024), kIdescMM, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {  // dX2 = B Q^T : A = B K-major (K = n), B = Q^T [n][p] MN-major
+                const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
+                mma_ss(tX2, smem_desc(b0a + off, 16, 1024), smem_desc(q0a + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
+            }
+            mma_commit(&bar_m2);  // the row epilogue only needs dX1 and dX2
+        }
         {   // Xd = d dt x in place (A operand of dB += Xd Q); dYe = e dY as bf16 pairs in TMEM
             // row weights as bf16 pairs: one packed multiply per two elements
             uint32_t a[16];
@@ -278,22 +295,11 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             tmem_st16(tdG + lanes + hf * 64, a);
             tmem_st_wait();
         }
-        if (tid == CTL) tma_store_wait_read();  // the previous head's dx store has read sdX
         tc_fence_before();
         fence_async_smem();
-        __syncthreads();  // (B) G, Xd, dYe complete; H / Q read by everyone
+        __syncthreads();  // (B) Xd, dYe complete
         if (tid == CTL) {
-            mbar_wait(&bar_hq, ph, &failed);  // H and Q of this head have landed
             tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)  // dX1 = G^T dY : A = G MN-major (M = j, K = i), B = dY MN-major
-                mma_ss(tX1, smem_desc(g0a + kk * 2048, PANEL, 1024), smem_desc(y0 + kk * 2048, PANEL, 1024), kIdescMM, kk > 0);
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {  // dX2 = B Q^T : A = B K-major (K = n), B = Q^T [n][p] MN-major
-                const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                mma_ss(tX2, smem_desc(b0a + off, 16, 1024), smem_desc(q0a + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
-            }
-            mma_commit(&bar_m2);  // the row epilogue only needs dX1 and dX2
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // dC += dYe H : A in TMEM (K = p), B = H^T [n][p] K-major, N = 128
                 mma_ts(tdC, tdG + (kk >> 1) * 64 + (kk & 1) * 8, smem_desc(h0a + kk * 32, 16, 1024), kIdescKK128,
@@ -305,29 +311,35 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         }
         mbar_wait(&bar_m2, ph, &failed);
         tc_fence_after();
-        float ddt_acc = 0.f, st_acc = 0.f;
+        float ddt_acc, st_acc;
         {
+            // fp32 pairs throughout: e = dX1 + d dX2, dx = dt e + D dy, and the two row sums <e, x>, <dX2, x>
+            float2 ddt2 = make_float2(0.f, 0.f), st2 = make_float2(0.f, 0.f);
+            const float2 dj2 = make_float2(dj, dj), dt2 = make_float2(dtv, dtv), D2 = make_float2(Dh, Dh);
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t a[16], b2[16];
                 tmem_ld16(tX1 + lanes + hf * 32 + sub * 16, a);
                 tmem_ld16(tX2 + lanes + hf * 32 + sub * 16, b2);
                 tmem_ld_wait();
+                const float2* A2 = reinterpret_cast<const float2*>(a);
+                const float2* S2 = reinterpret_cast<const float2*>(b2);
                 uint32_t dxp[8];
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
-                    float2 fx = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xr[sub * 8 + q]));
-                    float2 fy = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&yr[sub * 8 + q]));
-                    const float s0v = __uint_as_float(b2[2 * q]), s1v = __uint_as_float(b2[2 * q + 1]);
-                    const float e0 = __uint_as_float(a[2 * q]) + dj * s0v;
-                    const float e1 = __uint_as_float(a[2 * q + 1]) + dj * s1v;
-                    ddt_acc += e0 * fx.x + e1 * fx.y;
-                    st_acc += s0v * fx.x + s1v * fx.y;
-                    dxp[q] = pack_bf16(e0 * dtv + Dh * fy.x, e1 * dtv + Dh * fy.y);
+                    const float2 fx = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xr[sub * 8 + q]));
+                    const float2 fy = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&yr[sub * 8 + q]));
+                    const float2 e = fma2(dj2, S2[q], A2[q]);
+                    ddt2 = fma2(e, fx, ddt2);
+                    st2 = fma2(S2[q], fx, st2);
+                    const float2 o = fma2(D2, fy, mul2(e, dt2));
+                    dxp[q] = pack_bf16(o.x, o.y);
                 }
                 *reinterpret_cast<uint4*>(sdX + sw128(row, hf * 4 + sub * 2)) = make_uint4(dxp[0], dxp[1], dxp[2], dxp[3]);
                 *reinterpret_cast<uint4*>(sdX + sw128(row, hf * 4 + sub * 2 + 1)) = make_uint4(dxp[4], dxp[5], dxp[6], dxp[7]);
             }
+            ddt_acc = ddt2.x + ddt2.y;
+            st_acc = st2.x + st2.y;
         }
         {
             // gradient w.r.t. the tile-cumulative log-decay of this row, one partial per column half; the
@@ -340,8 +352,8 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             float red = dj * dtv * st_acc;
 #pragma unroll
             for (int of = 16; of > 0; of >>= 1) red += __shfl_xor_sync(0xffffffffu, red, of);
-            // the reverse walk already left exp(S) <Q_k, H_k> (the inter-tile decay term) in this slot
-            if (lane == 0) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + warp] += red;
+            // a plain store: a read-modify-write here would put a global load in front of the block-wide barrier
+            if (lane == 0) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + warp] = red;
         }
         if (hl + 1 < hpg) publish_columns((hl + 1) & 1);
         tc_fence_before();

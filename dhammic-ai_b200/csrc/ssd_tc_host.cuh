@@ -38,7 +38,7 @@ inline bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t c
 }
 
 struct Ws {
-    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, rterm, gS, dAh_part, dD_part, total;
+    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, rterm, gS, gS2, dAh_part, dD_part, total;
 };
 
 inline Ws ws_layout(const Dims& d, int pass) {
@@ -65,6 +65,7 @@ inline Ws ws_layout(const Dims& d, int pass) {
         w.dyx = take(2 * bht);
         w.rterm = take(2 * bht);
         w.gS = take((size_t)d.b * d.h * (d.T / LT) * 8 * 4);
+        w.gS2 = take((size_t)d.b * d.h * (d.T / LT) * 8 * 4);
         w.dAh_part = take((size_t)d.b * (d.T / LT) * d.h * 4);
         w.dD_part = take((size_t)d.b * (d.T / LT) * d.h * 4);
     }
@@ -230,13 +231,13 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.mX = mX; P.mdY = mdY; P.mB = mB; P.mC = mC; P.mH = mH; P.mQ = mQ; P.mdX = mdX; P.mdB = mdB; P.mdC = mdC;
         P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
         P.dyx = (float*)(ws + w.dyx); P.rterm = (const float*)(ws + w.rterm); P.status = status; P.T = d.T; P.h = d.h;
-        P.hpg = d.hpg; P.nt = nt; P.b = d.b; P.gS = (float*)(ws + w.gS);
+        P.hpg = d.hpg; P.nt = nt; P.b = d.b; P.gS = (float*)(ws + w.gS2);
         SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 256, kBwdSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_walk");
     }
     {
         DecayTileParams P{};
-        P.g = (const float*)(ws + w.g); P.ddtx = (const float*)(ws + w.ddtx); P.gS = (const float*)(ws + w.gS);
+        P.g = (const float*)(ws + w.g); P.ddtx = (const float*)(ws + w.ddtx); P.gS = (const float*)(ws + w.gS); P.gS2 = (const float*)(ws + w.gS2);
         P.dyx = (a->dt && a->D) ? (const float*)(ws + w.dyx) : nullptr;
         P.dt = a->dt; P.A_head = a->A_head; P.ddt = a->ddt; P.da = a->cumsum_is_input ? nullptr : a->da;
         P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = P.dyx ? (float*)(ws + w.dD_part) : nullptr;

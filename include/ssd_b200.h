@@ -184,7 +184,7 @@ int ssd_b200_bwd(const ssd_b200_bwd_args *args, void *stream);
  *     exceeds the array is refused with SSD_B200_EWORKSPACE and a message naming both sizes.
  *   - Every GPU on which the library is loaded holds the array until the process exits.
  *   - The first call on each device looks the array's device address up (with that device
- *     current); make that first call outside any stream capture.
+ *     current).
  *   - All calls on a device share the one array.  It keeps whatever the previous call left; the
  *     kernels overwrite what they read and the one word that must start at zero is cleared on
  *     the stream at the start of each call.  Two calls that overlap on the GPU (different
