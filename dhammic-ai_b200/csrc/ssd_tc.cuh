@@ -64,15 +64,14 @@ __global__ void tile_cumsum_kernel(const float* __restrict__ cum, const float* _
 // ------------------------------------------------------------------------------------------
 // Decay gradient of the tensor-core backward, one block per (128-tile, 32 heads, batch).
 // Inputs in (b,h,T) layout (coalesced along t): the per-row gradients g w.r.t. the tile-cumulative
-// log-decay (two column-half partials), ddtx = sum_p dX x (two partials), dyx = sum_p dy x (two
-// partials), and gS, the terms that act through the tile's last row.  Within a tile
+// log-decay, ddtx = sum_p dX x, dyx = sum_p dy x, and gS / gS2, the terms that act through the tile's last row.  Within a tile
 //   dA[t] = sum_{t' >= t} g[t']      (a suffix sum, four 32-lane segments per warp and head)
 // and  ddt = ddtx + dA A_head,  dA_head += dA dt,  dD += dyx.  dt is read and ddt / da written in the
 // caller's (b,T,h) layout through a shared-memory transpose, so both sides are 128-byte rows.
 struct DecayTileParams {
-    const float* g;      // (2,b,h,T)
-    const float* ddtx;   // (2,b,h,T)
-    const float* dyx;    // (2,b,h,T) or null
+    const float* g;      // (b,h,T)
+    const float* ddtx;   // (b,h,T)
+    const float* dyx;    // (b,h,T) or null
     const float* gS;     // (b,h,nt,8) from the reverse walk
     const float* gS2;    // (b,h,nt,8) from the backward tile kernel
     const float* dt;     // (b,T,h) or null (operator form)
@@ -90,7 +89,6 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
     const int k = blockIdx.x, hg = blockIdx.y, bb = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h0 = hg * 32;
-    const size_t half = (size_t)P.b * P.h * P.T;
     const bool head_ok = h0 + lane < P.h;
     if (P.dt) {
         for (int t = warp; t < LT; t += 8)
@@ -106,9 +104,9 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
 #pragma unroll
         for (int s4 = 0; s4 < 4; ++s4) {
             const int t = s4 * 32 + lane;
-            v[s4] = P.g[base + t] + P.g[half + base + t];
-            dx[s4] = P.ddtx[base + t] + P.ddtx[half + base + t];
-            if (P.dyx) yx += P.dyx[base + t] + P.dyx[half + base + t];
+            v[s4] = P.g[base + t];
+            dx[s4] = P.ddtx[base + t];
+            if (P.dyx) yx += P.dyx[base + t];
         }
         if (lane == 31) {
             const size_t so = ((((size_t)bb * P.h + hh) * P.nt) + k) * 8;

@@ -11,9 +11,17 @@
 //   rows      dx = dt (dX1 + d dX2) + D dy,  and the decay-gradient terms of the row
 // and once per group, after the heads:  dC += (sum_h dS_h) B,  dB += (sum_h dS_h)^T C.
 //
-// 256 threads: thread = (row, column half); thread 0 (row 0, whose causal row is the shortest) also
-// issues every TMA load and tcgen05.mma at the block-wide synchronisation points.  x / dy tiles are
-// double-buffered across heads; H / Q are reloaded as soon as phase 2 completes.
+// 512 threads: thread = (row, column quarter).  TMEM lanes are tied to warp % 4, so the rows 96-127, whose
+// causal rows are the longest, can only be read by the warps of one SM sub-partition; four warps per 32-row
+// block walk two 16-column steps each per head, and a quarter is exactly one 32-column block of the causal
+// mask (active iff quarter <= row block, diagonal iff equal).  Row 0 of the last quarter, whose mask work is
+// all zeros, also issues every TMA copy and tcgen05.mma.  Per head:
+//   S, dG -> mask loop (G -> smem, dS summed over heads in registers) -> [barrier A] -> dX1, dX2 issued;
+//   meanwhile Xd = d dt x in place and dYe = e dY -> TMEM -> [mbarrier B, control only] -> dC, dB products
+//   issued -> row epilogue on dX1, dX2 -> [barrier C] -> S, dG of the next head issued, dx stored.
+// x / dy tiles are double-buffered across heads; H / Q are reloaded as soon as the dC / dB products complete.
+// The per-row sums (gradient of the tile-cumulative log-decay, <dX, x>, <dy, x>) are summed over the four
+// quarters in shared memory and leave the kernel as one array each.
 #pragma once
 
 namespace ssd {
@@ -38,22 +46,21 @@ struct BwdParams {
     const float* dtT;              // (b,h,T) or null
     const float* D;                // (h) or null
     const float* rterm;            // (2,b,h,T) state part of d/dcum from the reverse walk
-    float* g;                      // (2,b,h,T) per column half: gradient w.r.t. the tile-cumulative log-decay
-    float* ddtx;                   // (2,b,h,T) per column half: sum_p dX * x
-    float* dyx;                    // (2,b,h,T) per column half: sum_p dy * x
-    float* gS;                     // (b,h,nt,8) per warp: this kernel's terms that act through S = cum[127] of the
+    float* g;                      // (b,h,T) gradient w.r.t. the tile-cumulative log-decay
+    float* ddtx;                   // (b,h,T) sum_p dX * x
+    float* dyx;                    // (b,h,T) sum_p dy * x
+    float* gS;                     // (b,h,nt,8): this kernel's terms that act through S = cum[127] of the
                                    // tile (the reverse walk writes its own array of the same shape)
     int* status;
     int T, h, hpg, nt, b;
 };
 
 
-constexpr size_t kBwdSmem = 13 * PANEL + 6 * LT * 4 + 1024;
+// 13 operand panels | scum2, sfL, sdt [2][128] | row partials [3][4][128] | warp partials [16] | alignment slack
+constexpr size_t kBwdSmem = 13 * PANEL + 6 * LT * 4 + 12 * LT * 4 + 64 + 1024;
 
-__global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant__ BwdParams P) {
+__global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant__ BwdParams P) {
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment by an offset on the __shared__ array itself, so that every access below stays a
-    // shared-memory instruction (a pointer rebuilt from an integer would be a generic-address access)
     uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sC = sm;                  // 2 panels [pos][n]
     uint8_t* sB = sC + 2 * PANEL;      // 2 panels [pos][n]
@@ -65,7 +72,9 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     float* scum2 = reinterpret_cast<float*>(sdX + PANEL);  // [2][128] each:
     float* sfL = scum2 + 2 * LT;       //   2^(cend - c_j)
     float* sdt = sfL + 2 * LT;         //   dt_j
-    __shared__ uint64_t bar_cb, bar_xy[2], bar_hq, bar_m1, bar_m2, bar_m2b, bar_m3;
+    float* sred = sdt + 2 * LT;        // [3][4][128]: per-quarter partials of g, ddtx, dyx of the current head
+    float* swred = sred + 12 * LT;     // [16]: per-warp partials of the S-borne term
+    __shared__ uint64_t bar_cb, bar_xy[2], bar_hq, bar_m1, bar_m2, bar_m2b, bar_m3, bar_b;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
 
@@ -73,10 +82,11 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     const int k = blockIdx.x, gg = blockIdx.y, bb = blockIdx.z;
     const int row0 = bb * P.T + k * LT;
     const int hpg = P.hpg;
-    const int row = tid & 127, hf = tid >> 7;
-    const int rowblk = row & ~31;
-    // control thread: lane 0 of warp 4 (rows 0-31, second column half), whose mask work is all zeros
-    constexpr int CTL = 128;
+    const int row = tid & 127, qc = tid >> 7;  // column quarter: S / dG columns [32 qc, 32 qc + 32), p columns [16 qc, +16)
+    const int rb = row >> 5;                   // row block, warp-uniform
+    const bool active = qc <= rb, diag = qc == rb;
+    // control thread: row 0 of the last quarter, whose mask work is all zeros
+    constexpr int CTL = 384;
 
     if (tid == 0) {
         failed = 0;
@@ -88,6 +98,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         mbar_init(&bar_m2, 1);
         mbar_init(&bar_m2b, 1);
         mbar_init(&bar_m3, 1);
+        mbar_init(&bar_b, 512);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -113,10 +124,9 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     // written before the last block-wide barrier of head hl
     float c_n = P.tcum[pos_of(0) + row], cend_n = P.tcum[pos_of(0) + (row | 31)];
     float dt_n = P.dtT ? P.dtT[pos_of(0) + row] : 1.f;
-    float r0_n = P.rterm[pos_of(0) + row], r1_n = P.rterm[bhT + pos_of(0) + row];
     float D_n = P.D ? P.D[gg * hpg] : 0.f;
     auto publish_columns = [&](int buf) {
-        if (hf == 0) {
+        if (qc == 0) {
             scum2[buf * LT + row] = c_n;
             sfL[buf * LT + row] = exp2f(cend_n - c_n);
             sdt[buf * LT + row] = dt_n;
@@ -136,9 +146,8 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         load_hq(0);
     }
     const uint32_t tm = tmem_slot;
-    // phase 1: S [0,128) dG [128,256); phase 2 aliases: dX1 [0,64) dX2 [64,128); dYe (bf16 pairs, 16 columns
-    // per column half) at [128,144) and [192,208), i.e. inside the dG columns the writing thread itself read;
-    // persistent over heads: dC [256,384) dB [384,512)
+    // phase 1: S [0,128) dG [128,256); after the mask loop (barrier A) dX1 [0,64) and dX2 [64,128) take the S
+    // columns and dYe (bf16 pairs) the dG columns [128,160); persistent over heads: dC [256,384) dB [384,512)
     const uint32_t tS = tm, tdG = tm + 128, tX1 = tm, tX2 = tm + 64, tdC = tm + 256, tdB = tm + 384;
     const uint32_t lanes = lane_base(warp);
     const uint32_t c0a = smem_u32(sC), b0a = smem_u32(sB), g0a = smem_u32(sG), h0a = smem_u32(sH), q0a = smem_u32(sQ);
@@ -155,9 +164,9 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         mma_commit(&bar_m1);
     };
 
-    float2 dS2[32];  // sum over heads of dS for this thread's 64 columns, as fp32 pairs
+    float2 dS2[16];  // sum over heads of dS for this thread's 32 columns, as fp32 pairs
 #pragma unroll
-    for (int q = 0; q < 32; ++q) dS2[q] = make_float2(0.f, 0.f);
+    for (int q = 0; q < 16; ++q) dS2[q] = make_float2(0.f, 0.f);
     mbar_wait(&bar_cb, 0, &failed);
     if (tid == CTL) {
         mbar_wait(&bar_xy[0], 0, &failed);
@@ -165,34 +174,39 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         issue_phase1(0);
         if (hpg > 1) load_xy(1);
     }
+    // G panel and 16-byte chunk of this thread's two 16-column steps
+    uint8_t* sGq = sG + (qc >> 1) * PANEL;
+    const int gch = (qc & 1) * 4;
 
     for (int hl = 0; hl < hpg; ++hl) {
         const int hh = gg * hpg + hl, xb = hl & 1, buf = hl & 1;
         const uint32_t ph = hl & 1;
         const size_t tpos = pos_of(hl) + row;
-        const float c_i = c_n, dtv = dt_n, rt0 = r0_n, rt1 = r1_n, Dh = D_n;
+        const float c_i = c_n, dtv = dt_n, Dh = D_n;
         if (hl + 1 < hpg) {
             const size_t o = pos_of(hl + 1);
             c_n = P.tcum[o + row];
             cend_n = P.tcum[o + (row | 31)];
             dt_n = P.dtT ? P.dtT[o + row] : 1.f;
-            r0_n = P.rterm[o + row];
-            r1_n = P.rterm[bhT + o + row];
             D_n = P.D ? P.D[hh + 1] : 0.f;
+        }
+        // state part of the gradient of this row (from the reverse walk): needed once per row, after the barrier (C)
+        float rt0 = 0.f, rt1 = 0.f;  // loaded here, first used after the barrier (C): no stall on the loads
+        if (qc == 0) {
+            rt0 = P.rterm[tpos];
+            rt1 = P.rterm[bhT + tpos];
         }
         mbar_wait(&bar_xy[xb], (hl >> 1) & 1, &failed);
         uint8_t* sX = sXY + (2 * xb) * PANEL;
         uint8_t* sdY = sX + PANEL;
         const uint32_t x0 = smem_u32(sX), y0 = x0 + PANEL;  // phase 1 of this head was issued one step earlier
         const float Sk = scum2[buf * LT + LT - 1];
-        // this thread's half rows of x and dy (raw)
-        uint32_t xr[16], yr[16];
+        // this thread's quarter row of x (raw); dy stays raw in shared memory and is re-read where needed
+        uint32_t xr[8];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-            uint4 v = *reinterpret_cast<const uint4*>(sX + sw128(row, hf * 4 + ch));
-            uint4 u = *reinterpret_cast<const uint4*>(sdY + sw128(row, hf * 4 + ch));
+        for (int ch = 0; ch < 2; ++ch) {
+            uint4 v = *reinterpret_cast<const uint4*>(sX + sw128(row, qc * 2 + ch));
             xr[ch * 4 + 0] = v.x; xr[ch * 4 + 1] = v.y; xr[ch * 4 + 2] = v.z; xr[ch * 4 + 3] = v.w;
-            yr[ch * 4 + 0] = u.x; yr[ch * 4 + 1] = u.y; yr[ch * 4 + 2] = u.z; yr[ch * 4 + 3] = u.w;
         }
         float dyx = 0.f;  // sum_p dy[i,p] x[i,p] is the diagonal entry of dG = dY x^T: picked up in the mask loop
         const float ei = exp2f(c_i);
@@ -200,62 +214,51 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         mbar_wait(&bar_m1, ph, &failed);
         tc_fence_after();
         float2 rowacc2 = make_float2(0.f, 0.f);
-        {
-            // 16 columns at a time; the TMEM loads of the next 16 are in flight while these are processed
-            uint32_t rs[2][16], rg[2][16];
-            auto active = [&](int sub) { return ((hf * 64 + sub * 16) & ~31) <= rowblk; };
-            if (active(0)) {
-                tmem_ld16(tS + lanes + hf * 64, rs[0]);
-                tmem_ld16(tdG + lanes + hf * 64, rg[0]);
-            }
+        if (active) {
+            const float rf = exp2f(c_i - scum2[buf * LT + qc * 32 + 31]);
+            const float2 rf2 = make_float2(rf, rf);
 #pragma unroll
-            for (int sub = 0; sub < 4; ++sub) {
-                const int c0 = hf * 64 + sub * 16, cb = c0 & ~31;
+            for (int sub = 0; sub < 2; ++sub) {
+                const int c0 = qc * 32 + sub * 16;
+                uint32_t rs[16], rg[16];
+                tmem_ld16(tS + lanes + c0, rs);
+                tmem_ld16(tdG + lanes + c0, rg);
+                const float2* F2 = reinterpret_cast<const float2*>(sfL + buf * LT + c0);
+                const float2* T2 = reinterpret_cast<const float2*>(sdt + buf * LT + c0);
+                tmem_ld_wait();
+                // Everything in fp32 pairs (one instruction, two columns).  rowacc uses the bf16-rounded G that
+                // the dX product reads (unpacked from the packed pair), so that the row and column sums of
+                // dG o G cancel exactly.
+                const float2* S2 = reinterpret_cast<const float2*>(rs);
+                const float2* G2 = reinterpret_cast<const float2*>(rg);
                 uint32_t gp[8];
-                if (!active(sub)) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) gp[q] = 0u;
-                } else {
-                    const float rf = exp2f(c_i - scum2[buf * LT + cb + 31]);
-                    const float4* fl4 = reinterpret_cast<const float4*>(sfL + buf * LT + c0);
-                    const float4* dt4 = reinterpret_cast<const float4*>(sdt + buf * LT + c0);
-                    tmem_ld_wait();
-                    if (sub < 3 && active(sub + 1)) {
-                        tmem_ld16(tS + lanes + c0 + 16, rs[(sub + 1) & 1]);
-                        tmem_ld16(tdG + lanes + c0 + 16, rg[(sub + 1) & 1]);
+                for (int q2 = 0; q2 < 8; ++q2) {
+                    float2 l = mul2(rf2, F2[q2]);
+                    if (diag) {  // columns beyond the row are masked
+                        if (c0 + 2 * q2 > row) l.x = 0.f;
+                        if (c0 + 2 * q2 + 1 > row) l.y = 0.f;
                     }
-                    // Everything in fp32 pairs (one instruction, two columns).  rowacc uses the bf16-rounded G that
-                    // the dX product reads (unpacked from the packed pair), so that the row and column sums of
-                    // dG o G cancel exactly.
-                    const float2* S2 = reinterpret_cast<const float2*>(rs[sub & 1]);
-                    const float2* G2 = reinterpret_cast<const float2*>(rg[sub & 1]);
-                    const float2* F2 = reinterpret_cast<const float2*>(fl4);
-                    const float2* T2 = reinterpret_cast<const float2*>(dt4);
-                    const float2 rf2 = make_float2(rf, rf);
-                    const bool diag = (cb == rowblk);
-#pragma unroll
-                    for (int q2 = 0; q2 < 8; ++q2) {
-                        float2 l = mul2(rf2, F2[q2]);
-                        if (diag) {  // columns beyond the row are masked
-                            if (c0 + 2 * q2 > row) l.x = 0.f;
-                            if (c0 + 2 * q2 + 1 > row) l.y = 0.f;
-                        }
-                        const float2 dg = mul2(G2[q2], T2[q2]);
-                        const float2 gl = mul2(S2[q2], l);
-                        const uint32_t pk = pack_bf16(gl.x, gl.y);
-                        dS2[sub * 8 + q2] = fma2(dg, l, dS2[sub * 8 + q2]);
-                        rowacc2 = fma2(dg, make_float2(__uint_as_float(pk << 16), __uint_as_float(pk & 0xffff0000u)), rowacc2);
-                        gp[q2] = pk;
-                    }
-                    if (diag) {
-#pragma unroll
-                        for (int q = 0; q < 16; ++q)
-                            if (c0 + q == row) dyx = __uint_as_float(rg[sub & 1][q]);
-                    }
+                    const float2 dg = mul2(G2[q2], T2[q2]);
+                    const float2 gl = mul2(S2[q2], l);
+                    const uint32_t pk = pack_bf16(gl.x, gl.y);
+                    dS2[sub * 8 + q2] = fma2(dg, l, dS2[sub * 8 + q2]);
+                    rowacc2 = fma2(dg, make_float2(__uint_as_float(pk << 16), __uint_as_float(pk & 0xffff0000u)), rowacc2);
+                    gp[q2] = pk;
                 }
-                *reinterpret_cast<uint4*>(sG + hf * PANEL + sw128(row, sub * 2)) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
-                *reinterpret_cast<uint4*>(sG + hf * PANEL + sw128(row, sub * 2 + 1)) = make_uint4(gp[4], gp[5], gp[6], gp[7]);
+                if (diag) {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        if (c0 + q == row) dyx = __uint_as_float(rg[q]);
+                }
+                *reinterpret_cast<uint4*>(sGq + sw128(row, gch + sub * 2)) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
+                *reinterpret_cast<uint4*>(sGq + sw128(row, gch + sub * 2 + 1)) = make_uint4(gp[4], gp[5], gp[6], gp[7]);
             }
+        } else if (hl == 0) {
+            // above the diagonal G is zero for every head: written once (the G panels are staging only after the loop)
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) *reinterpret_cast<uint4*>(sGq + sw128(row, gch + ch)) = z;
         }
         const float rowacc = rowacc2.x + rowacc2.y;
         if (tid == CTL) tma_store_wait_read();  // the previous head's dx store has read sdX
@@ -276,34 +279,35 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             mma_commit(&bar_m2);  // the row epilogue only needs dX1 and dX2
         }
         {   // Xd = d dt x in place (A operand of dB += Xd Q); dYe = e dY as bf16 pairs in TMEM
-            // row weights as bf16 pairs: one packed multiply per two elements
-            uint32_t a[16];
+            uint32_t a[8];
             const __nv_bfloat162 wx2 = __float2bfloat162_rn(dj * dtv), we2 = __float2bfloat162_rn(ei);
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-                uint4 v;
-                uint32_t* u = reinterpret_cast<uint32_t*>(&v);
+            for (int ch = 0; ch < 2; ++ch) {
+                uint4 v, u = *reinterpret_cast<const uint4*>(sdY + sw128(row, qc * 2 + ch));
+                uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+                uint32_t* uu = reinterpret_cast<uint32_t*>(&u);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     __nv_bfloat162 rx = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&xr[ch * 4 + q]), wx2);
-                    __nv_bfloat162 ry = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&yr[ch * 4 + q]), we2);
-                    u[q] = *reinterpret_cast<uint32_t*>(&rx);
+                    __nv_bfloat162 ry = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&uu[q]), we2);
+                    vv[q] = *reinterpret_cast<uint32_t*>(&rx);
                     a[ch * 4 + q] = *reinterpret_cast<uint32_t*>(&ry);
                 }
-                *reinterpret_cast<uint4*>(sX + sw128(row, hf * 4 + ch)) = v;
+                *reinterpret_cast<uint4*>(sX + sw128(row, qc * 2 + ch)) = v;
             }
-            tmem_st16(tdG + lanes + hf * 64, a);
+            tmem_st8(tdG + lanes + qc * 8, a);
             tmem_st_wait();
         }
+        // (B) Xd, dYe complete: only the control thread waits for it, the others go on to the row epilogue
         tc_fence_before();
         fence_async_smem();
-        __syncthreads();  // (B) Xd, dYe complete
+        mbar_arrive(&bar_b);
         if (tid == CTL) {
+            mbar_wait(&bar_b, ph, &failed);
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // dC += dYe H : A in TMEM (K = p), B = H^T [n][p] K-major, N = 128
-                mma_ts(tdC, tdG + (kk >> 1) * 64 + (kk & 1) * 8, smem_desc(h0a + kk * 32, 16, 1024), kIdescKK128,
-                       hl > 0 || kk > 0);
+                mma_ts(tdC, tdG + kk * 8, smem_desc(h0a + kk * 32, 16, 1024), kIdescKK128, hl > 0 || kk > 0);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)  // dB += Xd Q : A = Xd K-major (in place of x), B = Q^T [n][p] K-major
                 mma_ss(tdB, smem_desc(x0 + kk * 32, 16, 1024), smem_desc(q0a + kk * 32, 16, 1024), kIdescKK128, hl > 0 || kk > 0);
@@ -316,61 +320,70 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
             // fp32 pairs throughout: e = dX1 + d dX2, dx = dt e + D dy, and the two row sums <e, x>, <dX2, x>
             float2 ddt2 = make_float2(0.f, 0.f), st2 = make_float2(0.f, 0.f);
             const float2 dj2 = make_float2(dj, dj), dt2 = make_float2(dtv, dtv), D2 = make_float2(Dh, Dh);
+            uint32_t a[16], b2[16], yr[8];
+            tmem_ld16(tX1 + lanes + qc * 16, a);
+            tmem_ld16(tX2 + lanes + qc * 16, b2);
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-                uint32_t a[16], b2[16];
-                tmem_ld16(tX1 + lanes + hf * 32 + sub * 16, a);
-                tmem_ld16(tX2 + lanes + hf * 32 + sub * 16, b2);
-                tmem_ld_wait();
-                const float2* A2 = reinterpret_cast<const float2*>(a);
-                const float2* S2 = reinterpret_cast<const float2*>(b2);
-                uint32_t dxp[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const float2 fx = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xr[sub * 8 + q]));
-                    const float2 fy = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&yr[sub * 8 + q]));
-                    const float2 e = fma2(dj2, S2[q], A2[q]);
-                    ddt2 = fma2(e, fx, ddt2);
-                    st2 = fma2(S2[q], fx, st2);
-                    const float2 o = fma2(D2, fy, mul2(e, dt2));
-                    dxp[q] = pack_bf16(o.x, o.y);
-                }
-                *reinterpret_cast<uint4*>(sdX + sw128(row, hf * 4 + sub * 2)) = make_uint4(dxp[0], dxp[1], dxp[2], dxp[3]);
-                *reinterpret_cast<uint4*>(sdX + sw128(row, hf * 4 + sub * 2 + 1)) = make_uint4(dxp[4], dxp[5], dxp[6], dxp[7]);
+            for (int ch = 0; ch < 2; ++ch) {
+                uint4 u = *reinterpret_cast<const uint4*>(sdY + sw128(row, qc * 2 + ch));
+                yr[ch * 4 + 0] = u.x; yr[ch * 4 + 1] = u.y; yr[ch * 4 + 2] = u.z; yr[ch * 4 + 3] = u.w;
             }
+            tmem_ld_wait();
+            const float2* A2 = reinterpret_cast<const float2*>(a);
+            const float2* S2 = reinterpret_cast<const float2*>(b2);
+            uint32_t dxp[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float2 fx = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xr[q]));
+                const float2 fy = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&yr[q]));
+                const float2 e = fma2(dj2, S2[q], A2[q]);
+                ddt2 = fma2(e, fx, ddt2);
+                st2 = fma2(S2[q], fx, st2);
+                const float2 o = fma2(D2, fy, mul2(e, dt2));
+                dxp[q] = pack_bf16(o.x, o.y);
+            }
+            *reinterpret_cast<uint4*>(sdX + sw128(row, qc * 2)) = make_uint4(dxp[0], dxp[1], dxp[2], dxp[3]);
+            *reinterpret_cast<uint4*>(sdX + sw128(row, qc * 2 + 1)) = make_uint4(dxp[4], dxp[5], dxp[6], dxp[7]);
             ddt_acc = ddt2.x + ddt2.y;
             st_acc = st2.x + st2.y;
         }
         {
-            // gradient w.r.t. the tile-cumulative log-decay of this row, one partial per column half; the
-            // terms that act through S = cum[127] (state weights d_j and the inter-tile decay) are summed
-            // per warp and added to the tile's last row by the decay kernel, in a fixed order
-            const size_t o = (size_t)hf * bhT + tpos;
-            P.g[o] = rowacc - dtv * ddt_acc + (hf == 0 ? rt0 + rt1 : 0.f);
-            P.ddtx[o] = ddt_acc;
-            P.dyx[o] = dyx;
+            // gradient w.r.t. the tile-cumulative log-decay of this row, one partial per quarter, summed after the
+            // barrier; the terms that act through S = cum[127] (state weights d_j) are summed per warp
+            sred[(0 * 4 + qc) * LT + row] = rowacc - dtv * ddt_acc;
+            sred[(1 * 4 + qc) * LT + row] = ddt_acc;
+            sred[(2 * 4 + qc) * LT + row] = dyx;
             float red = dj * dtv * st_acc;
 #pragma unroll
             for (int of = 16; of > 0; of >>= 1) red += __shfl_xor_sync(0xffffffffu, red, of);
-            // a plain store: a read-modify-write here would put a global load in front of the block-wide barrier
-            if (lane == 0) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + warp] = red;
+            if (lane == 0) swred[warp] = red;
         }
         if (hl + 1 < hpg) publish_columns((hl + 1) & 1);
         tc_fence_before();
         fence_async_smem();
-        __syncthreads();  // (C) dx staged, TMEM reads done, next head's column arrays visible
+        __syncthreads();  // (C) dx staged, TMEM reads done, partial sums and next head's column arrays visible
+        if (qc == 0) {
+            // fixed order: deterministic
+            P.g[tpos] = ((sred[0 * LT + row] + sred[1 * LT + row]) + (sred[2 * LT + row] + sred[3 * LT + row])) + (rt0 + rt1);
+            P.ddtx[tpos] = (sred[4 * LT + row] + sred[5 * LT + row]) + (sred[6 * LT + row] + sred[7 * LT + row]);
+            P.dyx[tpos] = (sred[8 * LT + row] + sred[9 * LT + row]) + (sred[10 * LT + row] + sred[11 * LT + row]);
+            if (row < 8) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + row] = swred[row] + swred[row + 8];
+        }
         if (tid == CTL) {
-            tma_store_2d(&P.mdX, sdX, hh * HP, row0);
-            tma_store_commit();
-            mbar_wait(&bar_m2b, ph, &failed);  // dC / dB products of this head done
+            // the products of the next head first (every thread waits for them), the stores and loads after
+            mbar_wait(&bar_m2b, ph, &failed);  // dC / dB products of this head done: dYe, H, Q, Xd are free
             if (hl + 1 < hpg) {
-                load_hq(hl + 1);
                 // everyone has read dX1 / dX2, so S and dG of the next head may overwrite them now; its x / dy
-                // tiles were prefetched during this head, and this head's buffer is free for head hl + 2
+                // tiles were prefetched during this head
                 mbar_wait(&bar_xy[xb ^ 1], ((hl + 1) >> 1) & 1, &failed);
                 tc_fence_after();
                 issue_phase1(hl + 1);
-                if (hl + 2 < hpg) load_xy(hl + 2);
+            }
+            tma_store_2d(&P.mdX, sdX, hh * HP, row0);
+            tma_store_commit();
+            if (hl + 1 < hpg) {
+                load_hq(hl + 1);
+                if (hl + 2 < hpg) load_xy(hl + 2);  // this head's x / dy buffer is free
             }
         }
     }
@@ -379,14 +392,11 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     {
         float v[32];
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-#pragma unroll
-            for (int q = 0; q < 16; ++q) {
-                v[2 * q] = dS2[blk * 16 + q].x;
-                v[2 * q + 1] = dS2[blk * 16 + q].y;
-            }
-            store_half_row(sXY + hf * PANEL, row, blk * 4, v);
+        for (int q = 0; q < 16; ++q) {
+            v[2 * q] = dS2[q].x;
+            v[2 * q + 1] = dS2[q].y;
         }
+        store_half_row(sXY + (qc >> 1) * PANEL, row, gch, v);
     }
     tc_fence_before();
     fence_async_smem();
@@ -406,17 +416,18 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
     }
     mbar_wait(&bar_m3, 0, &failed);
     tc_fence_after();
-#pragma unroll
-    for (int blk = 0; blk < 2; ++blk) {
+    {
         uint32_t a[32], b2[32];
-        tmem_ld32(tdC + lanes + hf * 64 + blk * 32, a);
-        tmem_ld32(tdB + lanes + hf * 64 + blk * 32, b2);
+        tmem_ld32(tdC + lanes + qc * 32, a);
+        tmem_ld32(tdB + lanes + qc * 32, b2);
         tmem_ld_wait();
-        float va[32], vb[32];
+        float va[32];
 #pragma unroll
-        for (int q = 0; q < 32; ++q) { va[q] = __uint_as_float(a[q]); vb[q] = __uint_as_float(b2[q]); }
-        store_half_row(sG + hf * PANEL, row, blk * 4, va);
-        store_half_row(sXY + (2 + hf) * PANEL, row, blk * 4, vb);
+        for (int q = 0; q < 32; ++q) va[q] = __uint_as_float(a[q]);
+        store_half_row(sG + (qc >> 1) * PANEL, row, gch, va);
+#pragma unroll
+        for (int q = 0; q < 32; ++q) va[q] = __uint_as_float(b2[q]);
+        store_half_row(sXY + (2 + (qc >> 1)) * PANEL, row, gch, va);
     }
     tc_fence_before();
     fence_async_smem();
@@ -427,7 +438,7 @@ __global__ void __launch_bounds__(256, 1) bwd_tile_kernel(const __grid_constant_
         tma_store_2d(&P.mdB, sXY + 2 * PANEL, gg * DN, row0);
         tma_store_2d(&P.mdB, sXY + 3 * PANEL, gg * DN + 64, row0);
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();  // shared memory must outlive the reads only; the writes complete with the kernel
         if (failed) atomicExch(P.status, 1);
     }
     __syncthreads();

@@ -60,9 +60,9 @@ inline Ws ws_layout(const Dims& d, int pass) {
         w.Qst = take(st);
         w.final_state = take(bhpn);
         w.dinit = take(bhpn);
-        w.g = take(2 * bht);
-        w.ddtx = take(2 * bht);
-        w.dyx = take(2 * bht);
+        w.g = take(bht);
+        w.ddtx = take(bht);
+        w.dyx = take(bht);
         w.rterm = take(2 * bht);
         w.gS = take((size_t)d.b * d.h * (d.T / LT) * 8 * 4);
         w.gS2 = take((size_t)d.b * d.h * (d.T / LT) * 8 * 4);
@@ -232,7 +232,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
         P.dyx = (float*)(ws + w.dyx); P.rterm = (const float*)(ws + w.rterm); P.status = status; P.T = d.T; P.h = d.h;
         P.hpg = d.hpg; P.nt = nt; P.b = d.b; P.gS = (float*)(ws + w.gS2);
-        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 256, kBwdSmem, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 512, kBwdSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_walk");
     }
     {
