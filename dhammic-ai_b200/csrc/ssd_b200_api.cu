@@ -359,10 +359,10 @@ int m3_fwd_impl(const ssd::Dims& d, const void* x, const float* dt, const float*
     dim3 gs(nseg, (E + 255) / 256, d.b);
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<T><<<gs, 256, 0, st>>>((const T*)ang, segsum, d.T, E));
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<T, float><<<gs, 256, 0, st>>>((const T*)ang, segsum, cum, d.T, E, 0, -1.f)));
-    if ((d.n / 2) % VecOf<T>::N == 0)
+    if (d.n % VecOf<T>::N == 0)
         SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_fwd_kernel<T, VecOf<T>::N><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n)));
     else
-        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_fwd_kernel<T, 1><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n)));
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_fwd_kernel<T, 2><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n)));
     const size_t grows = (size_t)d.b * d.T * d.g, rows = (size_t)d.b * d.T * d.h;
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, bc_dot_kernel<T><<<(unsigned)((grows + 7) / 8), 256, 0, st>>>((const T*)B, (const T*)C, sdot, d.n, grows));
     M3_ROW_DISPATCH(xw_fwd_kernel, (const T*)x, dt, lam, A_head, (T*)xw, dA, d.T, d.h, d.p, rows);
@@ -390,12 +390,12 @@ int m3_bwd_impl(const ssd::Dims& d, const void* x, const void* dy, const float* 
     const size_t rows = (size_t)d.b * d.T * d.h;
     M3_ROW_DISPATCH(xw_bwd_kernel, (const T*)x, (const T*)dy, (const T*)dxw, dt, lam, D, sdot, (T*)dx, dw, dyx, d.T, d.h, d.hpg, d.p, rows);
     const size_t sm = ((size_t)2 * d.h * d.n + d.h) * sizeof(float);
-    if ((d.n / 2) % VecOf<T>::N == 0) {
+    if (d.n % VecOf<T>::N == 0) {
         if (int rc = set_smem(rope_bwd_kernel<T, VecOf<T>::N>, sm, "rope_bwd")) return rc;
         SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, VecOf<T>::N><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n)));
     } else {
-        if (int rc = set_smem(rope_bwd_kernel<T, 1>, sm, "rope_bwd")) return rc;
-        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, 1><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n)));
+        if (int rc = set_smem(rope_bwd_kernel<T, 2>, sm, "rope_bwd")) return rc;
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, 2><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n)));
     }
     dim3 gs(nseg, (E + 255) / 256, d.b);
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<float><<<gs, 256, 0, st>>>(dcum, segsum, d.T, E));

@@ -13,7 +13,7 @@
 // one scan instead of two, and <Br, Cr> = <B, C> because both are rotated by the same angles.  Steps:
 //
 //   cum    = -cumsum_T(raw_angles)                                  (b,T,h,n/2)   scanT kernels
-//   Br, Cr = rope(B_group(h), cum), rope(C_group(h), cum)           (b,T,h,n)     rope_fwd_kernel
+//   Br, Cr = rope(B_group(h), cum), rope(C_group(h), cum)           (b,T,h,n)     rope_fwd_kernel (interleaved pairs)
 //   s      = <B, C> per group                                       (b,T,g)       bc_dot_kernel
 //   xw = x w,  a = dt A_head                                                      xw_fwd_kernel
 //   y  = y_scan + (D - u s) x                                                     skip_fwd_kernel
@@ -124,7 +124,9 @@ __global__ void __launch_bounds__(256) scanT_apply_kernel(const TI* __restrict__
 }
 
 // ------------------------------------------------------------------------------------------
-// Rotation.  One block per (position, batch); thread e <-> (head, pair index m).
+// Rotation of the interleaved pairs (v[2m], v[2m+1]) by angle[m] (the reference's convention,
+// src/kernels/rope.py:40-85).  One block per (position, batch); a thread takes V consecutive elements
+// (one 16-byte vector, V/2 pairs; V = 2 is the scalar fallback) of one head.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void sincos_reduced(float a, float* s, float* c) {
     // reduce to [-pi, pi] first: the fast sine / cosine are accurate there
@@ -133,35 +135,74 @@ __device__ __forceinline__ void sincos_reduced(float a, float* s, float* c) {
     __sincosf(r, s, c);
 }
 
+// N consecutive fp32 angles: 16-byte vectors when N is a multiple of 4 (the address is then 16-byte aligned)
+template <int N>
+__device__ __forceinline__ void load_angles(const float* p, float (&f)[N]) {
+    if constexpr (N % 4 == 0) {
+        load_f32<N>(p, f);
+    } else {
+#pragma unroll
+        for (int q = 0; q < N; ++q) f[q] = p[q];
+    }
+}
+template <int N>
+__device__ __forceinline__ void store_angles(float* p, const float (&f)[N]) {
+    if constexpr (N % 4 == 0) {
+        store_f32<N>(p, f);
+    } else {
+#pragma unroll
+        for (int q = 0; q < N; ++q) p[q] = f[q];
+    }
+}
+
+// V elements starting at p (V = 2: two scalar accesses; else one 16-byte vector)
+template <class T, int V>
+__device__ __forceinline__ void load_elems(const T* p, float (&f)[V]) {
+    if constexpr (V == 2) {
+        f[0] = to_f(p[0]);
+        f[1] = to_f(p[1]);
+    } else {
+        load_vec<T, V>(p, f);
+    }
+}
+template <class T, int V>
+__device__ __forceinline__ void store_elems(T* p, const float (&f)[V]) {
+    if constexpr (V == 2) {
+        p[0] = from_f<T>(f[0]);
+        p[1] = from_f<T>(f[1]);
+    } else {
+        store_vec<T, V>(p, f);
+    }
+}
+
 template <class T, int V>
 __global__ void __launch_bounds__(256) rope_fwd_kernel(const T* __restrict__ B, const T* __restrict__ C,
                                                        const float* __restrict__ cum, T* __restrict__ Br,
                                                        T* __restrict__ Cr, int Tlen, int h, int g, int n) {
     const int t = blockIdx.x, bb = blockIdx.y;
-    const int half = n / 2, hpg = h / g, upr = half / V;  // V pair indices per thread
+    const int half = n / 2, hpg = h / g, upr = n / V;  // units per head row
     const size_t row = (size_t)bb * Tlen + t;
     for (int e = threadIdx.x; e < h * upr; e += 256) {
-        const int hh = e / upr, m = (e - hh * upr) * V;
+        const int hh = e / upr, j0 = (e - hh * upr) * V;
         const int gg = hh / hpg;
-        float ang[V], b1[V], b2[V], c1[V], c2[V], o1[V], o2[V];
-        load_f32<V>(cum + (row * h + hh) * half + m, ang);
-        const size_t ib = (row * g + gg) * n + m;
-        load_vec<T, V>(B + ib, b1);
-        load_vec<T, V>(B + ib + half, b2);
-        load_vec<T, V>(C + ib, c1);
-        load_vec<T, V>(C + ib + half, c2);
-        const size_t o = (row * h + hh) * n + m;
-        float sn[V], cs[V];
+        float bv[V], cv[V], ob[V], oc[V];
+        const size_t ib = (row * g + gg) * n + j0;
+        load_elems<T, V>(B + ib, bv);
+        load_elems<T, V>(C + ib, cv);
+        float ang[V / 2];
+        load_angles<V / 2>(cum + (row * h + hh) * half + j0 / 2, ang);
 #pragma unroll
-        for (int q = 0; q < V; ++q) sincos_reduced(ang[q], &sn[q], &cs[q]);
-#pragma unroll
-        for (int q = 0; q < V; ++q) { o1[q] = b1[q] * cs[q] - b2[q] * sn[q]; o2[q] = b1[q] * sn[q] + b2[q] * cs[q]; }
-        store_vec<T, V>(Br + o, o1);
-        store_vec<T, V>(Br + o + half, o2);
-#pragma unroll
-        for (int q = 0; q < V; ++q) { o1[q] = c1[q] * cs[q] - c2[q] * sn[q]; o2[q] = c1[q] * sn[q] + c2[q] * cs[q]; }
-        store_vec<T, V>(Cr + o, o1);
-        store_vec<T, V>(Cr + o + half, o2);
+        for (int q = 0; q < V / 2; ++q) {
+            float sn, cs;
+            sincos_reduced(ang[q], &sn, &cs);
+            ob[2 * q] = bv[2 * q] * cs - bv[2 * q + 1] * sn;
+            ob[2 * q + 1] = bv[2 * q] * sn + bv[2 * q + 1] * cs;
+            oc[2 * q] = cv[2 * q] * cs - cv[2 * q + 1] * sn;
+            oc[2 * q + 1] = cv[2 * q] * sn + cv[2 * q + 1] * cs;
+        }
+        const size_t o = (row * h + hh) * n + j0;
+        store_elems<T, V>(Br + o, ob);
+        store_elems<T, V>(Cr + o, oc);
     }
 }
 
@@ -183,45 +224,49 @@ __global__ void __launch_bounds__(256) rope_bwd_kernel(const T* __restrict__ B, 
                                                        int Tlen, int h, int g, int n) {
     extern __shared__ float sm[];  // [2][h][n]: d(un-rotated) B and C per head, then [h] d s
     const int t = blockIdx.x, bb = blockIdx.y;
-    const int half = n / 2, hpg = h / g, upr = half / V;
+    const int half = n / 2, hpg = h / g, upr = n / V;
     const size_t row = (size_t)bb * Tlen + t;
     float* sB = sm;
     float* sC = sm + (size_t)h * n;
     float* sds = sC + (size_t)h * n;
     for (int hh = threadIdx.x; hh < h; hh += 256) sds[hh] = -u_of(dt, lam, row * h + hh, t, Tlen, h) * dyx[row * h + hh];
     for (int e = threadIdx.x; e < h * upr; e += 256) {
-        const int hh = e / upr, m = (e - hh * upr) * V;
+        const int hh = e / upr, j0 = (e - hh * upr) * V;
         const int gg = hh / hpg;
-        float b1[V], b2[V], c1[V], c2[V], db1[V], db2[V], dc1[V], dc2[V];
-        const size_t ib = (row * g + gg) * n + m;
-        load_vec<T, V>(B + ib, b1);
-        load_vec<T, V>(B + ib + half, b2);
-        load_vec<T, V>(C + ib, c1);
-        load_vec<T, V>(C + ib + half, c2);
-        const size_t o = (row * h + hh) * n + m;
-        load_vec<T, V>(dBr + o, db1);
-        load_vec<T, V>(dBr + o + half, db2);
-        load_vec<T, V>(dCr + o, dc1);
-        load_vec<T, V>(dCr + o + half, dc2);
-        float ang[V], dth[V], ub1[V], ub2[V], uc1[V], uc2[V];
-        load_f32<V>(cum + (row * h + hh) * half + m, ang);
+        float bv[V], cv[V], db[V], dc[V], ub[V], uc[V];
+        const size_t ib = (row * g + gg) * n + j0;
+        load_elems<T, V>(B + ib, bv);
+        load_elems<T, V>(C + ib, cv);
+        const size_t o = (row * h + hh) * n + j0;
+        load_elems<T, V>(dBr + o, db);
+        load_elems<T, V>(dCr + o, dc);
+        float ang[V / 2], dth[V / 2];
+        load_angles<V / 2>(cum + (row * h + hh) * half + j0 / 2, ang);
 #pragma unroll
-        for (int q = 0; q < V; ++q) {
+        for (int q = 0; q < V / 2; ++q) {
             float s, c;
             sincos_reduced(ang[q], &s, &c);
-            const float ob1 = b1[q] * c - b2[q] * s, ob2 = b1[q] * s + b2[q] * c;
-            const float oc1 = c1[q] * c - c2[q] * s, oc2 = c1[q] * s + c2[q] * c;
-            dth[q] = (-db1[q] * ob2 + db2[q] * ob1) + (-dc1[q] * oc2 + dc2[q] * oc1);
-            ub1[q] = c * db1[q] + s * db2[q];
-            ub2[q] = -s * db1[q] + c * db2[q];
-            uc1[q] = c * dc1[q] + s * dc2[q];
-            uc2[q] = -s * dc1[q] + c * dc2[q];
+            const float b1 = bv[2 * q], b2 = bv[2 * q + 1], c1 = cv[2 * q], c2 = cv[2 * q + 1];
+            const float db1 = db[2 * q], db2 = db[2 * q + 1], dc1 = dc[2 * q], dc2 = dc[2 * q + 1];
+            const float ob1 = b1 * c - b2 * s, ob2 = b1 * s + b2 * c;
+            const float oc1 = c1 * c - c2 * s, oc2 = c1 * s + c2 * c;
+            dth[q] = (-db1 * ob2 + db2 * ob1) + (-dc1 * oc2 + dc2 * oc1);
+            ub[2 * q] = c * db1 + s * db2;
+            ub[2 * q + 1] = -s * db1 + c * db2;
+            uc[2 * q] = c * dc1 + s * dc2;
+            uc[2 * q + 1] = -s * dc1 + c * dc2;
         }
-        store_f32<V>(dcum + (row * h + hh) * half + m, dth);
-        store_f32<V>(sB + hh * n + m, ub1);
-        store_f32<V>(sB + hh * n + m + half, ub2);
-        store_f32<V>(sC + hh * n + m, uc1);
-        store_f32<V>(sC + hh * n + m + half, uc2);
+        store_angles<V / 2>(dcum + (row * h + hh) * half + j0 / 2, dth);
+        if constexpr (V >= 4) {
+            store_f32<V>(sB + hh * n + j0, ub);
+            store_f32<V>(sC + hh * n + j0, uc);
+        } else {
+#pragma unroll
+            for (int q = 0; q < V; ++q) {
+                sB[hh * n + j0 + q] = ub[q];
+                sC[hh * n + j0 + q] = uc[q];
+            }
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < g * n; e += 256) {

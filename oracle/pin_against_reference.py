@@ -13,7 +13,10 @@ variable).  It
    dx/dA/dB/dC/d_init, and the cached second call (which drops dA);
 3. checks the oracle (chunked and sequential forms) against the 30 stored
    golden vectors of stream/ces/ssd_reference/golden_vectors (headdim-1 form);
-4. writes tests/golden/*.npz: outputs OF THE REFERENCE for small seeded
+4. checks the Mamba-3 pieces of the oracle against the eager definitions in the reference's own tests
+   (tests/kernels/test_rope.py:31-43 rotation, tests/kernels/test_trapezoidal.py:20-34 coefficients) and the
+   block's two-call composition (src/mamba_base_engine.py:137-187) built from those and the imported scan;
+5. writes tests/golden/*.npz: outputs OF THE REFERENCE for small seeded
    inputs (so the tests can check the oracle and the CUDA path without the
    reference present), a copy of three of the stored golden vectors, and
    tests/golden/PINNING.txt with the measured errors.
@@ -75,6 +78,70 @@ def grads_of(fn, x, A, B, C, chunk, init, dY, dfinal, cache=None):
     gr = torch.autograd.grad(outs, ins, gouts, allow_unused=True)
     gr = [torch.zeros_like(i) if g_ is None else g_ for g_, i in zip(gr, ins)]
     return Y.detach(), fs.detach(), ch, gr
+
+
+def load_test_module(ref_root: Path, rel: str, name: str):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(name, ref_root / "r2" / "dhammic-ai" / rel)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def pin_mamba3(S, ref_root: Path, out_dir: Path, say):
+    """The block's composition from the reference's own pieces, on CPU: rotation and coefficients from its test
+    files, the scan from the imported operator (second call with the first call's cache, as the block does)."""
+    rope_ref = load_test_module(ref_root, "tests/kernels/test_rope.py", "_ref_test_rope").apply_rope
+    trap_ref = load_test_module(ref_root, "tests/kernels/test_trapezoidal.py", "_ref_test_trapezoidal")._eager
+    g = torch.Generator().manual_seed(4242)
+    b, T, h, p, n, l = 2, 128, 4, 8, 16, 32
+    x = torch.randn(b, T, h, p, generator=g) * 0.5
+    dt_raw = torch.randn(b, T, h, generator=g) * 0.5
+    lam_raw = torch.randn(b, T, h, generator=g) * 0.5
+    dt_bias = torch.randn(h, generator=g) * 0.1 - 3.0
+    A_log = torch.rand(h, generator=g) * 2.0
+    Bm = torch.randn(b, T, h, n, generator=g) * 0.4
+    Cm = torch.randn(b, T, h, n, generator=g) * 0.4
+    D = torch.randn(h, generator=g)
+    raw_angles = (torch.rand(b, T, h, n // 2, generator=g) * 2 - 1) * 3.14159 * torch.sigmoid(torch.randn(b, T, h, n // 2, generator=g))
+    dY = torch.randn(b, T, h, p, generator=g)
+    # coefficients and rotation against the reference's eager definitions
+    dt, dA_ref, beta_ref, gamma_ref = trap_ref(dt_raw, lam_raw, dt_bias, A_log)
+    lam, A_head = torch.sigmoid(lam_raw), -torch.exp(A_log)
+    dA_o, beta_o, gamma_o = O.trapezoid_coeffs(dt, lam, A_head)
+    e_coef = max(O.rel_to_max(dA_o, dA_ref), O.rel_to_max(beta_o, beta_ref), O.rel_to_max(gamma_o, gamma_ref))
+    cum = -torch.cumsum(raw_angles, dim=1)
+    e_rope = max(O.rel_to_max(O.apply_rope(Bm, cum), rope_ref(Bm, cum)), O.rel_to_max(O.apply_rope(Cm, cum), rope_ref(Cm, cum)))
+    say(f"mamba-3 pieces: trapezoid coefficients rel-to-max {e_coef:.2e}, rotation rel-to-max {e_rope:.2e}")
+    assert e_coef < 1e-6 and e_rope < 1e-6
+
+    def block(xv, dtv, lamv, Bv, Cv, angv, scan):
+        dA, beta, gamma = dtv * A_head, (1.0 - lamv) * dtv * torch.exp(dtv * A_head), lamv * dtv
+        cumv = -torch.cumsum(angv, dim=1)
+        Br, Cr = rope_ref(Bv, cumv), rope_ref(Cv, cumv)
+        y1, _, cache = scan(xv * gamma.unsqueeze(-1), dA, Br, Cr, l)
+        B_prev = F.pad(Br[:, :-1], (0, 0, 0, 0, 1, 0))
+        x_prev = F.pad(xv[:, :-1], (0, 0, 0, 0, 1, 0))
+        y2, _, _ = scan(x_prev * beta.unsqueeze(-1), dA, B_prev, Cr, l, cache=cache)
+        return y1 + y2 + D.view(1, 1, -1, 1) * xv
+
+    leaves = [t.clone().requires_grad_(True) for t in (x, dt, lam, Bm, Cm, raw_angles)]
+    y_ref = block(*leaves, S.fused_ssd_scan)
+    g_ref = torch.autograd.grad([y_ref], leaves, [dY])
+    lo = [t.clone().requires_grad_(True) for t in (x, dt, lam, Bm, Cm, raw_angles)]
+    y_o = O.mamba3_operator(lo[0], lo[1], A_head, lo[3], lo[4], D, lo[5], lo[2], l)
+    g_o = torch.autograd.grad([y_o], lo, [dY])
+    # the reference's cached second call drops its decay gradient, so d dt differs by design; everything that
+    # does not pass through the second call's decay must agree
+    errs = {"Y": O.rel_to_max(y_o, y_ref), "dx": O.rel_to_max(g_o[0], g_ref[0]), "dlam": O.rel_to_max(g_o[2], g_ref[2]),
+            "dB": O.rel_to_max(g_o[3], g_ref[3]), "dC": O.rel_to_max(g_o[4], g_ref[4]),
+            "d_raw_angles": O.rel_to_max(g_o[5], g_ref[5])}
+    say("mamba-3 block composition, oracle vs reference pieces: " + ", ".join(f"{k} {v:.2e}" for k, v in errs.items()))
+    assert max(errs.values()) < 1e-5, errs
+    np.savez_compressed(out_dir / "m3_reference_block.npz", x=x.numpy(), dt=dt.detach().numpy(), lam=lam.numpy(),
+                        A_head=A_head.numpy(), B=Bm.numpy(), C=Cm.numpy(), D=D.numpy(), raw_angles=raw_angles.numpy(),
+                        dY=dY.numpy(), chunk=np.int64(l), Y=y_ref.detach().numpy(), dx=g_ref[0].numpy(),
+                        dlam=g_ref[2].numpy(), dB=g_ref[3].numpy(), dC=g_ref[4].numpy(), d_raw_angles=g_ref[5].numpy())
 
 
 def main():
@@ -160,6 +227,7 @@ def main():
     say(f"{len(files)} stored golden vectors: chunked oracle rel-to-max {worst_c:.2e}, "
         f"sequential oracle rel-to-max {worst_s:.2e}")
     assert len(files) == 30 and worst_c < 1e-5 and worst_s < 1e-5
+    pin_mamba3(S, ref_root, out_dir, say)
     for f in files:
         if "_T128_" in f and any(s in f for s in ("seed42", "seed43", "seed44")):
             d = np.load(f, allow_pickle=True)

@@ -140,11 +140,18 @@ def mamba2_operator(x, dt, A_head, B, C, D, chunk_size, initial_states=None):
 
 
 def apply_rope(v: torch.Tensor, angles: torch.Tensor) -> torch.Tensor:
-    """Pairwise rotation of the two halves of the last dim: (x1,x2) -> (c x1 - s x2, s x1 + c x2)."""
-    half = v.shape[-1] // 2
-    x1, x2 = v[..., :half], v[..., half:]
+    """Rotation of the interleaved pairs (v[2m], v[2m+1]) by angles[m], as the reference's eager rotation does
+    (tests/kernels/test_rope.py:31-43; kernel src/kernels/rope.py:40-85): even = c x1 - s x2, odd = s x1 + c x2."""
+    x1, x2 = v[..., 0::2], v[..., 1::2]
     cs, sn = torch.cos(angles), torch.sin(angles)
-    return torch.cat([x1 * cs - x2 * sn, x1 * sn + x2 * cs], dim=-1)
+    return torch.stack([x1 * cs - x2 * sn, x1 * sn + x2 * cs], dim=-1).flatten(-2)
+
+
+def trapezoid_coeffs(dt: torch.Tensor, lam: torch.Tensor, A_head: torch.Tensor):
+    """(dA, beta, gamma) of the trapezoidal discretisation (src/kernels/trapezoidal.py:6-12;
+    tests/kernels/test_trapezoidal.py:20-34 after its softplus / sigmoid / -exp activations)."""
+    dA = dt * A_head
+    return dA, (1.0 - lam) * dt * torch.exp(dA), lam * dt
 
 
 def mamba3_operator(x, dt, A_head, B, C, D, raw_angles, lam, chunk_size):
@@ -155,9 +162,7 @@ def mamba3_operator(x, dt, A_head, B, C, D, raw_angles, lam, chunk_size):
     Both calls run under plain autograd (the full decay gradient, unlike the cached operator call).
     """
     h = x.shape[2]
-    dA = dt * A_head
-    gamma = lam * dt
-    beta = (1.0 - lam) * dt * torch.exp(dA)
+    dA, beta, gamma = trapezoid_coeffs(dt, lam, A_head)
     cum = -torch.cumsum(raw_angles, dim=1)
     Br = apply_rope(expand_groups(B, h), cum)
     Cr = apply_rope(expand_groups(C, h), cum)

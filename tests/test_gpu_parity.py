@@ -284,6 +284,23 @@ def test_mamba3_variant(pkg, cabi, oracle, dtype, tol):
     assert not bad, errs
 
 
+def test_mamba3_against_reference_fixture(pkg, cabi):
+    """The one-scan Mamba-3 form on the GPU against outputs of the reference's own two-call composition
+    (tests/golden/m3_reference_block.npz: reference rotation convention, coefficients and scan), fp32."""
+    g = load_golden("m3_reference_block.npz")
+    t = {k: torch.as_tensor(v) for k, v in g.items() if k != "chunk"}
+    names = ("x", "dt", "A_head", "B", "C", "D", "raw_angles", "lam")
+    lv = {k: t[k].to(DEV).requires_grad_(True) for k in names}
+    y = pkg.ssd_mamba3(*[lv[k] for k in names], int(g["chunk"]))
+    gr = dict(zip(names, torch.autograd.grad([y], list(lv.values()), [t["dY"].to(DEV)])))
+    torch.cuda.synchronize()
+    errs = {"Y": rel_err(y, t["Y"])}
+    for k, ref in (("x", "dx"), ("lam", "dlam"), ("B", "dB"), ("C", "dC"), ("raw_angles", "d_raw_angles")):
+        errs[ref] = rel_err(gr[k], t[ref])
+    bad = {k: v for k, v in errs.items() if not v < TOL_FP32}
+    assert not bad, errs
+
+
 def test_host_pipeline_matches_direct_call(pkg, cabi):
     """The host-buffer entry (micro-batches over three streams) returns what one call on device tensors returns."""
     cfg = pkg.shrink(pkg.CONFIGS[2], 4, 256)

@@ -123,3 +123,18 @@ def test_mamba3_two_call_equals_two_term_recurrence(oracle, pkg):
             H = H + bet[:, t, :, None, None] * inp["x"][:, t - 1, :, :, None] * Br[:, t - 1, :, None, :]
         ys.append(torch.einsum("bhpn,bhn->bhp", H, Cr[:, t]) + inp["D"][None, :, None] * inp["x"][:, t])
     assert rel_err(y, torch.stack(ys, 1)) < 1e-6
+
+
+def test_oracle_reproduces_reference_mamba3_composition(oracle):
+    """The block's two-call composition built from the reference's own pieces (its tests' eager rotation and
+    coefficients, its scan with the second call on the first call's cache), stored by
+    oracle/pin_against_reference.py.  d dt is not compared: the reference's cached call drops its decay gradient."""
+    g = load_golden("m3_reference_block.npz")
+    t = {k: torch.as_tensor(v) for k, v in g.items() if k != "chunk"}
+    names = ("x", "dt", "A_head", "B", "C", "D", "raw_angles", "lam")
+    lv = {k: t[k].clone().requires_grad_(True) for k in names}
+    y = oracle.mamba3_operator(*[lv[k] for k in names], int(g["chunk"]))
+    gr = dict(zip(names, torch.autograd.grad([y], list(lv.values()), [t["dY"]])))
+    assert rel_err(y, t["Y"]) < 1e-6
+    for k, ref in (("x", "dx"), ("lam", "dlam"), ("B", "dB"), ("C", "dC"), ("raw_angles", "d_raw_angles")):
+        assert rel_err(gr[k], t[ref]) < 1e-5, k
