@@ -130,6 +130,62 @@ def run_reference(args, cfg, pkg, rank):
     print(json.dumps(line))
 
 
+def run_elementwise(args, cfg, pkg):
+    """Rotation (fused_rope) and trapezoidal coefficients (fused_trapezoidal), forward + backward, at the shapes the
+    block would feed the scan with for this config: achieved HBM GB/s on the bytes each call must move."""
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    hbm_peak, _, peak_kind = measured_peaks()
+    b, T, h, n = cfg.batch, cfg.seqlen, cfg.nheads, cfg.d_state
+    dt = torch.bfloat16 if cfg.dtype == "bf16" else torch.float32
+    es = 2 if cfg.dtype == "bf16" else 4
+    g = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(b, T, h, n, generator=g, device=dev).to(dt).requires_grad_(True)
+    ang = torch.randn(b, T, h, n // 2, generator=g, device=dev).requires_grad_(True)
+    gy = torch.randn(b, T, h, n, generator=g, device=dev).to(dt)
+    dt_raw = torch.randn(b, T, h, generator=g, device=dev).to(dt).requires_grad_(True)
+    lam_raw = torch.randn(b, T, h, generator=g, device=dev).to(dt).requires_grad_(True)
+    bias = torch.zeros(h, device=dev, requires_grad=True)
+    alog = torch.zeros(h, device=dev, requires_grad=True)
+    g4 = [torch.randn(b, T, h, generator=g, device=dev).to(dt) for _ in range(4)]
+
+    def rope_step():
+        y = pkg.fused_rope(x, ang)
+        torch.autograd.grad([y], [x, ang], [gy])
+
+    def trap_step():
+        outs = pkg.fused_trapezoidal(dt_raw, lam_raw, bias, alog)
+        torch.autograd.grad(list(outs), [dt_raw, lam_raw, bias, alog], g4)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / args.steps
+
+    nx, na, nt_ = b * T * h * n, b * T * h * (n // 2), b * T * h
+    # rope: fwd reads x, angles, writes y; bwd reads x, angles, dy, writes dx, dangles (fp32 angles)
+    rope_bytes = (2 * nx * es + na * 4) + (3 * nx * es + 2 * na * 4)
+    # trapezoid: fwd reads 2, writes 4; bwd reads 2 + 4, writes 2
+    trap_bytes = 14 * nt_ * es
+    ms_r, ms_t = timed(rope_step), timed(trap_step)
+    line = {"metric": "elementwise_fwd_bwd_GBps", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "dtype": "bf16" if cfg.dtype == "bf16" else "f32", "data": "synthetic", "higher_is_better": True,
+            "config": {"workload": cfg.name, "rope": [b, T, h, n], "trapezoid": [b, T, h],
+                       "l2": "tensors larger than L2 (x %.0f MB)" % (nx * es / 1e6)},
+            "rope": {"ms": ms_r, "GBps": rope_bytes / ms_r / 1e6, "frac_of_hbm": rope_bytes / ms_r / 1e6 / hbm_peak},
+            "trapezoid": {"ms": ms_t, "GBps": trap_bytes / ms_t / 1e6, "frac_of_hbm": trap_bytes / ms_t / 1e6 / hbm_peak},
+            "peak": hbm_peak, "peak_kind": peak_kind}
+    line["value"] = line["rope"]["GBps"]
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -142,6 +198,8 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--op", default="scan", choices=["scan", "elementwise"],
+                    help="elementwise: time the rotation and trapezoidal-coefficient operators instead of the scan")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -155,6 +213,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, cfg, pkg, rank)
+        return
+    if args.op == "elementwise":
+        run_elementwise(args, cfg, pkg)
         return
 
     import torch.distributed as dist

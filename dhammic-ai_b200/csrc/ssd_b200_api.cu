@@ -9,6 +9,7 @@
 #include "ssd_simt.cuh"
 #include "ssd_tc_host.cuh"
 #include "ssd_mamba3.cuh"
+#include "ssd_elementwise.cuh"
 
 #include <atomic>
 #include <mutex>
@@ -404,6 +405,43 @@ int m3_bwd_impl(const ssd::Dims& d, const void* x, const void* dy, const float* 
     CUDA_LAUNCH_CHECK("mamba3 prologue backward");
     return 0;
 }
+
+template <class T>
+int rope_op_impl(bool backward, long long BT, int H, int D, int aH, const void* x, const float* ang, const void* dy,
+                 void* out, float* dang, cudaStream_t st) {
+    using namespace ssd::ew;
+    constexpr int V = VecOf<T>::N;
+    const bool vec = D % V == 0;
+    if (!backward) {
+        if (vec) SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_op_fwd_kernel<T, V><<<(unsigned)BT, 256, 0, st>>>((const T*)x, ang, (T*)out, H, D, aH)));
+        else SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_op_fwd_kernel<T, 2><<<(unsigned)BT, 256, 0, st>>>((const T*)x, ang, (T*)out, H, D, aH)));
+    } else {
+        if (vec) SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_op_bwd_kernel<T, V><<<(unsigned)BT, 128, 0, st>>>((const T*)x, ang, (const T*)dy, (T*)out, dang, H, D, aH)));
+        else SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_op_bwd_kernel<T, 2><<<(unsigned)BT, 128, 0, st>>>((const T*)x, ang, (const T*)dy, (T*)out, dang, H, D, aH)));
+    }
+    CUDA_LAUNCH_CHECK("rope");
+    return 0;
+}
+
+template <class T>
+int trapezoid_impl(bool backward, size_t M, int H, const void* dt_raw, const void* lam_raw, const float* dt_bias,
+                   const float* A_log, const void* const* g, void* const* out, float* d_dt_bias, float* d_A_log,
+                   float* part_ws, cudaStream_t st) {
+    using namespace ssd::ew;
+    if (!backward) {
+        const size_t total = M * (size_t)H;
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, trapezoid_fwd_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)dt_raw, (const T*)lam_raw, dt_bias, A_log, (T*)out[0], (T*)out[1], (T*)out[2], (T*)out[3], total, H));
+    } else {
+        const size_t nblk = (M + TRAP_ROWS - 1) / TRAP_ROWS;
+        float* pb = part_ws;
+        float* pa = part_ws + nblk * H;
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, trapezoid_bwd_kernel<T><<<(unsigned)nblk, 256, 0, st>>>((const T*)dt_raw, (const T*)lam_raw, dt_bias, A_log, (const T*)g[0], (const T*)g[1], (const T*)g[2], (const T*)g[3], (T*)out[0], (T*)out[1], pb, pa, M, H));
+        SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<H, 256, 0, st>>>(pb, d_dt_bias, (int)nblk, H));
+        SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<H, 256, 0, st>>>(pa, d_A_log, (int)nblk, H));
+    }
+    CUDA_LAUNCH_CHECK("trapezoid");
+    return 0;
+}
 }  // namespace
 
 
@@ -627,6 +665,61 @@ int ssd_b200_m3_prologue_bwd(const ssd_b200_shape* shape, const void* x, const v
     return shape->dtype == SSD_B200_BF16
                ? m3_bwd_impl<__nv_bfloat16>(d, x, dy, dt, lam, D, B, C, cum, sdot, dxw, dBr, dCr, dx, dw, dyx, dB, dC, d_raw_angles, dcum_ws, segsum_ws, st)
                : m3_bwd_impl<float>(d, x, dy, dt, lam, D, B, C, cum, sdot, dxw, dBr, dCr, dx, dw, dyx, dB, dC, d_raw_angles, dcum_ws, segsum_ws, st);
+}
+
+int ssd_b200_rope_fwd(int32_t dtype, int64_t B, int64_t T, int64_t H, int64_t D, int32_t broadcast_h, const void* x,
+                      const float* angles, void* y, void* stream) {
+    if (!x || !angles || !y) return fail(SSD_B200_EINVAL, "null pointer");
+    if (B <= 0 || T <= 0 || H <= 0 || D <= 0 || D % 2 || B * T > 2147483647LL) return fail(SSD_B200_EINVAL, "bad rope dimensions");
+    const int aH = broadcast_h ? 1 : (int)H;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SSD_B200_BF16) return rope_op_impl<__nv_bfloat16>(false, B * T, (int)H, (int)D, aH, x, angles, nullptr, y, nullptr, st);
+    if (dtype == SSD_B200_F32) return rope_op_impl<float>(false, B * T, (int)H, (int)D, aH, x, angles, nullptr, y, nullptr, st);
+    return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
+}
+
+int ssd_b200_rope_bwd(int32_t dtype, int64_t B, int64_t T, int64_t H, int64_t D, int32_t broadcast_h, const void* x,
+                      const float* angles, const void* dy, void* dx, float* dangles, void* stream) {
+    if (!x || !angles || !dy || !dx || !dangles) return fail(SSD_B200_EINVAL, "null pointer");
+    if (B <= 0 || T <= 0 || H <= 0 || D <= 0 || D % 2 || B * T > 2147483647LL) return fail(SSD_B200_EINVAL, "bad rope dimensions");
+    const int aH = broadcast_h ? 1 : (int)H;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SSD_B200_BF16) return rope_op_impl<__nv_bfloat16>(true, B * T, (int)H, (int)D, aH, x, angles, dy, dx, dangles, st);
+    if (dtype == SSD_B200_F32) return rope_op_impl<float>(true, B * T, (int)H, (int)D, aH, x, angles, dy, dx, dangles, st);
+    return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
+}
+
+size_t ssd_b200_trapezoid_ws_floats(int64_t rows, int64_t H) {
+    if (rows <= 0 || H <= 0) return 0;
+    return (size_t)2 * (size_t)((rows + ssd::ew::TRAP_ROWS - 1) / ssd::ew::TRAP_ROWS) * (size_t)H;
+}
+
+int ssd_b200_trapezoid_fwd(int32_t dtype, int64_t rows, int64_t H, const void* dt_raw, const void* lam_raw,
+                           const float* dt_bias, const float* A_log, void* dt, void* dA, void* beta, void* gamma,
+                           void* stream) {
+    if (!dt_raw || !lam_raw || !dt_bias || !A_log || !dt || !dA || !beta || !gamma) return fail(SSD_B200_EINVAL, "null pointer");
+    if (rows <= 0 || H <= 0 || H > 2147483647LL) return fail(SSD_B200_EINVAL, "bad trapezoid dimensions");
+    void* out[4] = {dt, dA, beta, gamma};
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SSD_B200_BF16) return trapezoid_impl<__nv_bfloat16>(false, (size_t)rows, (int)H, dt_raw, lam_raw, dt_bias, A_log, nullptr, out, nullptr, nullptr, nullptr, st);
+    if (dtype == SSD_B200_F32) return trapezoid_impl<float>(false, (size_t)rows, (int)H, dt_raw, lam_raw, dt_bias, A_log, nullptr, out, nullptr, nullptr, nullptr, st);
+    return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
+}
+
+int ssd_b200_trapezoid_bwd(int32_t dtype, int64_t rows, int64_t H, const void* dt_raw, const void* lam_raw,
+                           const float* dt_bias, const float* A_log, const void* g_dt, const void* g_dA, const void* g_beta,
+                           const void* g_gamma, void* d_dt_raw, void* d_lam_raw, float* d_dt_bias, float* d_A_log,
+                           float* ws, void* stream) {
+    if (!dt_raw || !lam_raw || !dt_bias || !A_log || !g_dt || !g_dA || !g_beta || !g_gamma || !d_dt_raw || !d_lam_raw ||
+        !d_dt_bias || !d_A_log || !ws)
+        return fail(SSD_B200_EINVAL, "null pointer");
+    if (rows <= 0 || H <= 0 || H > 65535) return fail(SSD_B200_EINVAL, "bad trapezoid dimensions");
+    const void* g[4] = {g_dt, g_dA, g_beta, g_gamma};
+    void* out[2] = {d_dt_raw, d_lam_raw};
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SSD_B200_BF16) return trapezoid_impl<__nv_bfloat16>(true, (size_t)rows, (int)H, dt_raw, lam_raw, dt_bias, A_log, g, out, d_dt_bias, d_A_log, ws, st);
+    if (dtype == SSD_B200_F32) return trapezoid_impl<float>(true, (size_t)rows, (int)H, dt_raw, lam_raw, dt_bias, A_log, g, out, d_dt_bias, d_A_log, ws, st);
+    return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
 }
 
 int ssd_b200_materialize_cache(const ssd_b200_shape* shape, const float* a_cumsum, void* L, void* decay_chunk,

@@ -251,6 +251,29 @@ int ssd_b200_m3_prologue_bwd(const ssd_b200_shape *shape, const void *x, const v
                              void *stream);
 
 /*
+ * The two element-wise operators that feed the scan in the reference's block, stand-alone:
+ *   rope:      y = rotation of the interleaved pairs (x[2m], x[2m+1]) by angles[m]     src/kernels/rope.py:228-325
+ *              (FusedRoPE / fused_rope).  x, y, dy, dx (B,T,H,D) in `dtype`; angles fp32 (B,T,1,D/2) when
+ *              broadcast_h, else (B,T,H,D/2); dangles fp32 in the angles' shape (summed over heads when broadcast).
+ *   trapezoid: dt = softplus(dt_raw + dt_bias), dA = dt * -exp(A_log), beta = (1 - sigmoid(lam_raw)) dt exp(dA),
+ *              gamma = sigmoid(lam_raw) dt                                     src/kernels/trapezoidal.py:220-335
+ *              (FusedTrapezoidal / fused_trapezoidal).  Tensors are (rows, H) in `dtype`; dt_bias, A_log,
+ *              d_dt_bias, d_A_log are fp32 (H); ws: ssd_b200_trapezoid_ws_floats(rows, H) floats of scratch.
+ */
+int ssd_b200_rope_fwd(int32_t dtype, int64_t B, int64_t T, int64_t H, int64_t D, int32_t broadcast_h, const void *x,
+                      const float *angles, void *y, void *stream);
+int ssd_b200_rope_bwd(int32_t dtype, int64_t B, int64_t T, int64_t H, int64_t D, int32_t broadcast_h, const void *x,
+                      const float *angles, const void *dy, void *dx, float *dangles, void *stream);
+size_t ssd_b200_trapezoid_ws_floats(int64_t rows, int64_t H);
+int ssd_b200_trapezoid_fwd(int32_t dtype, int64_t rows, int64_t H, const void *dt_raw, const void *lam_raw,
+                           const float *dt_bias, const float *A_log, void *dt, void *dA, void *beta, void *gamma,
+                           void *stream);
+int ssd_b200_trapezoid_bwd(int32_t dtype, int64_t rows, int64_t H, const void *dt_raw, const void *lam_raw,
+                           const float *dt_bias, const float *A_log, const void *g_dt, const void *g_dA,
+                           const void *g_beta, const void *g_gamma, void *d_dt_raw, void *d_lam_raw, float *d_dt_bias,
+                           float *d_A_log, float *ws, void *stream);
+
+/*
  * Measurement hooks (no counterpart in the reference).  ssd_b200_launch_count() is the number of
  * kernels this library has launched in the process.  With profiling enabled every launch is
  * bracketed by CUDA events on its stream; ssd_b200_profile_read() waits for them, adds their

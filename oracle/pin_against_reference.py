@@ -110,6 +110,8 @@ def pin_mamba3(S, ref_root: Path, out_dir: Path, say):
     lam, A_head = torch.sigmoid(lam_raw), -torch.exp(A_log)
     dA_o, beta_o, gamma_o = O.trapezoid_coeffs(dt, lam, A_head)
     e_coef = max(O.rel_to_max(dA_o, dA_ref), O.rel_to_max(beta_o, beta_ref), O.rel_to_max(gamma_o, gamma_ref))
+    for a_, b_ in zip(O.trapezoid_from_raw(dt_raw, lam_raw, dt_bias, A_log), (dt, dA_ref, beta_ref, gamma_ref)):
+        e_coef = max(e_coef, O.rel_to_max(a_, b_))
     cum = -torch.cumsum(raw_angles, dim=1)
     e_rope = max(O.rel_to_max(O.apply_rope(Bm, cum), rope_ref(Bm, cum)), O.rel_to_max(O.apply_rope(Cm, cum), rope_ref(Cm, cum)))
     say(f"mamba-3 pieces: trapezoid coefficients rel-to-max {e_coef:.2e}, rotation rel-to-max {e_rope:.2e}")

@@ -154,6 +154,15 @@ def trapezoid_coeffs(dt: torch.Tensor, lam: torch.Tensor, A_head: torch.Tensor):
     return dA, (1.0 - lam) * dt * torch.exp(dA), lam * dt
 
 
+def trapezoid_from_raw(dt_raw, lam_raw, dt_bias, A_log):
+    """(dt, dA, beta, gamma) from the raw projections, as the reference's eager path does
+    (tests/kernels/test_trapezoidal.py:20-34; fused in src/kernels/trapezoidal.py:89-143)."""
+    dt = F.softplus(dt_raw + dt_bias)
+    lam = torch.sigmoid(lam_raw)
+    dA, beta, gamma = trapezoid_coeffs(dt, lam, -torch.exp(A_log))
+    return dt, dA, beta, gamma
+
+
 def mamba3_operator(x, dt, A_head, B, C, D, raw_angles, lam, chunk_size):
     """Two-call trapezoidal composition with data-dependent rotary state angles.
 
