@@ -131,8 +131,9 @@ def run_reference(args, cfg, pkg, rank):
 
 
 def run_elementwise(args, cfg, pkg):
-    """Rotation (fused_rope) and trapezoidal coefficients (fused_trapezoidal), forward + backward, at the shapes the
-    block would feed the scan with for this config: achieved HBM GB/s on the bytes each call must move."""
+    """Rotation (fused_rope), trapezoidal coefficients (fused_trapezoidal) and the gated norm after the scan
+    (fused_gate_norm), forward + backward, at the shapes of the block around the scan for this config: achieved HBM
+    GB/s on the bytes each call must move."""
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     hbm_peak, _, peak_kind = measured_peaks()
@@ -157,6 +158,15 @@ def run_elementwise(args, cfg, pkg):
         outs = pkg.fused_trapezoidal(dt_raw, lam_raw, bias, alog)
         torch.autograd.grad(list(outs), [dt_raw, lam_raw, bias, alog], g4)
 
+    yg = torch.randn(b * T, h * cfg.headdim, generator=g, device=dev).to(dt).requires_grad_(True)
+    zg = torch.randn(b * T, h * cfg.headdim, generator=g, device=dev).to(dt).requires_grad_(True)
+    wg = torch.ones(h * cfg.headdim, device=dev, requires_grad=True)
+    gg_ = torch.randn(b * T, h * cfg.headdim, generator=g, device=dev).to(dt)
+
+    def gate_step():
+        o = pkg.fused_gate_norm(yg, zg, wg, 1e-6)
+        torch.autograd.grad([o], [yg, zg, wg], [gg_])
+
     def timed(fn):
         for _ in range(args.warmup):
             fn()
@@ -174,13 +184,17 @@ def run_elementwise(args, cfg, pkg):
     rope_bytes = (2 * nx * es + na * 4) + (3 * nx * es + 2 * na * 4)
     # trapezoid: fwd reads 2, writes 4; bwd reads 2 + 4, writes 2
     trap_bytes = 14 * nt_ * es
-    ms_r, ms_t = timed(rope_step), timed(trap_step)
+    # gate norm: fwd reads y, z, writes out; bwd reads y, z, dout, writes dy, dz (the dw pass re-reads three of them)
+    gate_bytes = 8 * b * T * h * cfg.headdim * es
+    ms_r, ms_t, ms_g = timed(rope_step), timed(trap_step), timed(gate_step)
     line = {"metric": "elementwise_fwd_bwd_GBps", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "dtype": "bf16" if cfg.dtype == "bf16" else "f32", "data": "synthetic", "higher_is_better": True,
             "config": {"workload": cfg.name, "rope": [b, T, h, n], "trapezoid": [b, T, h],
                        "l2": "tensors larger than L2 (x %.0f MB)" % (nx * es / 1e6)},
             "rope": {"ms": ms_r, "GBps": rope_bytes / ms_r / 1e6, "frac_of_hbm": rope_bytes / ms_r / 1e6 / hbm_peak},
             "trapezoid": {"ms": ms_t, "GBps": trap_bytes / ms_t / 1e6, "frac_of_hbm": trap_bytes / ms_t / 1e6 / hbm_peak},
+            "gate_norm": {"ms": ms_g, "GBps": gate_bytes / ms_g / 1e6, "frac_of_hbm": gate_bytes / ms_g / 1e6 / hbm_peak,
+                          "shape": [b * T, h * cfg.headdim]},
             "peak": hbm_peak, "peak_kind": peak_kind}
     line["value"] = line["rope"]["GBps"]
     print(json.dumps(line))

@@ -20,7 +20,8 @@ EXPORTS = (
     "ssd_b200_resolve_path",
     "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix",
     "ssd_b200_m3_prologue_fwd", "ssd_b200_m3_skip_fwd", "ssd_b200_m3_prologue_bwd", "ssd_b200_rope_fwd", "ssd_b200_rope_bwd",
-    "ssd_b200_trapezoid_ws_floats", "ssd_b200_trapezoid_fwd", "ssd_b200_trapezoid_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status",
+    "ssd_b200_trapezoid_ws_floats", "ssd_b200_trapezoid_fwd", "ssd_b200_trapezoid_bwd",
+    "ssd_b200_rmsnorm_ws_floats", "ssd_b200_rmsnorm_fwd", "ssd_b200_rmsnorm_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status",
     "ssd_b200_launch_count", "ssd_b200_profile_enable", "ssd_b200_profile_kernels", "ssd_b200_profile_kernel_name",
     "ssd_b200_profile_read",
 )
@@ -97,6 +98,12 @@ def load() -> C.CDLL:
     lib.ssd_b200_trapezoid_fwd.argtypes = [C.c_int32, C.c_int64, C.c_int64] + [C.c_void_p] * 9
     lib.ssd_b200_trapezoid_bwd.restype = C.c_int
     lib.ssd_b200_trapezoid_bwd.argtypes = [C.c_int32, C.c_int64, C.c_int64] + [C.c_void_p] * 14
+    lib.ssd_b200_rmsnorm_ws_floats.restype = C.c_size_t
+    lib.ssd_b200_rmsnorm_ws_floats.argtypes = [C.c_int64, C.c_int64]
+    lib.ssd_b200_rmsnorm_fwd.restype = C.c_int
+    lib.ssd_b200_rmsnorm_fwd.argtypes = [C.c_int32, C.c_int64, C.c_int64, C.c_float] + [C.c_void_p] * 6
+    lib.ssd_b200_rmsnorm_bwd.restype = C.c_int
+    lib.ssd_b200_rmsnorm_bwd.argtypes = [C.c_int32, C.c_int64, C.c_int64] + [C.c_void_p] * 10
     lib.ssd_b200_m3_skip_fwd.restype = C.c_int
     lib.ssd_b200_m3_skip_fwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 8
     lib.ssd_b200_m3_prologue_bwd.restype = C.c_int

@@ -442,6 +442,28 @@ int trapezoid_impl(bool backward, size_t M, int H, const void* dt_raw, const voi
     CUDA_LAUNCH_CHECK("trapezoid");
     return 0;
 }
+
+template <class T>
+int rmsnorm_impl(bool backward, size_t M, int D, float eps, const void* x, const float* w, const void* z, const void* dout,
+                 void* out, void* dz, float* rstd, float* dw, float* part_ws, cudaStream_t st) {
+    using namespace ssd::ew;
+    constexpr int V = VecOf<T>::N;
+    const bool vec = D % V == 0;
+    const unsigned blocks = (unsigned)((M + 7) / 8);
+    if (!backward) {
+        if (vec) SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_fwd_kernel<T, V><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (T*)out, rstd, M, D, eps)));
+        else SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_fwd_kernel<T, 1><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (T*)out, rstd, M, D, eps)));
+    } else {
+        if (vec) SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_bwd_kernel<T, V><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (const T*)dout, rstd, (T*)out, (T*)dz, M, D)));
+        else SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_bwd_kernel<T, 1><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (const T*)dout, rstd, (T*)out, (T*)dz, M, D)));
+        const unsigned chunks = (unsigned)((M + RMS_ROWS - 1) / RMS_ROWS);
+        if (vec) SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_dw_kernel<T, V><<<dim3((D + 32 * V - 1) / (32 * V), chunks), 256, 0, st>>>((const T*)x, (const T*)z, (const T*)dout, rstd, part_ws, M, D)));
+        else SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_dw_kernel<T, 1><<<dim3((D + 31) / 32, chunks), 256, 0, st>>>((const T*)x, (const T*)z, (const T*)dout, rstd, part_ws, M, D)));
+        SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<D, 256, 0, st>>>(part_ws, dw, (int)chunks, D));
+    }
+    CUDA_LAUNCH_CHECK("rmsnorm");
+    return 0;
+}
 }  // namespace
 
 
@@ -719,6 +741,32 @@ int ssd_b200_trapezoid_bwd(int32_t dtype, int64_t rows, int64_t H, const void* d
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == SSD_B200_BF16) return trapezoid_impl<__nv_bfloat16>(true, (size_t)rows, (int)H, dt_raw, lam_raw, dt_bias, A_log, g, out, d_dt_bias, d_A_log, ws, st);
     if (dtype == SSD_B200_F32) return trapezoid_impl<float>(true, (size_t)rows, (int)H, dt_raw, lam_raw, dt_bias, A_log, g, out, d_dt_bias, d_A_log, ws, st);
+    return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
+}
+
+size_t ssd_b200_rmsnorm_ws_floats(int64_t rows, int64_t D) {
+    if (rows <= 0 || D <= 0) return 0;
+    return (size_t)((rows + ssd::ew::RMS_ROWS - 1) / ssd::ew::RMS_ROWS) * (size_t)D;
+}
+
+int ssd_b200_rmsnorm_fwd(int32_t dtype, int64_t rows, int64_t D, float eps, const void* x, const float* weight,
+                         const void* z, void* out, float* rstd, void* stream) {
+    if (!x || !weight || !out || !rstd) return fail(SSD_B200_EINVAL, "null pointer");
+    if (rows <= 0 || D <= 0 || D > 2147483647LL || (rows + 7) / 8 > 2147483647LL) return fail(SSD_B200_EINVAL, "bad rmsnorm dimensions");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SSD_B200_BF16) return rmsnorm_impl<__nv_bfloat16>(false, (size_t)rows, (int)D, eps, x, weight, z, nullptr, out, nullptr, rstd, nullptr, nullptr, st);
+    if (dtype == SSD_B200_F32) return rmsnorm_impl<float>(false, (size_t)rows, (int)D, eps, x, weight, z, nullptr, out, nullptr, rstd, nullptr, nullptr, st);
+    return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
+}
+
+int ssd_b200_rmsnorm_bwd(int32_t dtype, int64_t rows, int64_t D, const void* x, const float* weight, const void* z,
+                         const void* dout, const float* rstd, void* dx, void* dz, float* dweight, float* ws, void* stream) {
+    if (!x || !weight || !dout || !rstd || !dx || !dweight || !ws || (z && !dz)) return fail(SSD_B200_EINVAL, "null pointer");
+    if (rows <= 0 || D <= 0 || D > 65535 * 32LL || (rows + 7) / 8 > 2147483647LL || (rows + ssd::ew::RMS_ROWS - 1) / ssd::ew::RMS_ROWS > 65535)
+        return fail(SSD_B200_EINVAL, "bad rmsnorm dimensions");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SSD_B200_BF16) return rmsnorm_impl<__nv_bfloat16>(true, (size_t)rows, (int)D, 0.f, x, weight, z, dout, dx, dz, const_cast<float*>(rstd), dweight, ws, st);
+    if (dtype == SSD_B200_F32) return rmsnorm_impl<float>(true, (size_t)rows, (int)D, 0.f, x, weight, z, dout, dx, dz, const_cast<float*>(rstd), dweight, ws, st);
     return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
 }
 

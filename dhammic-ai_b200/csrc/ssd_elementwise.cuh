@@ -1,4 +1,4 @@
-// The two element-wise operators that feed the scan in the reference's block, as stand-alone kernels:
+// The element-wise operators around the scan in the reference's block, as stand-alone kernels:
 //
 //   rotation      y = rope(x, angles)            src/kernels/rope.py:39-193 (FusedRoPE), interleaved pairs
 //                 (x[2m], x[2m+1]) -> (c x1 - s x2, s x1 + c x2); angles (B,T,1,D/2) broadcast over heads or
@@ -9,7 +9,9 @@
 //                 backward as derived there (:30-60), with the per-head sums of d dt_bias, d A_log reduced in a
 //                 fixed order.
 //
-// Both are HBM-bound streaming kernels: 16-byte vector accesses on the wide tensors, fp32 arithmetic.
+//   gate norm     out = rmsnorm(x, w) [* silu(z)]       src/kernels/rmsnorm.py:75-150, src/mamba_base_engine.py:189-191
+//
+// All are HBM-bound streaming kernels: 16-byte vector accesses on the wide tensors, fp32 arithmetic.
 #pragma once
 #include "ssd_common.cuh"
 #include "ssd_mamba3.cuh"
@@ -20,6 +22,18 @@ namespace ew {
 using m3::load_elems;
 using m3::store_elems;
 using m3::VecOf;
+
+// V consecutive elements: one 16-byte vector, or a single element for V = 1
+template <class T, int V>
+__device__ __forceinline__ void load_elems1(const T* p, float (&f)[V]) {
+    if constexpr (V == 1) f[0] = to_f(p[0]);
+    else m3::load_vec<T, V>(p, f);
+}
+template <class T, int V>
+__device__ __forceinline__ void store_elems1(T* p, const float (&f)[V]) {
+    if constexpr (V == 1) p[0] = from_f<T>(f[0]);
+    else m3::store_vec<T, V>(p, f);
+}
 
 // ------------------------------------------------------------------------------------------
 // Rotation.  One block per (b, t); a thread takes V consecutive elements (V/2 pairs) of one head.
@@ -164,6 +178,152 @@ __global__ void __launch_bounds__(256) trapezoid_bwd_kernel(const T* __restrict_
             part_alog[(size_t)blockIdx.x * H + hh] = ta;
         }
         __syncthreads();
+    }
+}
+
+
+// ------------------------------------------------------------------------------------------
+// RMS norm over the last dimension, optionally gated:  out = x * rsqrt(mean(x^2) + eps) * w  [* silu(z)]
+// (src/kernels/rmsnorm.py:75-150; the block's closing `norm(y) * silu(z)`, src/mamba_base_engine.py:189-191).
+// One warp per row, two passes over the row (the second one hits L1 / L2); V elements per lane and step.
+//   backward:  dn = do [* silu(z)],  s = sum_j w_j x_j dn_j,  dx_i = r (w_i dn_i - x_i r^2 s / D),
+//              dz_j = do_j n_j silu'(z_j),  dw_j = sum_rows x_j r dn_j  (a separate column reduction).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float silu_f(float z) { return z * sigmoid_f(z); }
+__device__ __forceinline__ float silu_grad_f(float z) {
+    const float sg = sigmoid_f(z);
+    return sg * (1.f + z * (1.f - sg));
+}
+
+template <class T, int V>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
+                                                          const T* __restrict__ z, T* __restrict__ out,
+                                                          float* __restrict__ rstd, size_t M, int D, float eps) {
+    const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const int lane = threadIdx.x & 31;
+    const T* xr = x + row * D;
+    float ss = 0.f;
+#pragma unroll 4
+    for (int c = lane * V; c < D; c += 32 * V) {
+        float v[V];
+        load_elems1<T, V>(xr + c, v);
+#pragma unroll
+        for (int q = 0; q < V; ++q) ss += v[q] * v[q];
+    }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, of);
+    const float r = rsqrtf(ss / (float)D + eps);
+    if (lane == 0) rstd[row] = r;
+#pragma unroll 4
+    for (int c = lane * V; c < D; c += 32 * V) {
+        float v[V], o[V];
+        load_elems1<T, V>(xr + c, v);
+        if (z) {
+            float g[V];
+            load_elems1<T, V>(z + row * D + c, g);
+#pragma unroll
+            for (int q = 0; q < V; ++q) o[q] = v[q] * r * w[c + q] * silu_f(g[q]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < V; ++q) o[q] = v[q] * r * w[c + q];
+        }
+        store_elems1<T, V>(out + row * D + c, o);
+    }
+}
+
+template <class T, int V>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
+                                                          const T* __restrict__ z, const T* __restrict__ dout,
+                                                          const float* __restrict__ rstd, T* __restrict__ dx,
+                                                          T* __restrict__ dz, size_t M, int D) {
+    const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const int lane = threadIdx.x & 31;
+    const T* xr = x + row * D;
+    const float r = rstd[row];
+    float s = 0.f;
+#pragma unroll 4
+    for (int c = lane * V; c < D; c += 32 * V) {
+        float v[V], g[V];
+        load_elems1<T, V>(xr + c, v);
+        load_elems1<T, V>(dout + row * D + c, g);
+        if (z) {
+            float zz[V];
+            load_elems1<T, V>(z + row * D + c, zz);
+#pragma unroll
+            for (int q = 0; q < V; ++q) g[q] *= silu_f(zz[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < V; ++q) s += w[c + q] * v[q] * g[q];
+    }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) s += __shfl_xor_sync(0xffffffffu, s, of);
+    const float k = r * r * s / (float)D;
+#pragma unroll 4
+    for (int c = lane * V; c < D; c += 32 * V) {
+        float v[V], g[V], o[V];
+        load_elems1<T, V>(xr + c, v);
+        load_elems1<T, V>(dout + row * D + c, g);
+        if (z) {
+            float zz[V], oz[V];
+            load_elems1<T, V>(z + row * D + c, zz);
+#pragma unroll
+            for (int q = 0; q < V; ++q) {
+                oz[q] = g[q] * (v[q] * r * w[c + q]) * silu_grad_f(zz[q]);
+                g[q] *= silu_f(zz[q]);
+            }
+            store_elems1<T, V>(dz + row * D + c, oz);
+        }
+#pragma unroll
+        for (int q = 0; q < V; ++q) o[q] = r * (w[c + q] * g[q] - v[q] * k);
+        store_elems1<T, V>(dx + row * D + c, o);
+    }
+}
+
+// dw partials: block = 32 column threads (V columns each) x 8 row lanes over RMS_ROWS rows; the eight row lanes
+// are added in a fixed order.
+constexpr int RMS_ROWS = 256;
+template <class T, int V>
+__global__ void __launch_bounds__(256) rmsnorm_dw_kernel(const T* __restrict__ x, const T* __restrict__ z,
+                                                         const T* __restrict__ dout, const float* __restrict__ rstd,
+                                                         float* __restrict__ part, size_t M, int D) {
+    __shared__ float sred[8][32 * V + 1];
+    const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
+    const int col = (blockIdx.x * 32 + cl) * V;
+    const size_t r0 = (size_t)blockIdx.y * RMS_ROWS;
+    float acc[V];
+#pragma unroll
+    for (int q = 0; q < V; ++q) acc[q] = 0.f;
+    if (col < D) {
+#pragma unroll 4
+        for (int r = rl; r < RMS_ROWS && r0 + r < M; r += 8) {
+            const size_t i = (r0 + r) * D + col;
+            float xv[V], g[V];
+            load_elems1<T, V>(x + i, xv);
+            load_elems1<T, V>(dout + i, g);
+            if (z) {
+                float zz[V];
+                load_elems1<T, V>(z + i, zz);
+#pragma unroll
+                for (int q = 0; q < V; ++q) g[q] *= silu_f(zz[q]);
+            }
+            const float rr = rstd[r0 + r];
+#pragma unroll
+            for (int q = 0; q < V; ++q) acc[q] += xv[q] * rr * g[q];
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < V; ++q) sred[rl][cl * V + q] = acc[q];
+    __syncthreads();
+    for (int e = threadIdx.x; e < 32 * V; e += 256) {
+        const int c = blockIdx.x * 32 * V + e;
+        if (c < D) {
+            float t = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) t += sred[q][e];
+            part[(size_t)blockIdx.y * D + c] = t;
+        }
     }
 }
 

@@ -1,8 +1,11 @@
-"""The two element-wise operators that feed the scan in the reference's block, with the reference's names,
-argument order, checks and dtypes, on CUDA kernels of the library:
+"""The element-wise operators around the scan in the reference's block, with the reference's names, argument
+order, checks and dtypes, on CUDA kernels of the library:
 
 * ``FusedRoPE`` / ``fused_rope(x, angles)``                                 (src/kernels/rope.py:228-325)
 * ``FusedTrapezoidal`` / ``fused_trapezoidal(dt_raw, lam_raw, dt_bias, A_log)``  (src/kernels/trapezoidal.py:220-335)
+* ``FusedRMSNorm`` / ``fused_rmsnorm(x, weight, eps)`` / ``FusedRMSNormModule``  (src/kernels/rmsnorm.py:154-245)
+* ``fused_gate_norm(y, z, weight, eps)``: the block's closing ``norm(y) * silu(z)``
+  (src/mamba_base_engine.py:189-191) in one pass instead of three
 
 Arithmetic is fp32 inside, results are in the input dtype; there is no CPU path (CPU tensors raise, as in the
 reference).
@@ -123,3 +126,81 @@ def fused_trapezoidal(dt_raw: Tensor, lam_raw: Tensor, dt_bias: Tensor, A_log: T
     """(dt, dA, beta, gamma), each of dt_raw's shape and dtype; same contract as the reference
     (src/kernels/trapezoidal.py:317-335)."""
     return FusedTrapezoidal.apply(dt_raw, lam_raw, dt_bias, A_log)
+
+
+class FusedRMSNorm(torch.autograd.Function):
+    """Same call signature as the reference's FusedRMSNorm (src/kernels/rmsnorm.py:154-219); an optional fourth
+    argument z turns it into the gated form ``rmsnorm(x) * silu(z)``."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, eps: float, *gate: Tensor) -> Tensor:
+        z = gate[0] if gate else None
+        ctx.n_gate = len(gate)
+        assert x.is_cuda and weight.is_cuda, "FusedRMSNorm requires CUDA tensors"
+        D = x.shape[-1]
+        assert weight.dim() == 1 and weight.shape[0] == D, f"weight shape {tuple(weight.shape)} mismatches D={D}"
+        if z is not None:
+            assert z.is_cuda and z.shape == x.shape, f"gate shape {tuple(z.shape)} vs x {tuple(x.shape)}"
+        lib = _cabi.load()
+        xc = x.contiguous()
+        zc = None if z is None else z.contiguous().to(x.dtype)
+        w = weight.contiguous().float()
+        rows = xc.numel() // D
+        dev = x.device
+        with torch.cuda.device(dev):
+            out = torch.empty_like(xc)
+            rstd = torch.empty(rows, dtype=torch.float32, device=dev)
+            _cabi.check(lib.ssd_b200_rmsnorm_fwd(_dt_code(xc), rows, D, float(eps), _ptr(xc), _ptr(w), _ptr(zc), _ptr(out),
+                                                 _ptr(rstd), _stream(dev)))
+        ctx.save_for_backward(xc, w, rstd, zc if zc is not None else torch.empty(0, device=dev))
+        ctx.has_gate = z is not None
+        ctx.weight_dtype = weight.dtype
+        ctx.gate_dtype = None if z is None else z.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        xc, w, rstd, zc = ctx.saved_tensors
+        lib = _cabi.load()
+        D = xc.shape[-1]
+        rows = xc.numel() // D
+        dev = xc.device
+        with torch.cuda.device(dev):
+            dyc = dy.contiguous().to(xc.dtype)
+            dx = torch.empty_like(xc)
+            dz = torch.empty_like(xc) if ctx.has_gate else None
+            dw = torch.empty(D, dtype=torch.float32, device=dev)
+            ws = torch.empty(int(lib.ssd_b200_rmsnorm_ws_floats(rows, D)), dtype=torch.float32, device=dev)
+            _cabi.check(lib.ssd_b200_rmsnorm_bwd(_dt_code(xc), rows, D, _ptr(xc), _ptr(w), _ptr(zc) if ctx.has_gate else None,
+                                                 _ptr(dyc), _ptr(rstd), _ptr(dx), _ptr(dz), _ptr(dw), _ptr(ws), _stream(dev)))
+        grads = (dx, dw.to(ctx.weight_dtype), None)
+        if ctx.n_gate:
+            grads += (None if dz is None else dz.to(ctx.gate_dtype),)
+        return grads
+
+
+def fused_rmsnorm(x: Tensor, weight: Tensor, eps: float = 1e-6) -> Tensor:
+    """x * rsqrt(mean(x^2) + eps) * weight over the last dim; same contract as the reference
+    (src/kernels/rmsnorm.py:222-230)."""
+    return FusedRMSNorm.apply(x, weight, eps)
+
+
+def fused_gate_norm(y: Tensor, z: Tensor, weight: Tensor, eps: float = 1e-6) -> Tensor:
+    """rmsnorm(y, weight, eps) * silu(z), the block's step after the scan (src/mamba_base_engine.py:189-191)."""
+    return FusedRMSNorm.apply(y, weight, eps, z)
+
+
+class FusedRMSNormModule(torch.nn.Module):
+    """Same interface as the reference's module (src/kernels/rmsnorm.py:232-245)."""
+
+    def __init__(self, d: int, eps: float = 1e-6):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.ones(d))
+        self.eps = eps
+        self.d = d
+
+    def forward(self, x: Tensor) -> Tensor:
+        return fused_rmsnorm(x, self.weight, self.eps)
+
+    def extra_repr(self) -> str:
+        return f"d={self.d}, eps={self.eps}"

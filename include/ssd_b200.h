@@ -274,6 +274,21 @@ int ssd_b200_trapezoid_bwd(int32_t dtype, int64_t rows, int64_t H, const void *d
                            float *d_A_log, float *ws, void *stream);
 
 /*
+ * RMS norm over the last dimension, optionally gated (the step after the scan in the reference's block):
+ *     out = x * rsqrt(mean(x^2) + eps) * weight  [* silu(z) when z != NULL]
+ * src/kernels/rmsnorm.py:154-230 (FusedRMSNorm / fused_rmsnorm); with z it is the block's `norm(y) * silu(z)`
+ * (src/mamba_base_engine.py:189-191) in one pass.  x, z, out, dout, dx, dz are (rows, D) in `dtype`; weight,
+ * dweight fp32 (D); rstd fp32 (rows), written by the forward and read by the backward; ws:
+ * ssd_b200_rmsnorm_ws_floats(rows, D) floats of scratch.
+ */
+size_t ssd_b200_rmsnorm_ws_floats(int64_t rows, int64_t D);
+int ssd_b200_rmsnorm_fwd(int32_t dtype, int64_t rows, int64_t D, float eps, const void *x, const float *weight,
+                         const void *z, void *out, float *rstd, void *stream);
+int ssd_b200_rmsnorm_bwd(int32_t dtype, int64_t rows, int64_t D, const void *x, const float *weight, const void *z,
+                         const void *dout, const float *rstd, void *dx, void *dz, float *dweight, float *ws,
+                         void *stream);
+
+/*
  * Measurement hooks (no counterpart in the reference).  ssd_b200_launch_count() is the number of
  * kernels this library has launched in the process.  With profiling enabled every launch is
  * bracketed by CUDA events on its stream; ssd_b200_profile_read() waits for them, adds their

@@ -122,3 +122,84 @@ def test_trapezoidal_rejects_bad_inputs(pkg, cabi):
         pkg.fused_trapezoidal(dt_raw, dt_raw, torch.zeros(3, device=DEV), torch.zeros(4, device=DEV))
     with pytest.raises(AssertionError):
         pkg.fused_trapezoidal(dt_raw.cpu(), dt_raw.cpu(), torch.zeros(4), torch.zeros(4))
+
+
+NORM_SHAPES = [(2, 256, 128), (4, 512, 256), (1, 1024, 96), (2, 64, 4, 32), (1, 128, 8, 16), (2, 64, 4096), (3, 7, 50)]
+EPS = 1e-6
+
+
+def _eager_rmsnorm(x, w, eps=EPS):
+    """The reference tests' eager definition (tests/kernels/test_rmsnorm.py:35-38)."""
+    return torch.nn.functional.rms_norm(x, (x.shape[-1],), w.to(x.dtype), eps)
+
+
+@pytest.mark.parametrize("shape", NORM_SHAPES)
+def test_rmsnorm_forward_fp32(pkg, cabi, shape):
+    torch.manual_seed(0)
+    x = torch.randn(*shape, device=DEV)
+    w = torch.randn(shape[-1], device=DEV) * 0.5 + 1.0
+    y = pkg.fused_rmsnorm(x, w, EPS)
+    assert y.shape == x.shape and y.dtype == x.dtype
+    assert (y - _eager_rmsnorm(x, w)).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("shape", NORM_SHAPES[:6])
+def test_rmsnorm_forward_bf16(pkg, cabi, shape):
+    torch.manual_seed(1)
+    x = torch.randn(*shape, device=DEV).bfloat16()
+    w = (torch.randn(shape[-1], device=DEV) * 0.5 + 1.0).bfloat16()
+    y = pkg.fused_rmsnorm(x, w, EPS)
+    assert y.dtype == torch.bfloat16
+    assert (y.float() - _eager_rmsnorm(x.float(), w.float())).abs().max().item() < 1e-2 * 4  # |y| reaches ~4 here; bf16 ulp scales
+
+
+@pytest.mark.parametrize("shape", NORM_SHAPES)
+def test_rmsnorm_backward_fp32(pkg, cabi, shape):
+    torch.manual_seed(3)
+    x = torch.randn(*shape, device=DEV)
+    w = torch.randn(shape[-1], device=DEV) * 0.5 + 1.0
+    g = torch.randn(*shape, device=DEV)
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    _eager_rmsnorm(xr, wr).backward(g)
+    xk, wk = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    pkg.fused_rmsnorm(xk, wk, EPS).backward(g)
+    assert (xk.grad - xr.grad).abs().max().item() < 1e-3
+    assert (wk.grad - wr.grad).abs().max().item() < 1e-3 * max(1.0, wr.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 5e-2)])
+@pytest.mark.parametrize("shape", [(2, 128, 4096), (2, 64, 256), (1, 33, 96)])
+def test_gate_norm_matches_block_epilogue(pkg, cabi, shape, dtype, tol):
+    """norm(y) * silu(z) as the block composes it (src/mamba_base_engine.py:189-191), forward and gradients."""
+    torch.manual_seed(5)
+    y = torch.randn(*shape, device=DEV).to(dtype)
+    z = torch.randn(*shape, device=DEV).to(dtype)
+    w = torch.randn(shape[-1], device=DEV) * 0.5 + 1.0
+    g = torch.randn(*shape, device=DEV).to(dtype)
+    lr = [t.float().clone().requires_grad_(True) for t in (y, z, w)]
+    ref = _eager_rmsnorm(lr[0], lr[2]) * torch.nn.functional.silu(lr[1])
+    gr = torch.autograd.grad([ref], lr, [g.float()])
+    lk = [t.clone().requires_grad_(True) for t in (y, z, w)]
+    out = pkg.fused_gate_norm(lk[0], lk[1], lk[2], EPS)
+    gk = torch.autograd.grad([out], lk, [g])
+    assert out.dtype == dtype
+    assert (out.float() - ref).abs().max().item() < tol * max(1.0, ref.abs().max().item())
+    gtol = 1e-3 if dtype == torch.float32 else 5e-2
+    for name, a, b in zip(("dy", "dz", "dw"), gk, gr):
+        assert (a.float() - b).abs().max().item() < gtol * max(1.0, b.abs().max().item()), name
+
+
+def test_rmsnorm_module_swap(pkg, cabi):
+    torch.manual_seed(6)
+    ref = torch.nn.RMSNorm(128, eps=EPS).to(DEV)
+    with torch.no_grad():
+        ref.weight.copy_(torch.randn(128, device=DEV) * 0.5 + 1.0)
+    mod = pkg.FusedRMSNormModule(128, EPS).to(DEV)
+    with torch.no_grad():
+        mod.weight.copy_(ref.weight)
+    x = torch.randn(4, 64, 128, device=DEV)
+    assert (mod(x) - ref(x)).abs().max().item() < 1e-5
+    # three-argument apply, as the reference's module calls it, and its backward
+    xk = x.clone().requires_grad_(True)
+    pkg.FusedRMSNorm.apply(xk, mod.weight, EPS).sum().backward()
+    assert xk.grad is not None and mod.weight.grad is not None
