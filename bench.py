@@ -336,8 +336,17 @@ def main():
     if not args.no_e2e:
         h2d = sum(pinned[k].numel() * pinned[k].element_size() for k in names)
         e2e_steps = max(2, min(args.steps, 5))
-        plain = cfg.mamba3 or cfg.seq_parallel
-        if not plain:
+        streamed = cfg.seq_parallel and world == 1 and cfg.seqlen % 16384 == 0
+        plain = (cfg.mamba3 or cfg.seq_parallel) and not streamed
+        if streamed:
+            # one long sequence on one GPU: sequence slices streamed from host memory with the state carried across
+            runner = pkg.SequenceStreamer(dev, slice_len=16384)
+            out_host = pkg.HostPipeline.alloc_outputs(pinned)
+            h2d = 2 * h2d - pinned["dy"].numel() * pinned["dy"].element_size()  # inputs cross twice (forward, backward)
+
+            def step_e2e():
+                runner.run(pinned, out_host, cfg.chunk)
+        elif not plain:
             # the package's host-buffer entry: micro-batches, copies overlapped with the kernels on three streams
             pipe = pkg.HostPipeline(dev, micro_batches=8)
             out_host = pkg.HostPipeline.alloc_outputs(pinned)
@@ -374,7 +383,8 @@ def main():
         d2h = sum(o.numel() * o.element_size() for o in outs_iter)
         e2e = {"value": tokens_all * e2e_steps / (float(t2.item()) * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-               "api": "HostPipeline.run (8 micro-batches, 3 streams)" if not plain else "operator call on pinned buffers"}
+               "api": ("SequenceStreamer.run (16384-position slices, state carried across)" if streamed else
+                       "HostPipeline.run (8 micro-batches, 3 streams)" if not plain else "operator call on pinned buffers")}
 
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -103,3 +103,135 @@ class HostPipeline:
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_cmp)
         cur.wait_stream(self.s_in)
+
+
+class SequenceStreamer:
+    """Forward + backward of the scan over a LONG sequence held in pinned host memory, one slice of the sequence
+    on the GPU at a time, exact across slices: the state leaving a slice enters the next one
+    (``initial_states`` / ``final_state`` of the operator), and in the backward the gradient of a slice's initial
+    state is the next-earlier slice's final-state gradient.  The reference's streaming runner cuts the sequence
+    the same way but lets every slice start from a zero state (src/runtime/chunked_offload.py:117-150); carrying
+    the state makes the sliced result equal to the one-call result.
+
+    GPU memory is independent of the sequence length: two input slots, one slice of results, and the small
+    boundary states ((b,h,p,n) fp32 per slice).  Copies of slice s+1 overlap the kernels of slice s on a second
+    stream.  The backward recomputes each slice's forward from its stored entering state (input-only
+    checkpointing at slice granularity), walking the slices in reverse.
+    """
+
+    def __init__(self, device: torch.device | str = "cuda", slice_len: int = 4096):
+        self.dev = torch.device(device)
+        self.slice_len = int(slice_len)
+        self.s_copy = torch.cuda.Stream(self.dev)
+        self.s_out = torch.cuda.Stream(self.dev)
+
+    def _load(self, host_in, names, s, slots, ev_free):
+        sl = slice(s * self.slice_len, (s + 1) * self.slice_len)
+        slot = slots[s % 2]
+        with torch.cuda.stream(self.s_copy):
+            if ev_free[s % 2] is not None:
+                self.s_copy.wait_event(ev_free[s % 2])
+            for k in names:
+                slot[k].copy_(host_in[k][:, sl], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.s_copy)
+        return slot, ev
+
+    def run(self, host_in: dict[str, Tensor], host_out: dict[str, Tensor], chunk_size: int) -> None:
+        """host_in: pinned x (b,T,h,p), dt (b,T,h), B, C (b,T,g,n), dy (b,T,h,p), A_head (h), D (h).  host_out: pinned
+        y, dx, ddt, dB, dC, dA_head, dD (``HostPipeline.alloc_outputs``).  Returns when every result is in host_out."""
+        T = host_in["x"].shape[1]
+        L = self.slice_len
+        assert T % L == 0 and L % chunk_size == 0, f"sequence {T} / slice {L} / chunk {chunk_size} do not divide"
+        ns = T // L
+        dev = self.dev
+        cur = torch.cuda.current_stream(dev)
+        self.s_copy.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+        A_head = host_in["A_head"].to(dev, non_blocking=True)
+        D = host_in["D"].to(dev, non_blocking=True)
+        b = host_in["x"].shape[0]
+
+        def new_slots(names):
+            return [{k: torch.empty((b, L) + tuple(host_in[k].shape[2:]), dtype=host_in[k].dtype, device=dev)
+                     for k in names} for _ in range(2)]
+
+        # ---- forward over the slices: y out, the state entering every slice kept on the GPU
+        fwd_names = ("x", "dt", "B", "C")
+        slots = new_slots(fwd_names)
+        ev_free = [None, None]
+        states = [None] * (ns + 1)
+        nxt = self._load(host_in, fwd_names, 0, slots, ev_free)
+        for s in range(ns):
+            slot, ev = nxt
+            if s + 1 < ns:
+                nxt = self._load(host_in, fwd_names, s + 1, slots, ev_free)
+            cur.wait_event(ev)
+            with torch.no_grad():
+                y, final = ssd_mamba2(slot["x"], slot["dt"], A_head, slot["B"], slot["C"], D, chunk_size, states[s])
+            states[s + 1] = final
+            done = torch.cuda.Event()
+            done.record(cur)
+            ev_free[s % 2] = done
+            self.s_out.wait_event(done)
+            with torch.cuda.stream(self.s_out):
+                y.record_stream(self.s_out)
+                host_out["y"][:, s * L:(s + 1) * L].copy_(y, non_blocking=True)
+        # ---- backward over the slices in reverse: recompute the slice from its entering state, pass d(state) on
+        bwd_names = ("x", "dt", "B", "C", "dy")
+        slots = new_slots(bwd_names)
+        ev_free = [None, None]
+        order = list(range(ns - 1, -1, -1))
+        dAh = torch.zeros_like(A_head, dtype=torch.float32)
+        dD = torch.zeros_like(D, dtype=torch.float32)
+        dstate = None
+        # slot parity follows the position in the reverse order
+        def load_rev(i):
+            s = order[i]
+            sl = slice(s * L, (s + 1) * L)
+            slot = slots[i % 2]
+            with torch.cuda.stream(self.s_copy):
+                if ev_free[i % 2] is not None:
+                    self.s_copy.wait_event(ev_free[i % 2])
+                for k in bwd_names:
+                    slot[k].copy_(host_in[k][:, sl], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.s_copy)
+            return slot, ev
+
+        nxt = load_rev(0)
+        for i, s in enumerate(order):
+            slot, ev = nxt
+            if i + 1 < ns:
+                nxt = load_rev(i + 1)
+            cur.wait_event(ev)
+            leaves = [slot["x"].detach().requires_grad_(True), slot["dt"].detach().requires_grad_(True),
+                      A_head.detach().requires_grad_(True), slot["B"].detach().requires_grad_(True),
+                      slot["C"].detach().requires_grad_(True), D.detach().requires_grad_(True)]
+            init = None if states[s] is None else states[s].detach().requires_grad_(True)
+            y, final = ssd_mamba2(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], leaves[5], chunk_size, init)
+            outs, gouts = [y], [slot["dy"]]
+            if dstate is not None:
+                outs.append(final)
+                gouts.append(dstate)
+            ins = leaves + ([init] if init is not None else [])
+            grads = torch.autograd.grad(outs, ins, gouts)
+            dAh += grads[2].float()
+            dD += grads[5].float()
+            dstate = grads[6] if init is not None else None
+            done = torch.cuda.Event()
+            done.record(cur)
+            ev_free[i % 2] = done
+            self.s_out.wait_event(done)
+            with torch.cuda.stream(self.s_out):
+                for k, gten in (("dx", grads[0]), ("ddt", grads[1]), ("dB", grads[3]), ("dC", grads[4])):
+                    gten.record_stream(self.s_out)
+                    host_out[k][:, s * L:(s + 1) * L].copy_(gten, non_blocking=True)
+        self.s_out.wait_stream(cur)
+        with torch.cuda.stream(self.s_out):
+            dAh.record_stream(self.s_out)
+            dD.record_stream(self.s_out)
+            host_out["dA_head"].copy_(dAh, non_blocking=True)
+            host_out["dD"].copy_(dD, non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_copy)

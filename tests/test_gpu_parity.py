@@ -315,3 +315,22 @@ def test_host_pipeline_matches_direct_call(pkg, cabi):
     for k in ("y", "dx", "ddt", "dB", "dC"):
         assert torch.equal(out[k], want[k]), k
     assert rel_err(out["dA_head"], want["dA_head"]) < 1e-5 and rel_err(out["dD"], want["dD"]) < 1e-5
+
+
+@pytest.mark.parametrize("idx,batch,seqlen,slice_len", [(2, 1, 1024, 256), (2, 2, 512, 128), (0, 2, 512, 128)])
+def test_sequence_streamer_is_exact_across_slices(pkg, cabi, idx, batch, seqlen, slice_len):
+    """The sequence-sliced host runner (state carried from slice to slice, its gradient carried back) returns what
+    one call over the whole sequence returns, within the rounding of one pass."""
+    cfg = pkg.shrink(pkg.CONFIGS[idx], batch, seqlen)
+    inp = pkg.make_inputs(cfg)
+    pinned = {k: v.pin_memory() for k, v in inp.items()}
+    out = pkg.HostPipeline.alloc_outputs(pinned)
+    runner = pkg.SequenceStreamer("cuda", slice_len=slice_len)
+    for _ in range(2):  # twice: slot reuse across calls
+        runner.run(pinned, out, cfg.chunk)
+    torch.cuda.synchronize()
+    want = mamba2_gpu(pkg, inp, cfg.chunk)
+    tol = TOL_BF16 if cfg.dtype == "bf16" else TOL_FP32
+    errs = {k: rel_err(out[k], want[k]) for k in ("y", "dx", "ddt", "dB", "dC", "dA_head", "dD")}
+    bad = {k: v for k, v in errs.items() if not v < tol}
+    assert not bad, errs
