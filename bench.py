@@ -59,7 +59,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "20", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -273,12 +273,14 @@ def main():
         y, _ = scan(leaves)
         return y, torch.autograd.grad([y], list(leaves.values()), [devin["dy"]])
 
-    for _ in range(args.warmup):
-        step_device()
-    barrier()
+    # the sampler starts before the warm-up (the timed region is tens of milliseconds; nvidia-smi needs a moment to
+    # come up) and keeps the samples taken from then to the end of the timed region, all of them under load
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step_device()
+    barrier()
     launches0 = cabi.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
