@@ -91,29 +91,51 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
     const int h0 = hg * 32;
     const bool head_ok = h0 + lane < P.h;
     if (P.dt) {
+#pragma unroll
         for (int t = warp; t < LT; t += 8)
             sdt[t][lane] = head_ok ? P.dt[((size_t)bb * P.T + (size_t)k * LT + t) * P.h + h0 + lane] : 0.f;
     }
+    // every load of the warp's four heads is issued before any of them is used
+    float va[4][4], dxa[4][4], yxa[4], gsa[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int hh = h0 + warp * 4 + i;
+        yxa[i] = 0.f;
+        gsa[i] = 0.f;
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) va[i][s4] = dxa[i][s4] = 0.f;
+        if (hh < P.h) {
+            const size_t base = ((size_t)bb * P.h + hh) * P.T + (size_t)k * LT;
+#pragma unroll
+            for (int s4 = 0; s4 < 4; ++s4) {
+                const int t = s4 * 32 + lane;
+                va[i][s4] = P.g[base + t];
+                dxa[i][s4] = P.ddtx[base + t];
+                if (P.dyx) yxa[i] += P.dyx[base + t];
+            }
+            if (lane < 16) {  // the 2 x 8 terms that act through the tile's last row, one per lane
+                const size_t so = ((((size_t)bb * P.h + hh) * P.nt) + k) * 8;
+                gsa[i] = lane < 8 ? P.gS[so + lane] : P.gS2[so + lane - 8];
+            }
+        }
+    }
     __syncthreads();
-#pragma unroll 1
+#pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int hl = warp * 4 + i, hh = h0 + hl;
         if (hh >= P.h) break;  // warp-uniform
-        const size_t base = ((size_t)bb * P.h + hh) * P.T + (size_t)k * LT;
-        float v[4], dx[4], yx = 0.f;
+        float v[4], dx[4], yx = yxa[i];
 #pragma unroll
         for (int s4 = 0; s4 < 4; ++s4) {
-            const int t = s4 * 32 + lane;
-            v[s4] = P.g[base + t];
-            dx[s4] = P.ddtx[base + t];
-            if (P.dyx) yx += P.dyx[base + t];
+            v[s4] = va[i][s4];
+            dx[s4] = dxa[i][s4];
         }
-        if (lane == 31) {
-            const size_t so = ((((size_t)bb * P.h + hh) * P.nt) + k) * 8;
-            const float* q = P.gS + so;
-            const float* r = P.gS2 + so;
-            v[3] += (((q[0] + q[1]) + (q[2] + q[3])) + ((q[4] + q[5]) + (q[6] + q[7]))) +
-                    (((r[0] + r[1]) + (r[2] + r[3])) + ((r[4] + r[5]) + (r[6] + r[7])));
+        {
+            float gs = gsa[i];  // fixed-order sum of the sixteen terms, result in every lane
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
+            gs += __shfl_xor_sync(0xffffffffu, gs, 16);
+            if (lane == 31) v[3] += gs;
         }
         // suffix sums: inside each 32-lane segment by shuffles, then the totals of the later segments
         float tot[4];
@@ -157,6 +179,7 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
     __syncthreads();
     float* out = P.dt ? P.ddt : P.da;
     if (out && head_ok) {
+#pragma unroll
         for (int t = warp; t < LT; t += 8) out[((size_t)bb * P.T + (size_t)k * LT + t) * P.h + h0 + lane] = sout[t][lane];
     }
 }
