@@ -41,24 +41,46 @@ inline bool supported(int dtype, int T, int h, int p, int n, int g, int l) {
 }
 
 // ------------------------------------------------------------------------------------------
-__global__ void tile_cumsum_kernel(const float* __restrict__ cum, const float* __restrict__ dt, float* __restrict__ tcum,
-                                   float* __restrict__ dtT, int b, int T, int h, int l) {
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    const int hh = blockIdx.y, bb = blockIdx.z;
-    if (t >= T) return;
-    const int c = T / l, k = t / l, i = t - k * l;
-    const float* cu = cum + ((size_t)((size_t)bb * h + hh) * c) * l;
-    float v = cu[(size_t)k * l + i];
-    if (l >= LT) {
-        const int i0 = (i / LT) * LT;
-        if (i0 > 0) v -= cu[(size_t)k * l + i0 - 1];
-    } else {
-        const int k0 = (t / LT) * (LT / l);
-        for (int kk = k0; kk < k; ++kk) v += cu[(size_t)kk * l + l - 1];
+// Tile-cumulative log2 decay and dt in (b,h,T) order, one block per (128-tile, 32 heads, batch): dt arrives in the
+// caller's (b,T,h) order and goes through a shared-memory transpose, so reads and writes are both 128-byte rows.
+__global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restrict__ cum, const float* __restrict__ dt,
+                                                          float* __restrict__ tcum, float* __restrict__ dtT, int b, int T,
+                                                          int h, int l) {
+    __shared__ float sdt[LT][33];
+    const int kt = blockIdx.x, hg = blockIdx.y, bb = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h0 = hg * 32;
+    (void)b;
+    if (dt) {
+        const bool head_ok = h0 + lane < h;
+#pragma unroll
+        for (int t = warp; t < LT; t += 8)
+            sdt[t][lane] = head_ok ? dt[((size_t)bb * T + (size_t)kt * LT + t) * h + h0 + lane] : 0.f;
     }
-    const size_t o = ((size_t)bb * h + hh) * T + t;
-    tcum[o] = v * 1.4426950408889634f;  // stored in log2 units: every consumer uses exp2
-    if (dt) dtT[o] = dt[((size_t)bb * T + t) * h + hh];
+    __syncthreads();
+    const int c = T / l;
+#pragma unroll
+    for (int i4 = 0; i4 < 4; ++i4) {
+        const int hl = warp * 4 + i4, hh = h0 + hl;
+        if (hh >= h) break;  // warp-uniform
+        const float* cu = cum + ((size_t)((size_t)bb * h + hh) * c) * l;
+        const size_t o = ((size_t)bb * h + hh) * T + (size_t)kt * LT;
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+            const int tt = s4 * 32 + lane, t = kt * LT + tt;
+            const int k = t / l, i = t - k * l;
+            float v = cu[(size_t)k * l + i];
+            if (l >= LT) {
+                const int i0 = (i / LT) * LT;
+                if (i0 > 0) v -= cu[(size_t)k * l + i0 - 1];
+            } else {
+                const int k0 = kt * (LT / l);
+                for (int kk = k0; kk < k; ++kk) v += cu[(size_t)kk * l + l - 1];
+            }
+            tcum[o + tt] = v * 1.4426950408889634f;  // stored in log2 units: every consumer uses exp2
+            if (dt) dtT[o + tt] = sdt[tt][hl];
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------

@@ -104,7 +104,7 @@ inline int set_walk_attrs(char* err, size_t errn) {
 
 inline int launch_tile_cumsum(const Dims& d, const float* cum, const float* dt, float* tcum, float* dtT,
                               cudaStream_t st, char* err, size_t errn) {
-    dim3 g((d.T + 255) / 256, d.h, d.b);
+    dim3 g(d.T / LT, (d.h + 31) / 32, d.b);
     SSD_LAUNCH(prof::K_TC_AUX, st, tile_cumsum_kernel<<<g, 256, 0, st>>>(cum, dt, tcum, dtT, d.b, d.T, d.h, d.l));
     SSD_TC_CHECK("tile_cumsum");
     return 0;
