@@ -130,25 +130,22 @@ __global__ void __launch_bounds__(NTHR) chunk_cumsum_kernel(Params P) {
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per = (d.l + 31) / 32;
+    // lane <-> position inside a 32-position segment (coalesced stores); segments in sequence with a running carry
     for (int hh = warp; hh < d.h; hh += NTHR / 32) {
-        float local = 0.f;
-        const int i0 = lane * per;
-        for (int q = 0; q < per; ++q)
-            if (i0 + q < d.l) local += sm[(i0 + q) * ldh + hh];
-        float incl = local;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            float v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
-        }
-        float run = incl - local;
         float* out = P.cum + cum_off(d, bb, hh, k);
-        for (int q = 0; q < per; ++q)
-            if (i0 + q < d.l) {
-                run += sm[(i0 + q) * ldh + hh];
-                out[i0 + q] = run;
+        float carry = 0.f;
+        for (int i0 = 0; i0 < d.l; i0 += 32) {
+            const int i = i0 + lane;
+            float incl = i < d.l ? sm[i * ldh + hh] : 0.f;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                float v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
             }
+            incl += carry;
+            if (i < d.l) out[i] = incl;
+            carry = __shfl_sync(0xffffffffu, incl, 31);
+        }
     }
 }
 
