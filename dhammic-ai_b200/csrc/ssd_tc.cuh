@@ -12,7 +12,9 @@
 //                       in registers:
 //        MODE 0  forward:   Y = ((C B^T) o L) X + diag(e) C H^T (+ D x);  H <- e^{S} H + X^T diag(d) B
 //        MODE 1  states:    only the recurrence; stores H_k (state entering tile k) as bf16
-//        MODE 2  dstates:   reverse walk, Q <- e^{S} Q + dY^T diag(e) C; stores Q_k = dH_{k+1} as bf16
+//        MODE 3  the reverse recurrence alone (gradient of the initial state only)
+//   rev_walk_kernel     reverse walk of the backward pass, Q <- e^{S} Q + dY^T diag(e) C, software-pipelined
+//                       over tiles; stores Q_k = dH_{k+1} as bf16 and the state parts of the decay gradient
 //   bwd_tile_kernel     one CTA per (batch, tile, group), heads of the group in an inner loop so
 //                       that dB and dC accumulate over heads in TMEM:
 //        dG = dY X^T, dS = dG o L, dX = G^T dY + diag(d) B Q^T, dC += dS B + diag(e) dY H,
@@ -221,19 +223,19 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restric
 
 // ------------------------------------------------------------------------------------------
 struct WalkParams {
-    CUtensorMap mU;   // x (modes 0,1) or dy (mode 2): 2D [b*T][h*64]
-    CUtensorMap mV;   // B (modes 0,1) or C (mode 2):  2D [b*T][g*128]
-    CUtensorMap mC;   // C (mode 0)
+    CUtensorMap mU;   // x (modes 0,1) or dy (reverse walks): 2D [b*T][h*64]
+    CUtensorMap mV;   // B (modes 0,1) or C (reverse walks):  2D [b*T][g*128]
+    CUtensorMap mC;   // C (mode 0); rev_walk_kernel: the stored forward states, 2D [b*nt*h*128][64]
     const float* tcum;
     const float* dtT;
     const float* D;
-    const float* seed;   // init (modes 0,1) or dfinal (mode 2), (b,h,p,n) fp32, may be null
-    float* out_state;    // final_state (modes 0,1) or dinit (mode 2), may be null
+    const float* seed;   // init (modes 0,1) or dfinal (reverse walks), (b,h,p,n) fp32, may be null
+    float* out_state;    // final_state (modes 0,1) or dinit (reverse walks), may be null
     CUtensorMap mY;   // y store (mode 0)
     CUtensorMap mS;   // state store: 2D [b*nt*h*128][64]
     int save_states;  // store the state entering every tile of the walk through mS
-    float* gS;           // mode 2: (b,h,nt,8) per warp exp(S_k) <Q_k, H_k>
-    float* rterm;        // mode 2: (2,b,h,T) halves of e_i * sum_p dY[i,p] (C_i . H_k[p,:])
+    float* gS;           // rev_walk_kernel: (b,h,nt,8) per warp exp(S_k) <Q_k, H_k>
+    float* rterm;        // rev_walk_kernel: (2,b,h,T) halves of e_i * sum_p dY[i,p] (C_i . H_k[p,:])
     int* status;
     int T, h, hpg, nt;
 };
@@ -280,6 +282,7 @@ __device__ __forceinline__ void store_row32(uint8_t* panel, int row, int col0_in
 }  // namespace tc
 }  // namespace ssd
 #include "ssd_tc_walk.cuh"
+#include "ssd_tc_revwalk.cuh"
 namespace ssd {
 namespace tc {
 

@@ -95,7 +95,7 @@ inline size_t states_bytes(const Dims& d) { return tile_states_bytes(d) + 2 * ((
 inline int set_walk_attrs(char* err, size_t errn) {
     cudaError_t e = cudaFuncSetAttribute(walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<0>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<1>::SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<2>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRevSmem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<3>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem);
     if (e != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "set shared memory size: %s", cudaGetErrorString(e));
@@ -223,7 +223,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.rterm = (float*)(ws + w.rterm); P.gS = (float*)(ws + w.gS);
         P.tcum = tcum; P.dtT = nullptr; P.D = nullptr; P.seed = a->dfinal; P.out_state = dinit; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
-        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<2><<<dim3(d.h, d.b), 288, WalkCfg<2>::SMEM, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, rev_walk_kernel<<<dim3(d.h, d.b), 288, kRevSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_dstate");
     }
     {

@@ -18,8 +18,8 @@
 //   bar_h      accumulators read, new state written, 256 arrive   (row warps -> control)
 //
 // MODE 0 forward (writes y), MODE 1 states only (stores the state entering every tile, bf16),
-// MODE 2 reverse walk over dy and C (stores the state gradient leaving every tile, and the state part of
-// the decay gradient of every row), MODE 3 the same reverse recurrence alone (for d initial-state only).
+// MODE 3 the reverse recurrence over dy and C alone (for d initial-state only).  The full reverse walk of the
+// backward pass is rev_walk_kernel (ssd_tc_revwalk.cuh).
 #pragma once
 
 namespace ssd {
@@ -69,7 +69,7 @@ __device__ __forceinline__ void store_state_slot(__nv_bfloat16* slot, int row, i
 template <int MODE>
 struct WalkCfg {
     static constexpr int NST = (MODE == 1 || MODE == 3) ? 3 : 2;              // load stages
-    static constexpr int STAGE_PANELS = (MODE == 0) ? 5 : (MODE == 2 ? 4 : 3);  // V(2) U(1) [C(2) | H_k(1)]
+    static constexpr int STAGE_PANELS = (MODE == 0) ? 5 : 3;                   // V(2) U(1) [C(2)]
     static constexpr uint32_t STAGE_BYTES = STAGE_PANELS * PANEL;
     // stages | sUd | sH | sY (mode 0) | scum2[2][128] sf[2][128] | alignment slack
     static constexpr size_t SMEM = (size_t)NST * STAGE_BYTES + 2 * PANEL + (MODE == 0 ? PANEL : 0) + 4 * LT * 4 + 1024;
@@ -79,7 +79,7 @@ template <int MODE>
 __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ WalkParams P) {
     using Cfg = WalkCfg<MODE>;
     constexpr int NST = Cfg::NST;
-    constexpr bool REV = (MODE == 2 || MODE == 3);
+    constexpr bool REV = (MODE == 3);
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment by an offset on the __shared__ array itself, so that every access below stays a
     // shared-memory instruction (a pointer rebuilt from an integer would be a generic-address access)
@@ -154,8 +154,6 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     tma_load_2d(st + 3 * PANEL, &P.mC, &bar_ld[s], gg * DN, grow);
                     tma_load_2d(st + 4 * PANEL, &P.mC, &bar_ld[s], gg * DN + 64, grow);
                 }
-                if (MODE == 2)  // the state that entered this tile in the forward direction (mC = its map here)
-                    tma_load_2d(st + 3 * PANEL, &P.mC, &bar_ld[s], 0, (int)((((size_t)bb * nt + k) * P.h + hh) * DN));
             };
             auto issue_S = [&](int it) {  // S = C B^T of tile `it` into TMEM buffer it & 1
                 const uint32_t st = smem_u32(sStage + (size_t)(it % NST) * Cfg::STAGE_BYTES);
@@ -191,15 +189,13 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     tma_store_commit();
                 }
                 tc_fence_after();
-                if (MODE == 0 || MODE == 2) {
-                    // Yo = C H^T : A = C K-major, B = state [n][p] MN-major.  Forward: the running state in
-                    // sH.  Reverse walk: C is the V operand and H_k comes from the stored forward states.
-                    const uint32_t h0 = MODE == 0 ? smem_u32(sH) : st + 3 * PANEL;
-                    const uint32_t a0 = MODE == 0 ? c0 : v0;
+                if (MODE == 0) {
+                    // Yo = C H^T : A = C K-major, B = the running state in sH, [n][p] MN-major
+                    const uint32_t h0 = smem_u32(sH);
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
                         const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                        mma_ss(tYo, smem_desc(a0 + off, 16, 1024), smem_desc(h0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
+                        mma_ss(tYo, smem_desc(c0 + off, 16, 1024), smem_desc(h0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
                     }
                 }
                 mbar_wait(&bar_u, ph, &failed);
@@ -287,26 +283,6 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     *reinterpret_cast<uint4*>(sUd + sw128(row, hf * 4 + ch)) = v;
                 }
             }
-            if (MODE == 2) {
-                // exp(S_k) <Q_k, H_k>: gradient of the inter-tile decay; Q_k is this thread's state row (fp32, not yet
-                // updated), H_k the stored forward state of the tile (rows n of the loaded panel)
-                const uint8_t* sHk = st + 3 * PANEL;
-                float qh = 0.f;
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint4 hv = *reinterpret_cast<const uint4*>(sHk + sw128(row, hf * 4 + ch));
-                    const uint32_t* hu = reinterpret_cast<const uint32_t*>(&hv);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        float2 fh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hu[q]));
-                        qh += fh.x * H[ch * 8 + 2 * q] + fh.y * H[ch * 8 + 2 * q + 1];
-                    }
-                }
-                qh *= exp2f(Sk);
-#pragma unroll
-                for (int of = 16; of > 0; of >>= 1) qh += __shfl_xor_sync(0xffffffffu, qh, of);
-                if (lane == 0) P.gS[((bh * (size_t)nt) + k) * 8 + warp] = qh;
-            }
             fence_async_smem();
             mbar_arrive(&bar_u);
             if (MODE == 0) {
@@ -375,21 +351,6 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     }
                 }
                 store_half_row(sY, row, hf * 4, y);
-            }
-            if (MODE == 2) {
-                // state part of the decay gradient of row i: e_i * sum_p dY[i,p] (C_i . H_k[p,:]); each half
-                // of the row writes its own partial
-                uint32_t o[32];
-                tmem_ld32(tYo + lanes + hf * 32, o);
-                const float e = exp2f(c_i);
-                tmem_ld_wait();
-                float acc = 0.f;
-#pragma unroll
-                for (int q = 0; q < 16; ++q) {
-                    float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xrow[q]));
-                    acc += __uint_as_float(o[2 * q]) * f.x + __uint_as_float(o[2 * q + 1]) * f.y;
-                }
-                P.rterm[((size_t)hf * gridDim.y * P.h + bh) * P.T + (size_t)k * LT + row] = e * acc;
             }
             {
                 uint32_t r[32];
