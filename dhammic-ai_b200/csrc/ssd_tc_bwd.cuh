@@ -53,6 +53,7 @@ struct BwdParams {
                                    // tile (the reverse walk writes its own array of the same shape)
     int* status;
     int T, h, hpg, nt, b;
+    int items;                     // nt * groups * b work items (tile, group, batch), tile fastest
 };
 
 
@@ -79,9 +80,14 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
     __shared__ int failed;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int k = blockIdx.x, gg = blockIdx.y, bb = blockIdx.z;
-    const int row0 = bb * P.T + k * LT;
-    const int hpg = P.hpg;
+    // Persistent over work items (tile k, group gg, batch bb): the loads and the per-row scalars of the next item
+    // are issued while the group terms of the current one are stored.  `hc` counts heads and `ic` items since the
+    // start of the kernel; every buffer index and mbarrier phase derives from them.
+    const int hpg = P.hpg, ngroups = P.h / P.hpg;
+    int item = blockIdx.x;
+    int k = item % P.nt, gg = (item / P.nt) % ngroups, bb = item / (P.nt * ngroups);
+    int row0 = bb * P.T + k * LT;
+    uint32_t hc = 0, ic = 0;
     const int row = tid & 127, qc = tid >> 7;  // column quarter: S / dG columns [32 qc, 32 qc + 32), p columns [16 qc, +16)
     const int rb = row >> 5;                   // row block, warp-uniform
     const bool active = qc <= rb, diag = qc == rb;
@@ -106,7 +112,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
         tmem_relinquish();
     }
     auto load_xy = [&](int hl) {
-        const int hh = gg * hpg + hl, xb = hl & 1;
+        const int hh = gg * hpg + hl, xb = (hc + hl) & 1;
         mbar_expect_tx(&bar_xy[xb], 2 * PANEL);
         tma_load_2d(sXY + (2 * xb) * PANEL, &P.mX, &bar_xy[xb], hh * HP, row0);
         tma_load_2d(sXY + (2 * xb + 1) * PANEL, &P.mdY, &bar_xy[xb], hh * HP, row0);
@@ -136,7 +142,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (tid == CTL) {
+    auto load_item = [&]() {  // C and B of the item, x / dy / H / Q of its first head
         mbar_expect_tx(&bar_cb, 4 * PANEL);
         tma_load_2d(sC, &P.mC, &bar_cb, gg * DN, row0);
         tma_load_2d(sC + PANEL, &P.mC, &bar_cb, gg * DN + 64, row0);
@@ -144,15 +150,16 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
         tma_load_2d(sB + PANEL, &P.mB, &bar_cb, gg * DN + 64, row0);
         load_xy(0);
         load_hq(0);
-    }
+    };
+    if (tid == CTL) load_item();
     const uint32_t tm = tmem_slot;
     // phase 1: S [0,128) dG [128,256); after the mask loop (barrier A) dX1 [0,64) and dX2 [64,128) take the S
     // columns and dYe (bf16 pairs) the dG columns [128,160); persistent over heads: dC [256,384) dB [384,512)
     const uint32_t tS = tm, tdG = tm + 128, tX1 = tm, tX2 = tm + 64, tdC = tm + 256, tdB = tm + 384;
     const uint32_t lanes = lane_base(warp);
     const uint32_t c0a = smem_u32(sC), b0a = smem_u32(sB), g0a = smem_u32(sG), h0a = smem_u32(sH), q0a = smem_u32(sQ);
-    auto issue_phase1 = [&](int hl) {  // S = C B^T (K = n) and dG = dY x^T (K = p) of head hl
-        const uint32_t x0 = smem_u32(sXY + (2 * (hl & 1)) * PANEL), y0 = x0 + PANEL;
+    auto issue_phase1 = [&](int hl, bool commit) {  // S = C B^T (K = n) and dG = dY x^T (K = p) of head hl
+        const uint32_t x0 = smem_u32(sXY + (2 * ((hc + hl) & 1)) * PANEL), y0 = x0 + PANEL;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
             const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
@@ -161,26 +168,33 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
             mma_ss(tdG, smem_desc(y0 + kk * 32, 16, 1024), smem_desc(x0 + kk * 32, 16, 1024), kIdescKK128, kk > 0);
-        mma_commit(&bar_m1);
+        if (commit) mma_commit(&bar_m1);
     };
 
-    float2 dS2[16];  // sum over heads of dS for this thread's 32 columns, as fp32 pairs
-#pragma unroll
-    for (int q = 0; q < 16; ++q) dS2[q] = make_float2(0.f, 0.f);
-    mbar_wait(&bar_cb, 0, &failed);
-    if (tid == CTL) {
-        mbar_wait(&bar_xy[0], 0, &failed);
-        tc_fence_after();
-        issue_phase1(0);
-        if (hpg > 1) load_xy(1);
-    }
     // G panel and 16-byte chunk of this thread's two 16-column steps
     uint8_t* sGq = sG + (qc >> 1) * PANEL;
     const int gch = (qc & 1) * 4;
 
+  for (;;) {
+    float2 dS2[16];  // sum over heads of dS for this thread's 32 columns, as fp32 pairs
+#pragma unroll
+    for (int q = 0; q < 16; ++q) dS2[q] = make_float2(0.f, 0.f);
+    mbar_wait(&bar_cb, ic & 1, &failed);
+    if (tid == CTL && ic == 0) {  // later items: issued at the end of the item before
+        mbar_wait(&bar_xy[hc & 1], (hc >> 1) & 1, &failed);
+        tc_fence_after();
+        issue_phase1(0, true);
+        if (hpg > 1) load_xy(1);
+    }
+    // the item after this one (its row scalars are fetched during the last head of this one)
+    const int nitem = item + (int)gridDim.x;
+    const bool more = nitem < P.items;
+    const int nk = nitem % P.nt, ngg = (nitem / P.nt) % ngroups, nbb = nitem / (P.nt * ngroups);
+
     for (int hl = 0; hl < hpg; ++hl) {
-        const int hh = gg * hpg + hl, xb = hl & 1, buf = hl & 1;
-        const uint32_t ph = hl & 1;
+        const uint32_t hcur = hc + hl;
+        const int hh = gg * hpg + hl, xb = hcur & 1, buf = hcur & 1;
+        const uint32_t ph = hcur & 1;
         const size_t tpos = pos_of(hl) + row;
         const float c_i = c_n, dtv = dt_n, Dh = D_n;
         if (hl + 1 < hpg) {
@@ -189,6 +203,12 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             cend_n = P.tcum[o + (row | 31)];
             dt_n = P.dtT ? P.dtT[o + row] : 1.f;
             D_n = P.D ? P.D[hh + 1] : 0.f;
+        } else if (more) {
+            const size_t o = ((size_t)nbb * P.h + ngg * hpg) * P.T + (size_t)nk * LT;
+            c_n = P.tcum[o + row];
+            cend_n = P.tcum[o + (row | 31)];
+            dt_n = P.dtT ? P.dtT[o + row] : 1.f;
+            D_n = P.D ? P.D[ngg * hpg] : 0.f;
         }
         // state part of the gradient of this row (from the reverse walk): needed once per row, after the barrier (C)
         float rt0 = 0.f, rt1 = 0.f;  // loaded here, first used after the barrier (C): no stall on the loads
@@ -196,7 +216,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             rt0 = P.rterm[tpos];
             rt1 = P.rterm[bhT + tpos];
         }
-        mbar_wait(&bar_xy[xb], (hl >> 1) & 1, &failed);
+        mbar_wait(&bar_xy[xb], (hcur >> 1) & 1, &failed);
         uint8_t* sX = sXY + (2 * xb) * PANEL;
         uint8_t* sdY = sX + PANEL;
         const uint32_t x0 = smem_u32(sX), y0 = x0 + PANEL;  // phase 1 of this head was issued one step earlier
@@ -358,7 +378,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             for (int of = 16; of > 0; of >>= 1) red += __shfl_xor_sync(0xffffffffu, red, of);
             if (lane == 0) swred[warp] = red;
         }
-        if (hl + 1 < hpg) publish_columns((hl + 1) & 1);
+        if (hl + 1 < hpg) publish_columns((hcur + 1) & 1);
         tc_fence_before();
         fence_async_smem();
         __syncthreads();  // (C) dx staged, TMEM reads done, partial sums and next head's column arrays visible
@@ -375,9 +395,9 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             if (hl + 1 < hpg) {
                 // everyone has read dX1 / dX2, so S and dG of the next head may overwrite them now; its x / dy
                 // tiles were prefetched during this head
-                mbar_wait(&bar_xy[xb ^ 1], ((hl + 1) >> 1) & 1, &failed);
+                mbar_wait(&bar_xy[xb ^ 1], ((hcur + 1) >> 1) & 1, &failed);
                 tc_fence_after();
-                issue_phase1(hl + 1);
+                issue_phase1(hl + 1, true);
             }
             tma_store_2d(&P.mdX, sdX, hh * HP, row0);
             tma_store_commit();
@@ -387,8 +407,10 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             }
         }
     }
-    // ---- group terms: stage sum_h dS as bf16 [i][j] (panel = column half) for the two closing products
-    mbar_wait(&bar_m2b, (hpg - 1) & 1, &failed);  // the last head's products have read Xd / dY
+    // ---- group terms: stage sum_h dS as bf16 [i][j] (panel = column half) in the H / Q panels for the two
+    // closing products
+    const uint32_t hlast = hc + hpg - 1;
+    mbar_wait(&bar_m2b, hlast & 1, &failed);  // the last head's products have read H, Q, Xd / dY
     {
         float v[32];
 #pragma unroll
@@ -396,14 +418,14 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             v[2 * q] = dS2[q].x;
             v[2 * q + 1] = dS2[q].y;
         }
-        store_half_row(sXY + (qc >> 1) * PANEL, row, gch, v);
+        store_half_row(sH + (qc >> 1) * PANEL, row, gch, v);
     }
     tc_fence_before();
     fence_async_smem();
     __syncthreads();
     if (tid == CTL) {
         tc_fence_after();
-        const uint32_t s0 = smem_u32(sXY);
+        const uint32_t s0 = h0a;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {  // dC += dS B : A = dS K-major (K = j), B = B [j][n] MN-major, N = 128
             const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
@@ -414,8 +436,22 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             mma_ss(tdB, smem_desc(s0 + kk * 2048, PANEL, 1024), smem_desc(c0a + kk * 2048, PANEL, 1024), kIdescMM128, true);
         mma_commit(&bar_m3);
     }
-    mbar_wait(&bar_m3, 0, &failed);
+    mbar_wait(&bar_m3, ic & 1, &failed);
     tc_fence_after();
+    // C, B, H, Q and the x / dy buffer of the head before the last are free now: the next item's loads and row
+    // scalars go out before this item's group terms are stored
+    const int st_gg = gg, st_row0 = row0;
+    uint8_t* sdBst = sXY + (2 * (hlast & 1)) * PANEL;  // dB staging: the last head's x / dy buffer
+    item = nitem;
+    hc += hpg;
+    ic += 1;
+    if (more) {
+        k = nk;
+        gg = ngg;
+        bb = nbb;
+        row0 = bb * P.T + k * LT;
+        if (tid == CTL) load_item();
+    }
     {
         uint32_t a[32], b2[32];
         tmem_ld32(tdC + lanes + qc * 32, a);
@@ -427,20 +463,36 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
         store_half_row(sG + (qc >> 1) * PANEL, row, gch, va);
 #pragma unroll
         for (int q = 0; q < 32; ++q) va[q] = __uint_as_float(b2[q]);
-        store_half_row(sXY + (2 + (qc >> 1)) * PANEL, row, gch, va);
+        store_half_row(sdBst + (qc >> 1) * PANEL, row, gch, va);
     }
+    if (more) publish_columns(hc & 1);
     tc_fence_before();
     fence_async_smem();
     __syncthreads();
     if (tid == CTL) {
-        tma_store_2d(&P.mdC, sG, gg * DN, row0);
-        tma_store_2d(&P.mdC, sG + PANEL, gg * DN + 64, row0);
-        tma_store_2d(&P.mdB, sXY + 2 * PANEL, gg * DN, row0);
-        tma_store_2d(&P.mdB, sXY + 3 * PANEL, gg * DN + 64, row0);
+        if (more) {  // S and dG of the next item's first head run while the stores below read their staging panels
+            mbar_wait(&bar_cb, ic & 1, &failed);
+            mbar_wait(&bar_xy[hc & 1], (hc >> 1) & 1, &failed);
+            tc_fence_after();
+            issue_phase1(0, false);
+        }
+        tma_store_2d(&P.mdC, sG, st_gg * DN, st_row0);
+        tma_store_2d(&P.mdC, sG + PANEL, st_gg * DN + 64, st_row0);
+        tma_store_2d(&P.mdB, sdBst, st_gg * DN, st_row0);
+        tma_store_2d(&P.mdB, sdBst + PANEL, st_gg * DN + 64, st_row0);
         tma_store_commit();
-        tma_store_wait_read();  // shared memory must outlive the reads only; the writes complete with the kernel
-        if (failed) atomicExch(P.status, 1);
+        // shared memory must outlive the reads only (the writes complete with the kernel); S and dG of the next
+        // item are announced after this wait, and nobody overwrites the staging panels before that
+        tma_store_wait_read();
+        if (more) {
+            mma_commit(&bar_m1);
+            if (hpg > 1) load_xy(1);
+        }
     }
+    if (!more) break;
+  }
+    if (tid == CTL && failed) atomicExch(P.status, 1);
+    tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tm, 512);
 }

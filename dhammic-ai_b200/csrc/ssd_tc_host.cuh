@@ -92,6 +92,13 @@ inline size_t states_bytes(const Dims& d) { return tile_states_bytes(d) + 2 * ((
         if (e_ != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "%s: %s", what, cudaGetErrorString(e_)); \
     } while (0)
 
+inline int sm_count() {  // SMs of the current device (one persistent CTA each)
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+        return 148;
+    return n;
+}
+
 inline int set_walk_attrs(char* err, size_t errn) {
     cudaError_t e = cudaFuncSetAttribute(walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<0>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<1>::SMEM);
@@ -232,7 +239,8 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
         P.dyx = (float*)(ws + w.dyx); P.rterm = (const float*)(ws + w.rterm); P.status = status; P.T = d.T; P.h = d.h;
         P.hpg = d.hpg; P.nt = nt; P.b = d.b; P.gS = (float*)(ws + w.gS2);
-        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(nt, d.g, d.b), 512, kBwdSmem, st>>>(P));
+        P.items = nt * d.g * d.b;
+        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(std::min(P.items, sm_count())), 512, kBwdSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_walk");
     }
     {
