@@ -111,12 +111,12 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
         tmem_alloc(&tmem_slot, 512);
         tmem_relinquish();
     }
-    auto load_xy = [&](int hl) {
-        const int hh = gg * hpg + hl, xb = (hc + hl) & 1;
+    auto load_xy_at = [&](int hh, int r0, int xb) {
         mbar_expect_tx(&bar_xy[xb], 2 * PANEL);
-        tma_load_2d(sXY + (2 * xb) * PANEL, &P.mX, &bar_xy[xb], hh * HP, row0);
-        tma_load_2d(sXY + (2 * xb + 1) * PANEL, &P.mdY, &bar_xy[xb], hh * HP, row0);
+        tma_load_2d(sXY + (2 * xb) * PANEL, &P.mX, &bar_xy[xb], hh * HP, r0);
+        tma_load_2d(sXY + (2 * xb + 1) * PANEL, &P.mdY, &bar_xy[xb], hh * HP, r0);
     };
+    auto load_xy = [&](int hl) { load_xy_at(gg * hpg + hl, row0, (hc + hl) & 1); };
     auto load_hq = [&](int hl) {
         const int hh = gg * hpg + hl;
         const int srow = (int)((((size_t)bb * P.nt + k) * P.h + hh) * DN);
@@ -142,16 +142,18 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    auto load_item = [&]() {  // C and B of the item, x / dy / H / Q of its first head
+    auto load_item = [&]() {  // C and B of the item, H / Q of its first head
         mbar_expect_tx(&bar_cb, 4 * PANEL);
         tma_load_2d(sC, &P.mC, &bar_cb, gg * DN, row0);
         tma_load_2d(sC + PANEL, &P.mC, &bar_cb, gg * DN + 64, row0);
         tma_load_2d(sB, &P.mB, &bar_cb, gg * DN, row0);
         tma_load_2d(sB + PANEL, &P.mB, &bar_cb, gg * DN + 64, row0);
-        load_xy(0);
         load_hq(0);
     };
-    if (tid == CTL) load_item();
+    if (tid == CTL) {
+        load_xy(0);
+        load_item();
+    }
     const uint32_t tm = tmem_slot;
     // phase 1: S [0,128) dG [128,256); after the mask loop (barrier A) dX1 [0,64) and dX2 [64,128) take the S
     // columns and dYe (bf16 pairs) the dG columns [128,160); persistent over heads: dC [256,384) dB [384,512)
@@ -404,6 +406,10 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             if (hl + 1 < hpg) {
                 load_hq(hl + 1);
                 if (hl + 2 < hpg) load_xy(hl + 2);  // this head's x / dy buffer is free
+            } else if (more) {
+                // x / dy of the next item's first head into the buffer of the head before this one (this head's
+                // buffer stages dB at the end of the item)
+                load_xy_at(ngg * hpg, nbb * P.T + nk * LT, (hcur + 1) & 1);
             }
         }
     }
@@ -470,17 +476,17 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
     fence_async_smem();
     __syncthreads();
     if (tid == CTL) {
-        if (more) {  // S and dG of the next item's first head run while the stores below read their staging panels
-            mbar_wait(&bar_cb, ic & 1, &failed);
-            mbar_wait(&bar_xy[hc & 1], (hc >> 1) & 1, &failed);
-            tc_fence_after();
-            issue_phase1(0, false);
-        }
         tma_store_2d(&P.mdC, sG, st_gg * DN, st_row0);
         tma_store_2d(&P.mdC, sG + PANEL, st_gg * DN + 64, st_row0);
         tma_store_2d(&P.mdB, sdBst, st_gg * DN, st_row0);
         tma_store_2d(&P.mdB, sdBst + PANEL, st_gg * DN + 64, st_row0);
         tma_store_commit();
+        if (more) {  // S and dG of the next item's first head run while the stores read their staging panels
+            mbar_wait(&bar_cb, ic & 1, &failed);
+            mbar_wait(&bar_xy[hc & 1], (hc >> 1) & 1, &failed);
+            tc_fence_after();
+            issue_phase1(0, false);
+        }
         // shared memory must outlive the reads only (the writes complete with the kernel); S and dG of the next
         // item are announced after this wait, and nobody overwrites the staging panels before that
         tma_store_wait_read();
