@@ -320,7 +320,7 @@ def main():
     ms_step = ms_max / args.steps
     # dram read + write of one launch, from the committed ncu capture of the same per-token shape at batch 4
     # (profiles/), scaled by tokens; None for kernels / shapes without a capture
-    ncu_bytes_per_token = {"tc_bwd_walk": 811.3e6 / 16384, "tc_fwd_walk": 438.3e6 / 16384, "tc_bwd_state": 438.0e6 / 16384}
+    ncu_bytes_per_token = {"tc_bwd_walk": 815.2e6 / 16384, "tc_fwd_walk": 438.3e6 / 16384, "tc_bwd_state": 438.0e6 / 16384}
     traffic = None
     if cfg.index == 2 and top in ncu_bytes_per_token:
         traffic = ncu_bytes_per_token[top] * cfg.tokens
