@@ -141,6 +141,19 @@ def test_bf16_config_shapes_reduced(pkg, cabi, oracle, idx, batch, seqlen, path)
         pkg.set_kernel_path("auto")
 
 
+@pytest.mark.parametrize("heads,groups,batch", [(16, 2, 4), (6, 2, 4), (4, 4, 2)])
+def test_tensor_core_path_with_several_items_per_cta(pkg, cabi, oracle, heads, groups, batch):
+    """The backward tile kernel is persistent: with more (tile, group, batch) items than the GPU has SMs some CTAs
+    process two items in a row.  8, 3 and 1 heads per group: the buffer indices and mbarrier phases carried from
+    one item to the next start even, odd, and alternate every item."""
+    seqlen = 128 * 20
+    cfg = replace(pkg.shrink(pkg.CONFIGS[2], batch, seqlen), nheads=heads, ngroups=groups)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert (seqlen // 128) * groups * batch > sms
+    assert pkg.resolved_path_name(cfg) == "tc"
+    check_mamba2(pkg, oracle, cfg, TOL_BF16, init=True, dfinal=True, seed=21)
+
+
 @pytest.mark.parametrize("h,p,n,g,l,T", [(3, 24, 12, 1, 32, 96), (4, 80, 40, 2, 48, 96), (6, 16, 72, 3, 100, 200),
                                          (2, 128, 130, 1, 64, 64), (2, 8, 8, 2, 16, 16)])
 def test_ragged_shapes_fp32(pkg, cabi, oracle, h, p, n, g, l, T):
