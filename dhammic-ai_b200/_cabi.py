@@ -19,7 +19,7 @@ EXPORTS = (
     "ssd_b200_abi_version", "ssd_b200_last_error", "ssd_b200_workspace_bytes", "ssd_b200_states_bytes",
     "ssd_b200_resolve_path",
     "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix",
-    "ssd_b200_m3_prologue_fwd", "ssd_b200_m3_skip_fwd", "ssd_b200_m3_prologue_bwd", "ssd_b200_rope_fwd", "ssd_b200_rope_bwd",
+    "ssd_b200_m3_prologue_fwd", "ssd_b200_m3_skip_fwd", "ssd_b200_m3_prologue_bwd", "ssd_b200_m3_chain_ws_floats", "ssd_b200_m3_chain_bwd", "ssd_b200_rope_fwd", "ssd_b200_rope_bwd",
     "ssd_b200_trapezoid_ws_floats", "ssd_b200_trapezoid_fwd", "ssd_b200_trapezoid_bwd",
     "ssd_b200_rmsnorm_ws_floats", "ssd_b200_rmsnorm_fwd", "ssd_b200_rmsnorm_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status",
     "ssd_b200_launch_count", "ssd_b200_profile_enable", "ssd_b200_profile_kernels", "ssd_b200_profile_kernel_name",
@@ -108,6 +108,10 @@ def load() -> C.CDLL:
     lib.ssd_b200_m3_skip_fwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 8
     lib.ssd_b200_m3_prologue_bwd.restype = C.c_int
     lib.ssd_b200_m3_prologue_bwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 21
+    lib.ssd_b200_m3_chain_ws_floats.restype = C.c_size_t
+    lib.ssd_b200_m3_chain_ws_floats.argtypes = [C.POINTER(Shape)]
+    lib.ssd_b200_m3_chain_bwd.restype = C.c_int
+    lib.ssd_b200_m3_chain_bwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 13
     lib.ssd_b200_fwd_static_scratch.restype = C.c_int
     lib.ssd_b200_fwd_static_scratch.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
     lib.ssd_b200_static_scratch_bytes.restype = C.c_size_t

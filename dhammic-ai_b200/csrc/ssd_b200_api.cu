@@ -672,6 +672,31 @@ int ssd_b200_m3_skip_fwd(const ssd_b200_shape* shape, const void* y_scan, const 
                                          : m3_skip_impl<float>(d, y_scan, x, D, dt, lam, sdot, y, st);
 }
 
+size_t ssd_b200_m3_chain_ws_floats(const ssd_b200_shape* shape) {
+    if (!shape || shape->batch <= 0 || shape->seqlen <= 0 || shape->nheads <= 0) return 0;
+    const size_t M = (size_t)shape->batch * shape->seqlen;
+    return 2 * ((M + ssd::m3::CHAIN_ROWS - 1) / ssd::m3::CHAIN_ROWS) * (size_t)shape->nheads;
+}
+
+int ssd_b200_m3_chain_bwd(const ssd_b200_shape* shape, const float* dw, const float* dyx, const float* sdot, const float* dt,
+                          const float* lam, const float* da, const float* A_head, float* dlam, float* ddt, float* dA_head,
+                          float* dD, float* ws, void* stream) {
+    if (int rc = check_shape(shape)) return rc;
+    if (!dw || !dyx || !sdot || !dt || !lam || !da || !A_head || !dlam || !ddt || !dA_head || !ws)
+        return fail(SSD_B200_EINVAL, "null pointer");
+    ssd::Dims d = dims_of(*shape);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t M = (size_t)d.b * d.T, nblk = (M + ssd::m3::CHAIN_ROWS - 1) / ssd::m3::CHAIN_ROWS;
+    float* pA = ws;
+    float* pD = ws + nblk * d.h;
+    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, ssd::m3::chain_bwd_kernel<<<(unsigned)nblk, 256, 0, st>>>(dw, dyx, sdot, dt, lam, da, A_head, dlam, ddt, pA, pD, M, d.T, d.h, d.g));
+    SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<d.h, 256, 0, st>>>(pA, dA_head, (int)nblk, d.h));
+    if (dD) SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<d.h, 256, 0, st>>>(pD, dD, (int)nblk, d.h));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(SSD_B200_ECUDA, cudaGetErrorString(e));
+    return SSD_B200_OK;
+}
+
 int ssd_b200_m3_prologue_bwd(const ssd_b200_shape* shape, const void* x, const void* dy, const float* dt, const float* lam,
                              const float* D, const void* B, const void* C, const float* cum, const float* sdot,
                              const void* dxw, const void* dBr, const void* dCr, void* dx, float* dw, float* dyx, void* dB,

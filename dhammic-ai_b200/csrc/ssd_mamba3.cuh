@@ -390,5 +390,60 @@ __global__ void __launch_bounds__(256) xw_bwd_kernel(const T* __restrict__ x, co
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Chain rule of the single-scan form on the (b,T,h) tensors.  With w = lam dt + u, u[t] = (1 - lam[t+1]) dt[t+1]
+// (u[T-1] = 0), the diagonal term -u s x and a = dt A_head:
+//     v[t]    = dw[t] - s[t] dyx[t]                     (d/du: through w and through the diagonal term)
+//     dlam[t] = (dw[t] - v[t-1]) dt[t]                  (v[-1] = 0)
+//     ddt[t]  = dw[t] lam[t] + v[t-1] (1 - lam[t]) + da[t] A_head
+//     dA_head = sum_{b,t} da dt,   dD = sum_{b,t} dyx
+// Thread = (row group, head column) over CHAIN_ROWS rows of (b*T); per-block partial sums of the two head
+// gradients, added over the row groups in a fixed order (a second kernel adds the blocks).
+// ------------------------------------------------------------------------------------------
+constexpr int CHAIN_ROWS = 64;
+
+__global__ void __launch_bounds__(256) chain_bwd_kernel(const float* __restrict__ dw, const float* __restrict__ dyx,
+                                                        const float* __restrict__ sdot, const float* __restrict__ dt,
+                                                        const float* __restrict__ lam, const float* __restrict__ da,
+                                                        const float* __restrict__ A_head, float* __restrict__ dlam,
+                                                        float* __restrict__ ddt, float* __restrict__ part_A,
+                                                        float* __restrict__ part_D, size_t M, int Tlen, int H, int G) {
+    __shared__ float sred[2][256];
+    const size_t r0 = (size_t)blockIdx.x * CHAIN_ROWS;
+    const int cols = H < 256 ? H : 256, groups = 256 / cols, hpg = H / G;
+    const int gi = threadIdx.x / cols, hc = threadIdx.x - gi * cols;
+    for (int h0 = 0; h0 < H; h0 += cols) {
+        const int hh = h0 + hc;
+        float sA = 0.f, sD = 0.f;
+        if (gi < groups && hh < H) {
+            const float Ah = A_head[hh];
+            const int gq = hh / hpg;
+            for (int r = gi; r < CHAIN_ROWS && r0 + r < M; r += groups) {
+                const size_t rowi = r0 + r, i = rowi * H + hh;
+                const int t = (int)(rowi % (size_t)Tlen);
+                const float vprev = t > 0 ? dw[i - H] - sdot[(rowi - 1) * G + gq] * dyx[i - H] : 0.f;
+                const float dwi = dw[i], li = lam[i], di = dt[i], dai = da[i];
+                dlam[i] = (dwi - vprev) * di;
+                ddt[i] = dwi * li + vprev * (1.f - li) + dai * Ah;
+                sA += dai * di;
+                sD += dyx[i];
+            }
+        }
+        sred[0][threadIdx.x] = sA;
+        sred[1][threadIdx.x] = sD;
+        __syncthreads();
+        if (gi == 0 && hh < H) {
+            float ta = 0.f, td = 0.f;
+            for (int q = 0; q < groups; ++q) {
+                ta += sred[0][q * cols + hc];
+                td += sred[1][q * cols + hc];
+            }
+            part_A[(size_t)blockIdx.x * H + hh] = ta;
+            part_D[(size_t)blockIdx.x * H + hh] = td;
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace m3
 }  // namespace ssd

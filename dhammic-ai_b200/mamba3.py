@@ -16,15 +16,14 @@ which halves the scan work and never materialises shift(x) * beta or shift(B_r).
 their backward are CUDA kernels of the library (``ssd_b200_m3_prologue_fwd`` / ``_skip_fwd`` / ``_prologue_bwd``);
 the scan runs on the scan kernels in operator form (one head per group after the per-head rotation).  Unlike
 the reference's cached second call (src/kernels/ssd_scan.py:494-500) the decay gradient is the full one of the
-expression above.  Only the chain rule on (b,T,h)-sized tensors (through w, u and a) is left to tensor
-operations.
+expression above; the chain rule on the (b,T,h)-sized tensors (through w, u and a) is one more kernel
+(``ssd_b200_m3_chain_bwd``).
 """
 from __future__ import annotations
 
 import ctypes as C
 
 import torch
-import torch.nn.functional as F
 from torch import Tensor
 
 from . import _cabi
@@ -97,14 +96,14 @@ class _SSDMamba3(torch.autograd.Function):
                                                      _ptr(dyx), _ptr(dB), _ptr(dC), _ptr(dang), _ptr(dcum), _ptr(seg),
                                                      _stream(dev)))
             # chain rule through w = lam dt + u, u[t] = (1 - lam[t+1]) dt[t+1], the diagonal term -u s x and
-            # a = dt A_head   [(b,T,h)-sized tensors]
-            s_h = sdot.repeat_interleave(h // g, dim=2)
-            v = dw - s_h * dyx                              # d/du: through w and through the diagonal term
-            v_prev = F.pad(v[:, :-1], (0, 0, 1, 0))         # u[t-1] depends on lam[t], dt[t]
-            dlam = (dw - v_prev) * dt
-            ddt = dw * lam + v_prev * (1.0 - lam) + da * Ah
-            dAh = (da * dt).sum(dim=(0, 1))
-            dD = dyx.sum(dim=(0, 1)) if ctx.has_D else None
+            # a = dt A_head, with the two per-head sums, in one kernel on the (b,T,h) tensors
+            dlam, ddt = torch.empty_like(dw), torch.empty_like(dw)
+            dAh = torch.empty(h, dtype=torch.float32, device=dev)
+            dD = torch.empty(h, dtype=torch.float32, device=dev) if ctx.has_D else None
+            ws = torch.empty(int(lib.ssd_b200_m3_chain_ws_floats(C.byref(ctx.shape_struct))), dtype=torch.float32, device=dev)
+            _cabi.check(lib.ssd_b200_m3_chain_bwd(C.byref(ctx.shape_struct), _ptr(dw), _ptr(dyx), _ptr(sdot), _ptr(dt),
+                                                  _ptr(lam), _ptr(da.contiguous()), _ptr(Ah), _ptr(dlam), _ptr(ddt), _ptr(dAh),
+                                                  _ptr(dD), _ptr(ws), _stream(dev)))
         dtd, ahd, angd, lamd, dd = ctx.in_dtypes
         return (dx, ddt.to(dtd), dAh.to(ahd), dB, dC, None if dD is None else dD.to(dd), dang.to(angd), dlam.to(lamd),
                 None)

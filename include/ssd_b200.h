@@ -244,6 +244,17 @@ int ssd_b200_m3_prologue_fwd(const ssd_b200_shape *shape, const void *x, const f
                              float *dA, void *Br, void *Cr, float *sdot, float *cum, float *segsum_ws, void *stream);
 int ssd_b200_m3_skip_fwd(const ssd_b200_shape *shape, const void *y_scan, const void *x, const float *D, const float *dt,
                          const float *lam, const float *sdot, void *y, void *stream);
+/* Chain rule of the single-scan form on the (b,T,h) fp32 tensors, after ssd_b200_m3_prologue_bwd (dw, dyx) and the
+ * scan backward (da): with v[t] = dw[t] - s[t] dyx[t] (s = sdot of the head's group) and v[-1] = 0,
+ *   dlam = (dw - v[t-1]) dt,   ddt = dw lam + v[t-1] (1 - lam) + da A_head,
+ *   dA_head[h] = sum_{b,t} da dt,   dD[h] = sum_{b,t} dyx  (dD may be null).
+ * The sums over (b,t) are two-stage with a fixed order (deterministic).  ws: ssd_b200_m3_chain_ws_floats(shape)
+ * floats of scratch.  In the reference these steps are autograd through the block's element-wise expressions
+ * (src/mamba_base_engine.py:150-187). */
+size_t ssd_b200_m3_chain_ws_floats(const ssd_b200_shape *shape);
+int ssd_b200_m3_chain_bwd(const ssd_b200_shape *shape, const float *dw, const float *dyx, const float *sdot,
+                          const float *dt, const float *lam, const float *da, const float *A_head, float *dlam,
+                          float *ddt, float *dA_head, float *dD, float *ws, void *stream);
 int ssd_b200_m3_prologue_bwd(const ssd_b200_shape *shape, const void *x, const void *dy, const float *dt,
                              const float *lam, const float *D, const void *B, const void *C, const float *cum,
                              const float *sdot, const void *dxw, const void *dBr, const void *dCr, void *dx, float *dw,
