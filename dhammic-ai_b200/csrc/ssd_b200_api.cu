@@ -390,13 +390,12 @@ int m3_bwd_impl(const ssd::Dims& d, const void* x, const void* dy, const float* 
     const int E = d.h * (d.n / 2), nseg = (d.T + SEG - 1) / SEG;
     const size_t rows = (size_t)d.b * d.T * d.h;
     M3_ROW_DISPATCH(xw_bwd_kernel, (const T*)x, (const T*)dy, (const T*)dxw, dt, lam, D, sdot, (T*)dx, dw, dyx, d.T, d.h, d.hpg, d.p, rows);
-    const size_t sm = ((size_t)2 * d.h * d.n + d.h) * sizeof(float);
     if (d.n % VecOf<T>::N == 0) {
-        if (int rc = set_smem(rope_bwd_kernel<T, VecOf<T>::N>, sm, "rope_bwd")) return rc;
-        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, VecOf<T>::N><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n)));
+        const size_t items = (size_t)d.b * d.T * d.g * (d.n / VecOf<T>::N);
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, VecOf<T>::N><<<(unsigned)((items + 255) / 256), 256, 0, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n, items)));
     } else {
-        if (int rc = set_smem(rope_bwd_kernel<T, 2>, sm, "rope_bwd")) return rc;
-        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, 2><<<dim3(d.T, d.b), 256, sm, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n)));
+        const size_t items = (size_t)d.b * d.T * d.g * (d.n / 2);
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, 2><<<(unsigned)((items + 255) / 256), 256, 0, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n, items)));
     }
     dim3 gs(nseg, (E + 255) / 256, d.b);
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<float><<<gs, 256, 0, st>>>(dcum, segsum, d.T, E));

@@ -213,74 +213,64 @@ __device__ __forceinline__ float u_of(const float* __restrict__ dt, const float*
 
 // Backward of the rotation and of the diagonal term.
 //   d v = R(-theta) d out ;  d theta = -d out1 * out2 + d out2 * out1   (summed over B and C)
-// dB / dC are summed over the heads of a group through shared memory (fixed order, deterministic); the
-// diagonal term -u s x contributes d s = -u <dy, x> per head, i.e. (sum_h d s) C to dB and (sum_h d s) B to dC.
+// Thread = (position, group, V consecutive state columns); it walks the heads of its group, so dB / dC are
+// summed over the heads in registers in a fixed order (deterministic), B and C are read once per group, and
+// there is no shared memory or block barrier.  The diagonal term -u s x contributes d s = -u <dy, x> per head,
+// i.e. (sum_h d s) C to dB and (sum_h d s) B to dC.
 template <class T, int V>
 __global__ void __launch_bounds__(256) rope_bwd_kernel(const T* __restrict__ B, const T* __restrict__ C,
                                                        const float* __restrict__ cum, const T* __restrict__ dBr,
                                                        const T* __restrict__ dCr, const float* __restrict__ dyx,
                                                        const float* __restrict__ dt, const float* __restrict__ lam,
                                                        T* __restrict__ dB, T* __restrict__ dC, float* __restrict__ dcum,
-                                                       int Tlen, int h, int g, int n) {
-    extern __shared__ float sm[];  // [2][h][n]: d(un-rotated) B and C per head, then [h] d s
-    const int t = blockIdx.x, bb = blockIdx.y;
+                                                       int Tlen, int h, int g, int n, size_t items) {
+    const size_t w = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (w >= items) return;
     const int half = n / 2, hpg = h / g, upr = n / V;
-    const size_t row = (size_t)bb * Tlen + t;
-    float* sB = sm;
-    float* sC = sm + (size_t)h * n;
-    float* sds = sC + (size_t)h * n;
-    for (int hh = threadIdx.x; hh < h; hh += 256) sds[hh] = -u_of(dt, lam, row * h + hh, t, Tlen, h) * dyx[row * h + hh];
-    for (int e = threadIdx.x; e < h * upr; e += 256) {
-        const int hh = e / upr, j0 = (e - hh * upr) * V;
-        const int gg = hh / hpg;
-        float bv[V], cv[V], db[V], dc[V], ub[V], uc[V];
-        const size_t ib = (row * g + gg) * n + j0;
-        load_elems<T, V>(B + ib, bv);
-        load_elems<T, V>(C + ib, cv);
-        const size_t o = (row * h + hh) * n + j0;
-        load_elems<T, V>(dBr + o, db);
-        load_elems<T, V>(dCr + o, dc);
-        float ang[V / 2], dth[V / 2];
-        load_angles<V / 2>(cum + (row * h + hh) * half + j0 / 2, ang);
+    const int j0 = (int)(w % upr) * V;
+    const size_t rg = w / upr;          // (b, t, g) flattened
+    const int gg = (int)(rg % g);
+    const size_t row = rg / g;
+    const int t = (int)(row % (size_t)Tlen);
+    float bv[V], cv[V], ab[V], ac[V];
+    const size_t ib = rg * n + j0;
+    load_elems<T, V>(B + ib, bv);
+    load_elems<T, V>(C + ib, cv);
+#pragma unroll
+    for (int q = 0; q < V; ++q) ab[q] = ac[q] = 0.f;
+    float ds = 0.f;
+#pragma unroll 2
+    for (int hl = 0; hl < hpg; ++hl) {
+        const size_t ih = row * h + gg * hpg + hl;
+        float db[V], dc[V], ang[V / 2], dth[V / 2];
+        load_elems<T, V>(dBr + ih * n + j0, db);
+        load_elems<T, V>(dCr + ih * n + j0, dc);
+        load_angles<V / 2>(cum + ih * half + j0 / 2, ang);
+        ds += -u_of(dt, lam, ih, t, Tlen, h) * dyx[ih];
 #pragma unroll
         for (int q = 0; q < V / 2; ++q) {
-            float s, c;
-            sincos_reduced(ang[q], &s, &c);
+            float sn, c;
+            sincos_reduced(ang[q], &sn, &c);
             const float b1 = bv[2 * q], b2 = bv[2 * q + 1], c1 = cv[2 * q], c2 = cv[2 * q + 1];
             const float db1 = db[2 * q], db2 = db[2 * q + 1], dc1 = dc[2 * q], dc2 = dc[2 * q + 1];
-            const float ob1 = b1 * c - b2 * s, ob2 = b1 * s + b2 * c;
-            const float oc1 = c1 * c - c2 * s, oc2 = c1 * s + c2 * c;
+            const float ob1 = b1 * c - b2 * sn, ob2 = b1 * sn + b2 * c;
+            const float oc1 = c1 * c - c2 * sn, oc2 = c1 * sn + c2 * c;
             dth[q] = (-db1 * ob2 + db2 * ob1) + (-dc1 * oc2 + dc2 * oc1);
-            ub[2 * q] = c * db1 + s * db2;
-            ub[2 * q + 1] = -s * db1 + c * db2;
-            uc[2 * q] = c * dc1 + s * dc2;
-            uc[2 * q + 1] = -s * dc1 + c * dc2;
+            ab[2 * q] += c * db1 + sn * db2;
+            ab[2 * q + 1] += -sn * db1 + c * db2;
+            ac[2 * q] += c * dc1 + sn * dc2;
+            ac[2 * q + 1] += -sn * dc1 + c * dc2;
         }
-        store_angles<V / 2>(dcum + (row * h + hh) * half + j0 / 2, dth);
-        if constexpr (V >= 4) {
-            store_f32<V>(sB + hh * n + j0, ub);
-            store_f32<V>(sC + hh * n + j0, uc);
-        } else {
+        store_angles<V / 2>(dcum + ih * half + j0 / 2, dth);
+    }
+    float ob[V], oc[V];
 #pragma unroll
-            for (int q = 0; q < V; ++q) {
-                sB[hh * n + j0 + q] = ub[q];
-                sC[hh * n + j0 + q] = uc[q];
-            }
-        }
+    for (int q = 0; q < V; ++q) {
+        ob[q] = ab[q] + ds * cv[q];
+        oc[q] = ac[q] + ds * bv[q];
     }
-    __syncthreads();
-    for (int e = threadIdx.x; e < g * n; e += 256) {
-        const int gg = e / n, nn = e - gg * n;
-        float ab = 0.f, ac = 0.f, ds = 0.f;
-        for (int hl = 0; hl < hpg; ++hl) {
-            ab += sB[(gg * hpg + hl) * n + nn];
-            ac += sC[(gg * hpg + hl) * n + nn];
-            ds += sds[gg * hpg + hl];
-        }
-        const size_t ib = (row * g + gg) * n + nn;
-        dB[ib] = from_f<T>(ab + ds * to_f(C[ib]));
-        dC[ib] = from_f<T>(ac + ds * to_f(B[ib]));
-    }
+    store_elems<T, V>(dB + ib, ob);
+    store_elems<T, V>(dC + ib, oc);
 }
 
 // ------------------------------------------------------------------------------------------
