@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(128) rope_op_bwd_kernel(const T* __restrict__ 
 // already rounded to the working dtype (the reference casts them, src/kernels/trapezoidal.py:241-243).
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ float softplus_f(float s) { return fmaxf(s, 0.f) + log1pf(__expf(-fabsf(s))); }
-__device__ __forceinline__ float sigmoid_f(float s) { return 1.f / (1.f + __expf(-s)); }
+__device__ __forceinline__ float sigmoid_f(float s) { return __fdividef(1.f, 1.f + __expf(-s)); }
 
 template <class T>
 __global__ void __launch_bounds__(256) trapezoid_fwd_kernel(const T* __restrict__ dt_raw, const T* __restrict__ lam_raw,
@@ -189,6 +189,20 @@ __global__ void __launch_bounds__(256) trapezoid_bwd_kernel(const T* __restrict_
 //   backward:  dn = do [* silu(z)],  s = sum_j w_j x_j dn_j,  dx_i = r (w_i dn_i - x_i r^2 s / D),
 //              dz_j = do_j n_j silu'(z_j),  dw_j = sum_rows x_j r dn_j  (a separate column reduction).
 // ------------------------------------------------------------------------------------------
+// V consecutive weights (16-byte vector loads when V is a multiple of 4: the column index then is too)
+template <int V>
+__device__ __forceinline__ void load_w(const float* __restrict__ p, float (&f)[V]) {
+    if constexpr (V % 4 == 0) {
+#pragma unroll
+        for (int q = 0; q < V; q += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(p + q);
+            f[q] = v.x; f[q + 1] = v.y; f[q + 2] = v.z; f[q + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < V; ++q) f[q] = p[q];
+    }
+}
 __device__ __forceinline__ float silu_f(float z) { return z * sigmoid_f(z); }
 __device__ __forceinline__ float silu_grad_f(float z) {
     const float sg = sigmoid_f(z);
@@ -217,16 +231,17 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const T* __restrict__ 
     if (lane == 0) rstd[row] = r;
 #pragma unroll 4
     for (int c = lane * V; c < D; c += 32 * V) {
-        float v[V], o[V];
+        float v[V], o[V], wv[V];
         load_elems1<T, V>(xr + c, v);
+        load_w<V>(w + c, wv);
         if (z) {
             float g[V];
             load_elems1<T, V>(z + row * D + c, g);
 #pragma unroll
-            for (int q = 0; q < V; ++q) o[q] = v[q] * r * w[c + q] * silu_f(g[q]);
+            for (int q = 0; q < V; ++q) o[q] = v[q] * r * wv[q] * silu_f(g[q]);
         } else {
 #pragma unroll
-            for (int q = 0; q < V; ++q) o[q] = v[q] * r * w[c + q];
+            for (int q = 0; q < V; ++q) o[q] = v[q] * r * wv[q];
         }
         store_elems1<T, V>(out + row * D + c, o);
     }
@@ -245,9 +260,10 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const T* __restrict__ 
     float s = 0.f;
 #pragma unroll 4
     for (int c = lane * V; c < D; c += 32 * V) {
-        float v[V], g[V];
+        float v[V], g[V], wv[V];
         load_elems1<T, V>(xr + c, v);
         load_elems1<T, V>(dout + row * D + c, g);
+        load_w<V>(w + c, wv);
         if (z) {
             float zz[V];
             load_elems1<T, V>(z + row * D + c, zz);
@@ -255,28 +271,29 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const T* __restrict__ 
             for (int q = 0; q < V; ++q) g[q] *= silu_f(zz[q]);
         }
 #pragma unroll
-        for (int q = 0; q < V; ++q) s += w[c + q] * v[q] * g[q];
+        for (int q = 0; q < V; ++q) s += wv[q] * v[q] * g[q];
     }
 #pragma unroll
     for (int of = 16; of > 0; of >>= 1) s += __shfl_xor_sync(0xffffffffu, s, of);
     const float k = r * r * s / (float)D;
 #pragma unroll 4
     for (int c = lane * V; c < D; c += 32 * V) {
-        float v[V], g[V], o[V];
+        float v[V], g[V], o[V], wv[V];
         load_elems1<T, V>(xr + c, v);
         load_elems1<T, V>(dout + row * D + c, g);
+        load_w<V>(w + c, wv);
         if (z) {
             float zz[V], oz[V];
             load_elems1<T, V>(z + row * D + c, zz);
 #pragma unroll
             for (int q = 0; q < V; ++q) {
-                oz[q] = g[q] * (v[q] * r * w[c + q]) * silu_grad_f(zz[q]);
+                oz[q] = g[q] * (v[q] * r * wv[q]) * silu_grad_f(zz[q]);
                 g[q] *= silu_f(zz[q]);
             }
             store_elems1<T, V>(dz + row * D + c, oz);
         }
 #pragma unroll
-        for (int q = 0; q < V; ++q) o[q] = r * (w[c + q] * g[q] - v[q] * k);
+        for (int q = 0; q < V; ++q) o[q] = r * (wv[q] * g[q] - v[q] * k);
         store_elems1<T, V>(dx + row * D + c, o);
     }
 }
