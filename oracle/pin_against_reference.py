@@ -148,8 +148,11 @@ def pin_mamba3(S, ref_root: Path, out_dir: Path, say):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("REFERENCE_ROOT"),
+                    help="root of the reference checkout (or set REFERENCE_ROOT)")
     args = ap.parse_args()
+    if not args.reference:
+        ap.error("pass --reference or set REFERENCE_ROOT")
     ref_root = Path(args.reference)
     S = load_reference(ref_root)
     out_dir = ROOT / "tests" / "golden"
