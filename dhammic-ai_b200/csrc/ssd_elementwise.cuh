@@ -59,46 +59,76 @@ __global__ void __launch_bounds__(256) rope_op_fwd_kernel(const T* __restrict__ 
     }
 }
 
-// One block per (b, t); a thread owns V/2 pair indices and walks the heads, so the sum over heads of the
-// broadcast case stays in registers (fixed order).
+// One block per (b, t); thread = (head slice, V/2 pair indices): it walks the heads of its slice, so the sum over
+// heads of the broadcast case stays in registers per slice; the slices are then added in a fixed order through
+// shared memory (deterministic).  With D / V pair groups per head, 128 / (D / V) slices share the heads.
 template <class T, int V>
 __global__ void __launch_bounds__(128) rope_op_bwd_kernel(const T* __restrict__ x, const float* __restrict__ ang,
                                                           const T* __restrict__ dy, T* __restrict__ dx,
                                                           float* __restrict__ dang, int H, int D, int aH) {
+    __shared__ float sacc[128 * (V / 2)];
     const size_t bt = blockIdx.x;
     const int half = D / 2, upr = D / V;
-    for (int u = threadIdx.x; u < upr; u += 128) {
+    const int slices = upr >= 128 ? 1 : 128 / upr;
+    const int sl = upr >= 128 ? 0 : threadIdx.x / upr;
+    const int hps = (H + slices - 1) / slices;
+    const int h_lo = sl * hps, h_hi = min(H, h_lo + hps);
+    const int ustep = upr >= 128 ? 128 : upr;
+    for (int u0 = 0; u0 < upr; u0 += ustep) {
+        const int u = u0 + (upr >= 128 ? (int)threadIdx.x : (int)threadIdx.x - sl * upr);
+        const bool live = sl < slices && u < upr;
         const int j0 = u * V;
         float acc[V / 2];
 #pragma unroll
         for (int q = 0; q < V / 2; ++q) acc[q] = 0.f;
-        float s[V / 2], c[V / 2];
-        if (aH == 1) {
+        if (live) {
+            float s[V / 2], c[V / 2];
+            if (aH == 1) {
 #pragma unroll
-            for (int q = 0; q < V / 2; ++q) sincosf(ang[bt * half + j0 / 2 + q], &s[q], &c[q]);
-        }
-        for (int hh = 0; hh < H; ++hh) {
-            if (aH != 1) {
-#pragma unroll
-                for (int q = 0; q < V / 2; ++q) sincosf(ang[(bt * H + hh) * half + j0 / 2 + q], &s[q], &c[q]);
+                for (int q = 0; q < V / 2; ++q) sincosf(ang[bt * half + j0 / 2 + q], &s[q], &c[q]);
             }
-            float v[V], g[V], o[V];
-            load_elems<T, V>(x + (bt * H + hh) * D + j0, v);
-            load_elems<T, V>(dy + (bt * H + hh) * D + j0, g);
+            for (int hh = h_lo; hh < h_hi; ++hh) {
+                if (aH != 1) {
 #pragma unroll
-            for (int q = 0; q < V / 2; ++q) {
-                const float x1 = v[2 * q], x2 = v[2 * q + 1], ge = g[2 * q], go = g[2 * q + 1];
-                o[2 * q] = c[q] * ge + s[q] * go;
-                o[2 * q + 1] = -s[q] * ge + c[q] * go;
-                const float d = ge * (-s[q] * x1 - c[q] * x2) + go * (c[q] * x1 - s[q] * x2);
-                if (aH == 1) acc[q] += d;
-                else dang[(bt * H + hh) * half + j0 / 2 + q] = d;
+                    for (int q = 0; q < V / 2; ++q) sincosf(ang[(bt * H + hh) * half + j0 / 2 + q], &s[q], &c[q]);
+                }
+                float v[V], g[V], o[V];
+                load_elems<T, V>(x + (bt * H + hh) * D + j0, v);
+                load_elems<T, V>(dy + (bt * H + hh) * D + j0, g);
+#pragma unroll
+                for (int q = 0; q < V / 2; ++q) {
+                    const float x1 = v[2 * q], x2 = v[2 * q + 1], ge = g[2 * q], go = g[2 * q + 1];
+                    o[2 * q] = c[q] * ge + s[q] * go;
+                    o[2 * q + 1] = -s[q] * ge + c[q] * go;
+                    const float d = ge * (-s[q] * x1 - c[q] * x2) + go * (c[q] * x1 - s[q] * x2);
+                    if (aH == 1) acc[q] += d;
+                    else dang[(bt * H + hh) * half + j0 / 2 + q] = d;
+                }
+                store_elems<T, V>(dx + (bt * H + hh) * D + j0, o);
             }
-            store_elems<T, V>(dx + (bt * H + hh) * D + j0, o);
         }
-        if (aH == 1) {
+        if (aH == 1) {  // block-uniform
+            if (slices == 1) {
+                if (live) {
 #pragma unroll
-            for (int q = 0; q < V / 2; ++q) dang[bt * half + j0 / 2 + q] = acc[q];
+                    for (int q = 0; q < V / 2; ++q) dang[bt * half + j0 / 2 + q] = acc[q];
+                }
+            } else {
+                if (live) {
+#pragma unroll
+                    for (int q = 0; q < V / 2; ++q) sacc[(sl * upr + u) * (V / 2) + q] = acc[q];
+                }
+                __syncthreads();
+                if (live && sl == 0) {
+#pragma unroll
+                    for (int q = 0; q < V / 2; ++q) {
+                        float t = 0.f;
+                        for (int k = 0; k < slices; ++k) t += sacc[(k * upr + u) * (V / 2) + q];
+                        dang[bt * half + j0 / 2 + q] = t;
+                    }
+                }
+                __syncthreads();
+            }
         }
     }
 }
