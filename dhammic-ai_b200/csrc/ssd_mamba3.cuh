@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(256) scanT_segsum_kernel(const T* __restrict__
     const int t0 = seg * SEG, t1 = min(Tlen, t0 + SEG);
     const T* p = in + ((size_t)bb * Tlen + t0) * E + e;
     float s = 0.f;
-    for (int t = t0; t < t1; ++t, p += E) s += to_f(*p);
+#pragma unroll 8
+    for (int t = t0; t < t1; ++t, p += E) s += to_f(*p);  // eight loads in flight per thread
     segsum[((size_t)bb * nseg + seg) * E + e] = s;
 }
 
@@ -109,12 +110,14 @@ __global__ void __launch_bounds__(256) scanT_apply_kernel(const TI* __restrict__
     }
     const int t0 = seg * SEG, t1 = min(Tlen, t0 + SEG);
     if (!reverse) {
+#pragma unroll 8
         for (int t = t0; t < t1; ++t) {
             const size_t o = ((size_t)bb * Tlen + t) * E + e;
             run += to_f(in[o]);
             out[o] = from_f<TO>(sign * run);
         }
     } else {
+#pragma unroll 8
         for (int t = t1 - 1; t >= t0; --t) {
             const size_t o = ((size_t)bb * Tlen + t) * E + e;
             run += to_f(in[o]);
