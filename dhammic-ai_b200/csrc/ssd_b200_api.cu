@@ -12,7 +12,6 @@
 #include "ssd_elementwise.cuh"
 
 #include <atomic>
-#include <mutex>
 #include <vector>
 
 namespace ssd {
@@ -572,30 +571,22 @@ int ssd_b200_bwd(const ssd_b200_bwd_args* a, void* stream) {
 // carries its own scratch: one fixed array in device memory, part of the loaded module.
 //
 // The array below exists once per GPU that loads this library and stays until the process exits.
-// In host code its name is only a handle, not a device address; the address on the current device
-// comes from cudaGetSymbolAddress, looked up the first time the entry point runs on that device.
+// In host code its name is only a handle, not a device address; the address comes from
+// cudaGetSymbolAddress, which is asked on EVERY call: the answer belongs to the CUDA context that is
+// current on the calling thread, so a value remembered from an earlier call could be stale after a
+// device reset or belong to another context on the same GPU.  The lookup is a host-side table read
+// and allocates nothing; the very first one on a device loads the library's device code there.
 // ------------------------------------------------------------------------------------------
 #define SSD_B200_STATIC_SCRATCH_BYTES (64u << 20)
 static __device__ __align__(256) unsigned char g_static_scratch[SSD_B200_STATIC_SCRATCH_BYTES];
 
 namespace {
-std::mutex g_static_scratch_mu;
-void* g_static_scratch_addr[64] = {};  // per device ordinal, filled on first use
-
 int static_scratch_on_current_device(void** out) {
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return fail(SSD_B200_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
-    if (dev < 0 || dev >= 64) return fail(SSD_B200_EUNSUPPORTED, "device ordinal %d out of range", dev);
-    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
-    if (!g_static_scratch_addr[dev]) {
-        void* p = nullptr;
-        e = cudaGetSymbolAddress(&p, g_static_scratch);
-        if (e != cudaSuccess || !p)
-            return fail(SSD_B200_ECUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
-        g_static_scratch_addr[dev] = p;
-    }
-    *out = g_static_scratch_addr[dev];
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p)
+        return fail(SSD_B200_ECUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    *out = p;
     return 0;
 }
 }  // namespace
@@ -620,20 +611,13 @@ int ssd_b200_fwd_static_scratch(const ssd_b200_fwd_args* a, void* stream) {
 
 size_t ssd_b200_static_scratch_bytes(void) { return (size_t)SSD_B200_STATIC_SCRATCH_BYTES; }
 
-#ifdef SSD_TC_TIMELINE
-int ssd_b200_debug_wtimeline(long long* out, int n) {
-    if (n > 4096) n = 4096;
-    return cudaMemcpyFromSymbol(out, ssd::tc::g_wtimeline, (size_t)n * sizeof(long long)) == cudaSuccess ? 0 : -4;
-}
-int ssd_b200_debug_timeline(long long* out, int n) {
-    if (n > 4096) n = 4096;
-    return cudaMemcpyFromSymbol(out, ssd::tc::g_timeline, (size_t)n * sizeof(long long)) == cudaSuccess ? 0 : -4;
-}
-#endif
-
 int ssd_b200_device_status(const ssd_b200_shape* shape, const void* workspace, void* stream) {
     if (int rc = check_shape(shape)) return rc;
-    if (!workspace) return fail(SSD_B200_EINVAL, "workspace is null");
+    if (!workspace) {  // the caller of ssd_b200_fwd_static_scratch never sees the scratch address
+        void* scratch = nullptr;
+        if (int rc = static_scratch_on_current_device(&scratch)) return rc;
+        workspace = scratch;
+    }
     int path = resolve_path(*shape);
     if (path < 0) return path;
     if (path != SSD_B200_PATH_TC) return 0;  // only the tensor-core kernels have bounded waits to report

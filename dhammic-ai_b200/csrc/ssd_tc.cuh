@@ -35,6 +35,11 @@ constexpr int LT = 128;  // tile length
 constexpr int HP = 64;   // headdim
 constexpr int DN = 128;  // d_state
 constexpr int PANEL = 16384;  // bytes of one [128 rows][64 bf16] swizzled panel
+// The decay mask of a 32-column block is the product of a per-row and a per-column factor taken relative to the
+// block's last column.  Below the diagonal both are <= 1.  Inside the diagonal block the row factor is
+// 2^(decay from the row to the block end) >= 1 and the column factor its inverse scale; beyond this many log2
+// units across the block one of them would leave the fp32 range, and the block is evaluated entry by entry.
+constexpr float kMaskSafeLog2 = 100.f;
 
 inline bool supported(int dtype, int T, int h, int p, int n, int g, int l) {
     (void)h;

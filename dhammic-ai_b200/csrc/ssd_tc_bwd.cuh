@@ -27,17 +27,6 @@
 namespace ssd {
 namespace tc {
 
-#ifdef SSD_TC_TIMELINE
-// Debug build only: clock stamps of one CTA's pipeline events, read back by ssd_b200_debug_timeline.
-__device__ long long g_timeline[4096];
-#define SSD_TL(slot)                                                                              \
-    do {                                                                                          \
-        if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 4096 && (slot) >= 0) g_timeline[(slot)] = clock64(); \
-    } while (0)
-#else
-#define SSD_TL(slot) do {} while (0)
-#endif
-
 struct BwdParams {
     CUtensorMap mX, mdY, mB, mC;   // loads: [b*T][h*64] and [b*T][g*128]
     CUtensorMap mH, mQ;            // loads: states [b*nt*h*128][64]
@@ -254,9 +243,20 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
                 const float2* S2 = reinterpret_cast<const float2*>(rs);
                 const float2* G2 = reinterpret_cast<const float2*>(rg);
                 uint32_t gp[8];
+                // see the forward walk: inside the diagonal block the factorised mask is only used while the decay
+                // across the block stays inside the fp32 range (warp-uniform test)
+                const bool exact = diag && scum2[buf * LT + qc * 32] - scum2[buf * LT + qc * 32 + 31] > kMaskSafeLog2;
+                const float2* C2 = reinterpret_cast<const float2*>(scum2 + buf * LT + c0);
 #pragma unroll
                 for (int q2 = 0; q2 < 8; ++q2) {
-                    float2 l = mul2(rf2, F2[q2]);
+                    float2 l;
+                    if (exact) {
+                        const float2 cj = C2[q2];
+                        l.x = exp2f(c_i - cj.x);
+                        l.y = exp2f(c_i - cj.y);
+                    } else {
+                        l = mul2(rf2, F2[q2]);
+                    }
                     if (diag) {  // columns beyond the row are masked
                         if (c0 + 2 * q2 > row) l.x = 0.f;
                         if (c0 + 2 * q2 + 1 > row) l.y = 0.f;

@@ -25,16 +25,6 @@
 namespace ssd {
 namespace tc {
 
-#ifdef SSD_TC_TIMELINE
-__device__ long long g_wtimeline[4096];
-#define SSD_WTL(slot)                                                                              \
-    do {                                                                                           \
-        if (MODE == 0 && blockIdx.x == 1 && blockIdx.y == 0 && (slot) < 4096 && (slot) >= 0) g_wtimeline[(slot)] = clock64(); \
-    } while (0)
-#else
-#define SSD_WTL(slot) do {} while (0)
-#endif
-
 __device__ __forceinline__ void named_barrier(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -71,8 +61,8 @@ struct WalkCfg {
     static constexpr int NST = (MODE == 1 || MODE == 3) ? 3 : 2;              // load stages
     static constexpr int STAGE_PANELS = (MODE == 0) ? 5 : 3;                   // V(2) U(1) [C(2)]
     static constexpr uint32_t STAGE_BYTES = STAGE_PANELS * PANEL;
-    // stages | sUd | sH | sY (mode 0) | scum2[2][128] sf[2][128] | alignment slack
-    static constexpr size_t SMEM = (size_t)NST * STAGE_BYTES + 2 * PANEL + (MODE == 0 ? PANEL : 0) + 4 * LT * 4 + 1024;
+    // stages | sUd | sH | sY (mode 0) | scum2[2][128] sf[2][128] sdtc[2][128] | alignment slack
+    static constexpr size_t SMEM = (size_t)NST * STAGE_BYTES + 2 * PANEL + (MODE == 0 ? PANEL : 0) + 6 * LT * 4 + 1024;
 };
 
 template <int MODE>
@@ -90,6 +80,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
     uint8_t* sY = sH + PANEL;                              // y staging (mode 0 only)
     float* scum2 = reinterpret_cast<float*>(sH + PANEL + (MODE == 0 ? PANEL : 0));  // [2][128]
     float* sf = scum2 + 2 * LT;                            // [2][128] column factors dt_j 2^(cend - c_j)
+    float* sdtc = sf + 2 * LT;                             // [2][128] dt_j (only read when a block's decay is extreme)
     __shared__ uint64_t bar_ld[3], bar_s, bar_u, bar_g, bar_m2, bar_h;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
@@ -256,6 +247,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
             if (hf == 0) {
                 scum2[buf * LT + row] = c_i;
                 sf[buf * LT + row] = dtv * exp2f(cend - c_i);
+                sdtc[buf * LT + row] = dtv;
             }
             mbar_wait(&bar_ld[s], (it / NST) & 1, &failed);
             named_barrier(1, 256);
@@ -308,15 +300,32 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                         const float2* S2 = reinterpret_cast<const float2*>(r);
                         const float2* F2 = reinterpret_cast<const float2*>(f4);
                         const float2 rf2 = make_float2(rf, rf);
+                        // Inside the diagonal block the row factor is >= 1 and the column factor <= 1; their
+                        // exponents are bounded by the decay across the block.  When that leaves the fp32 range the
+                        // entries of the block are evaluated one by one instead (warp-uniform branch).
+                        if (diag && scum2[buf * LT + c0] - scum2[buf * LT + c0 + 31] > kMaskSafeLog2) {
+                            const float2* C2 = reinterpret_cast<const float2*>(scum2 + buf * LT + c0);
+                            const float2* T2 = reinterpret_cast<const float2*>(sdtc + buf * LT + c0);
 #pragma unroll
-                        for (int q2 = 0; q2 < 16; ++q2) {  // fp32 pairs: one instruction, two columns
-                            float2 l = mul2(rf2, F2[q2]);
-                            if (diag) {
-                                if (c0 + 2 * q2 > row) l.x = 0.f;
-                                if (c0 + 2 * q2 + 1 > row) l.y = 0.f;
+                            for (int q2 = 0; q2 < 16; ++q2) {
+                                const float2 cj = C2[q2], tj = T2[q2];
+                                float2 l;
+                                l.x = (c0 + 2 * q2 > row) ? 0.f : tj.x * exp2f(c_i - cj.x);
+                                l.y = (c0 + 2 * q2 + 1 > row) ? 0.f : tj.y * exp2f(c_i - cj.y);
+                                const float2 v = mul2(S2[q2], l);
+                                packed[blk * 16 + q2] = pack_bf16(v.x, v.y);
                             }
-                            const float2 v = mul2(S2[q2], l);
-                            packed[blk * 16 + q2] = pack_bf16(v.x, v.y);
+                        } else {
+#pragma unroll
+                            for (int q2 = 0; q2 < 16; ++q2) {  // fp32 pairs: one instruction, two columns
+                                float2 l = mul2(rf2, F2[q2]);
+                                if (diag) {
+                                    if (c0 + 2 * q2 > row) l.x = 0.f;
+                                    if (c0 + 2 * q2 + 1 > row) l.y = 0.f;
+                                }
+                                const float2 v = mul2(S2[q2], l);
+                                packed[blk * 16 + q2] = pack_bf16(v.x, v.y);
+                            }
                         }
                     }
                 }

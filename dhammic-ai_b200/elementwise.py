@@ -22,14 +22,15 @@ from .ssd_scan import _dt_code, _ptr, _stream
 
 
 def _check_rope_inputs(x: Tensor, angles: Tensor):
-    assert x.is_cuda and angles.is_cuda, "fused_rope requires CUDA tensors"
-    assert x.dim() == 4 and angles.dim() == 4, f"expected x.dim()==4, angles.dim()==4, got {x.dim()}, {angles.dim()}"
+    assert x.is_cuda and angles.is_cuda, "rotation runs on the GPU only: x and angles must be CUDA tensors"
+    assert x.dim() == 4 and angles.dim() == 4, \
+        f"x must be (B,T,H,D) and angles (B,T,1 or H,D/2); got {x.dim()} and {angles.dim()} dimensions"
     B, T, H, D = x.shape
-    assert D % 2 == 0, f"x last dim must be even, got {D}"
+    assert D % 2 == 0, f"pairs are rotated, so the last dimension of x must be even (it is {D})"
     aB, aT, aH, aDh = angles.shape
     assert aB == B and aT == T and aDh == D // 2, \
-        f"angles shape {tuple(angles.shape)} mismatch (B,T,{{1|H}},D/2)=({B},{T},{{1|{H}}},{D // 2})"
-    assert aH == 1 or aH == H, f"angles H dim must be 1 (broadcast) or {H} (per-head), got {aH}"
+        f"angles {tuple(angles.shape)} do not fit x {tuple(x.shape)}: want ({B}, {T}, 1 or {H}, {D // 2})"
+    assert aH == 1 or aH == H, f"angles carry {aH} heads; give 1 (shared by all heads) or {H} (one set per head)"
     return B, T, H, D, aH == 1
 
 
@@ -79,12 +80,13 @@ class FusedTrapezoidal(torch.autograd.Function):
     @staticmethod
     def forward(ctx, dt_raw: Tensor, lam_raw: Tensor, dt_bias: Tensor, A_log: Tensor):
         assert dt_raw.is_cuda and lam_raw.is_cuda and dt_bias.is_cuda and A_log.is_cuda, \
-            "FusedTrapezoidal requires CUDA tensors"
-        assert dt_raw.shape == lam_raw.shape, f"dt_raw {dt_raw.shape} vs lam_raw {lam_raw.shape}"
-        assert dt_raw.dim() >= 1, "expected at least (..., H) tensor"
+            "the coefficient kernel runs on the GPU only: all four arguments must be CUDA tensors"
+        assert dt_raw.shape == lam_raw.shape, \
+            f"dt_raw and lam_raw must have one shape, got {tuple(dt_raw.shape)} and {tuple(lam_raw.shape)}"
+        assert dt_raw.dim() >= 1, "dt_raw needs a trailing head dimension"
         H = dt_raw.shape[-1]
-        assert dt_bias.dim() == 1 and dt_bias.shape[0] == H, f"dt_bias shape {dt_bias.shape} mismatches H={H}"
-        assert A_log.dim() == 1 and A_log.shape[0] == H, f"A_log shape {A_log.shape} mismatches H={H}"
+        assert dt_bias.dim() == 1 and dt_bias.shape[0] == H, f"dt_bias must be ({H},), got {tuple(dt_bias.shape)}"
+        assert A_log.dim() == 1 and A_log.shape[0] == H, f"A_log must be ({H},), got {tuple(A_log.shape)}"
         lib = _cabi.load()
         out_dtype = dt_raw.dtype
         dtc = dt_raw.contiguous()

@@ -48,9 +48,11 @@ class HostPipeline:
                "dD": torch.empty(h, dtype=torch.float32)}
         return {k: v.pin_memory() for k, v in out.items()}
 
-    def run(self, host_in: dict[str, Tensor], host_out: dict[str, Tensor], chunk_size: int) -> None:
+    def run(self, host_in: dict[str, Tensor], host_out: dict[str, Tensor], chunk_size: int, wait: bool = True):
         """host_in: pinned x (b,T,h,p), dt (b,T,h), B, C (b,T,g,n), dy (b,T,h,p), A_head (h), D (h).
-        Returns when every result is in host_out (the calling thread is synchronised with the copy-out stream)."""
+        With ``wait`` (default) the calling THREAD blocks until every result is in host_out, so the host may read
+        the buffers right after the call.  With ``wait=False`` the call returns at once with a CUDA event that
+        completes when the last copy has landed; host_out must not be read before ``event.synchronize()``."""
         b = host_in["x"].shape[0]
         nmb = min(self.nmb, b)
         while b % nmb:
@@ -103,6 +105,12 @@ class HostPipeline:
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_cmp)
         cur.wait_stream(self.s_in)
+        done = torch.cuda.Event()
+        done.record(self.s_out)  # s_out is ordered after the kernels, which are ordered after the copies in
+        if wait:
+            done.synchronize()
+            return None
+        return done
 
 
 class SequenceStreamer:
@@ -139,7 +147,8 @@ class SequenceStreamer:
 
     def run(self, host_in: dict[str, Tensor], host_out: dict[str, Tensor], chunk_size: int) -> None:
         """host_in: pinned x (b,T,h,p), dt (b,T,h), B, C (b,T,g,n), dy (b,T,h,p), A_head (h), D (h).  host_out: pinned
-        y, dx, ddt, dB, dC, dA_head, dD (``HostPipeline.alloc_outputs``).  Returns when every result is in host_out."""
+        y, dx, ddt, dB, dC, dA_head, dD (``HostPipeline.alloc_outputs``).  The calling thread blocks until every
+        result is in host_out."""
         T = host_in["x"].shape[1]
         L = self.slice_len
         assert T % L == 0 and L % chunk_size == 0, f"sequence {T} / slice {L} / chunk {chunk_size} do not divide"
@@ -235,3 +244,4 @@ class SequenceStreamer:
             host_out["dD"].copy_(dD, non_blocking=True)
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_copy)
+        self.s_out.synchronize()  # the last copies out are ordered after every kernel: the host may read host_out

@@ -10,7 +10,7 @@
  *
  * The reference has no native code; its operator is Python over Triton and
  * cuBLAS.  A maintainer binds these entry points from Python with ctypes
- * (see INTEGRATION.md).  Conventions:
+ * (dhammic-ai_b200/_cabi.py is such a binding).  Conventions:
  *
  *   - plain pointers and sizes only; every pointer is a DEVICE pointer on the
  *     current CUDA device unless stated otherwise; tensors are dense row-major
@@ -52,7 +52,7 @@ enum { SSD_B200_F32 = 0, SSD_B200_BF16 = 1 };
 enum { SSD_B200_PASS_FWD = 0, SSD_B200_PASS_BWD = 1 };
 
 /* Which kernels run.  AUTO picks the tcgen05 tensor-core path when the shape
- * and dtype allow it (bf16; p = 64; n in {64,128}; T a multiple of 128) and the
+ * and dtype allow it (bf16; p = 64; n = 128; T a multiple of 128) and the
  * fp32 SIMT path otherwise; the other two force a path (for tests). */
 enum { SSD_B200_PATH_AUTO = 0, SSD_B200_PATH_SIMT = 1, SSD_B200_PATH_TC = 2 };
 
@@ -183,8 +183,10 @@ int ssd_b200_bwd(const ssd_b200_bwd_args *args, void *stream);
  *   - Limit: a shape whose forward scratch (ssd_b200_workspace_bytes(shape, SSD_B200_PASS_FWD))
  *     exceeds the array is refused with SSD_B200_EWORKSPACE and a message naming both sizes.
  *   - Every GPU on which the library is loaded holds the array until the process exits.
- *   - The first call on each device looks the array's device address up (with that device
- *     current).
+ *   - Every call looks the array's device address up with cudaGetSymbolAddress for the context that
+ *     is current on the calling thread (nothing is cached, so a device reset or a second context on
+ *     the same GPU cannot leave a stale address behind).  The first lookup on a device loads the
+ *     library's device code there: make the first call before any stream capture.
  *   - All calls on a device share the one array.  It keeps whatever the previous call left; the
  *     kernels overwrite what they read and the one word that must start at zero is cleared on
  *     the stream at the start of each call.  Two calls that overlap on the GPU (different
@@ -196,7 +198,9 @@ size_t ssd_b200_static_scratch_bytes(void);
 /*
  * Optional check after a call (it synchronises `stream`): the tensor-core kernels bound every
  * wait on a barrier; if one ran out, the kernel finished anyway, set a status word at the start
- * of the workspace and this returns SSD_B200_EDEVICE.  No counterpart in the reference.
+ * of the workspace and this returns SSD_B200_EDEVICE.  `workspace` is the buffer the call was given;
+ * NULL means the built-in array of ssd_b200_fwd_static_scratch on the current device.  No counterpart
+ * in the reference.
  */
 int ssd_b200_device_status(const ssd_b200_shape *shape, const void *workspace, void *stream);
 

@@ -323,11 +323,15 @@ def test_host_pipeline_matches_direct_call(pkg, cabi):
     pipe = pkg.HostPipeline("cuda", micro_batches=2)
     for _ in range(2):  # twice: slot reuse across calls
         pipe.run(pinned, out, cfg.chunk)
-    torch.cuda.synchronize()
+    got = {k: v.clone() for k, v in out.items()}  # read by the CPU right after run() returned: no device synchronise
     want = mamba2_gpu(pkg, inp, cfg.chunk)
     for k in ("y", "dx", "ddt", "dB", "dC"):
-        assert torch.equal(out[k], want[k]), k
-    assert rel_err(out["dA_head"], want["dA_head"]) < 1e-5 and rel_err(out["dD"], want["dD"]) < 1e-5
+        assert torch.equal(got[k], want[k]), k
+    assert rel_err(got["dA_head"], want["dA_head"]) < 1e-5 and rel_err(got["dD"], want["dD"]) < 1e-5
+    # the stream-ordered form: nothing may be read before the returned event has completed
+    ev = pipe.run(pinned, out, cfg.chunk, wait=False)
+    ev.synchronize()
+    assert torch.equal(out["y"], want["y"])
 
 
 @pytest.mark.parametrize("idx,batch,seqlen,slice_len", [(2, 1, 1024, 256), (2, 2, 512, 128), (0, 2, 512, 128)])
@@ -341,9 +345,9 @@ def test_sequence_streamer_is_exact_across_slices(pkg, cabi, idx, batch, seqlen,
     runner = pkg.SequenceStreamer("cuda", slice_len=slice_len)
     for _ in range(2):  # twice: slot reuse across calls
         runner.run(pinned, out, cfg.chunk)
-    torch.cuda.synchronize()
+    got = {k: v.clone() for k, v in out.items()}  # CPU read right after run() returned
     want = mamba2_gpu(pkg, inp, cfg.chunk)
     tol = TOL_BF16 if cfg.dtype == "bf16" else TOL_FP32
-    errs = {k: rel_err(out[k], want[k]) for k in ("y", "dx", "ddt", "dB", "dC", "dA_head", "dD")}
+    errs = {k: rel_err(got[k], want[k]) for k in ("y", "dx", "ddt", "dB", "dC", "dA_head", "dD")}
     bad = {k: v for k, v in errs.items() if not v < tol}
     assert not bad, errs

@@ -36,6 +36,8 @@ def _forward(cabi, pkg, entry, cfg, inp, use_workspace):
                         _ptr(final), _ptr(cum), 0, 0, _ptr(ws), 0 if ws is None else ws.numel(), None)
     stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
     cabi.check(getattr(lib, entry)(C.byref(args), stream))
+    # bounded-wait status of the call: a NULL workspace asks about the library's own array
+    cabi.check(lib.ssd_b200_device_status(C.byref(shape), _ptr(ws), stream))
     torch.cuda.synchronize(dev)
     return y.float().cpu(), final.cpu(), cum.cpu()
 
