@@ -45,6 +45,19 @@ def measured_peaks():
     return FALLBACK_HBM_GBS, 1400.0, "fallback"
 
 
+def dram_bytes_per_token(cfg_tag: str) -> dict[str, float]:
+    """profiles/dram_traffic_per_token.txt: lines `<cfg tag> <kernel slot> <dram bytes per token>` taken from the
+    ncu captures summarised beside it."""
+    p = ROOT / "profiles" / "dram_traffic_per_token.txt"
+    out = {}
+    if p.exists():
+        for line in p.read_text().splitlines():
+            f = line.split()
+            if len(f) >= 3 and not line.startswith("#") and f[0] == cfg_tag:
+                out[f[1]] = float(f[2])
+    return out
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -200,11 +213,83 @@ def run_elementwise(args, cfg, pkg):
     print(json.dumps(line))
 
 
+def seq_parallel_record(pkg, dmod, cabi, args, dev, rank, world, barrier):
+    """Config 4 (one sequence of 131,072 positions split contiguously over the ranks; per-rank state summaries cross
+    NVLink through NCCL): tokens/s over all ranks, the same sequence on ONE GPU (rank 0, cut into segments that run
+    as batch entries) for comparison, and where a step's time goes (library kernels by CUDA events on the launching
+    stream, collectives by events on their side stream)."""
+    import torch.distributed as dist
+    full = pkg.CONFIGS[4]
+    cfg = pkg.shrink(full, full.batch, full.seqlen // world)
+    names = ("x", "dt", "A_head", "B", "C", "D", "dy")
+
+    def make_step(c, seed_rank, comm):
+        host = pkg.make_inputs(c, rank=seed_rank)
+        d = {k: host[k].to(dev) for k in names}
+        lv = {k: d[k].detach().requires_grad_(True) for k in names if k != "dy"}
+
+        def step():
+            y, _ = dmod.ssd_mamba2_sequence_parallel(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], c.chunk,
+                                                     comm=comm, segments=0)
+            return torch.autograd.grad([y], list(lv.values()), [d["dy"]])
+        return step
+
+    def timed(step, sync, steps, collective):
+        for _ in range(max(3, args.warmup)):
+            step()
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        sync()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if collective:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    steps = max(3, min(args.steps, 10))
+    comm = dmod.TorchDistComm()
+    step = make_step(cfg, rank, comm)
+    ms = timed(step, barrier, steps, True)
+    # phases of one step: kernels per slot, collectives from the communicator's own events
+    cabi.profile_enable(True)
+    comm.timings = []
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize(dev)
+    prof = cabi.profile_read()
+    cabi.profile_enable(False)
+    coll = comm.read_timings()
+    comm.timings = None
+    phases = {k: v[0] / steps for k, v in prof.items()}
+    phases.update({f"nccl_{k}": v / steps for k, v in coll.items()})
+    del step
+    torch.cuda.empty_cache()
+    barrier()
+    one_gpu = None
+    if rank == 0:  # the whole sequence on one GPU, segments as batch entries, no communicator
+        step1 = make_step(full, 0, dmod.LoopbackComm())
+        ms1 = timed(step1, lambda: torch.cuda.synchronize(dev), steps, False)
+        one_gpu = {"ms_per_step": ms1, "tokens_per_s": full.tokens / (ms1 * 1e-3)}
+        del step1
+        torch.cuda.empty_cache()
+    barrier()
+    return {"workload": full.name, "scaling": "strong", "n_gpus": world, "tokens_per_step": full.tokens,
+            "ms_per_step": ms, "value": full.tokens / (ms * 1e-3), "unit": "tokens/s", "steps": steps,
+            "one_gpu_segmented": one_gpu,
+            "segments_per_rank": dmod.pick_segments(cfg.batch, cfg.nheads, cfg.seqlen),
+            "exchange": "1 all_gather (forward) + 1 all_gather + 1 all_reduce (backward) per step, on a side stream",
+            "phase_ms_per_step": phases}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--repeats", type=int, default=5, help="timed loops of --steps steps each; the median loop is reported")
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (debug)")
     ap.add_argument("--seqlen", type=int, default=0, help="override the sequence length (debug)")
@@ -212,6 +297,7 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-seq-parallel", action="store_true", help="N > 1: skip the sequence-split sub-record")
     ap.add_argument("--op", default="scan", choices=["scan", "elementwise"],
                     help="elementwise: time the rotation and trapezoidal-coefficient operators instead of the scan")
     args = ap.parse_args()
@@ -282,20 +368,24 @@ def main():
         step_device()
     barrier()
     launches0 = cabi.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        step_device()
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
-    launches = cabi.launch_count() - launches0
+    # EXACTLY args.steps steps per timed loop, barrier + synchronise on both sides, CUDA events on the launching
+    # stream, max over ranks; the loop is repeated and the median loop is reported (the spread goes into the line)
+    loops = []
+    for _ in range(max(1, args.repeats)):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            step_device()
+        ev1.record()
+        barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        loops.append(float(t.item()))
+    launches = (cabi.launch_count() - launches0) // len(loops)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
+    ms_max = statistics.median(loops)
     tokens_all = cfg.tokens * world
     value = tokens_all * args.steps / (ms_max * 1e-3)
 
@@ -318,12 +408,10 @@ def main():
     step_bytes = cfg.bytes_per_token() * cfg.tokens
     step_flops = cfg.flops_per_token() * cfg.tokens
     ms_step = ms_max / args.steps
-    # dram read + write of one launch, from the committed ncu capture of the same per-token shape at batch 4
-    # (profiles/), scaled by tokens; None for kernels / shapes without a capture
-    ncu_bytes_per_token = {"tc_bwd_walk": 815.2e6 / 16384, "tc_fwd_walk": 438.3e6 / 16384, "tc_bwd_state": 438.0e6 / 16384}
-    traffic = None
-    if cfg.index == 2 and top in ncu_bytes_per_token:
-        traffic = ncu_bytes_per_token[top] * cfg.tokens
+    # dram read + write of one launch, from the tracked ncu summary (bytes per token of this per-token shape,
+    # captured at a smaller batch and scaled by tokens: traffic grows in proportion); None without a capture
+    per_token = dram_bytes_per_token(cfg.name.split("_")[0])
+    traffic = per_token[top] * cfg.tokens if top in per_token else None
     roofline = {
         "bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
         "frac": achieved / hbm_peak, "traffic": traffic, "peak_kind": peak_kind,
@@ -388,6 +476,12 @@ def main():
                "api": ("SequenceStreamer.run (16384-position slices, state carried across)" if streamed else
                        "HostPipeline.run (8 micro-batches, 3 streams)" if not plain else "operator call on pinned buffers")}
 
+    # N > 1: the long-context configuration, whose sequence is split over the ranks (the only one with a collective
+    # on the data path), rides along as a sub-record; `value` stays the batch-sharded configuration
+    seq_record = None
+    if world > 1 and not cfg.seq_parallel and not cfg.mamba3 and not args.no_seq_parallel:
+        seq_record = seq_parallel_record(pkg, dmod, cabi, args, dev, rank, world, barrier)
+
     cpu_base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         v, threads, sample = cpu_oracle_tokens_per_s(cfg, pkg)
@@ -407,7 +501,11 @@ def main():
                        "kernel_path": pkg.resolved_path_name(cfg), "accumulate": "fp32",
                        "l2": "inputs larger than L2 (x alone %.0f MB per GPU)" % (cfg.tokens * cfg.nheads * cfg.headdim * 2 / 1e6)},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_base,
+            "timed_loops": {"count": len(loops), "ms_per_step_median": ms_step, "ms_per_step_min": min(loops) / args.steps,
+                            "ms_per_step_max": max(loops) / args.steps},
         }
+        if seq_record is not None:
+            line["seq_parallel"] = seq_record
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -7,7 +7,7 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 F32, BF16 = 0, 1
 PASS_FWD, PASS_BWD = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
@@ -18,7 +18,7 @@ BWD_DINIT_ONLY = 1
 EXPORTS = (
     "ssd_b200_abi_version", "ssd_b200_last_error", "ssd_b200_workspace_bytes", "ssd_b200_states_bytes",
     "ssd_b200_resolve_path",
-    "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix",
+    "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix_all",
     "ssd_b200_m3_prologue_fwd", "ssd_b200_m3_skip_fwd", "ssd_b200_m3_prologue_bwd", "ssd_b200_m3_chain_ws_floats", "ssd_b200_m3_chain_bwd", "ssd_b200_rope_fwd", "ssd_b200_rope_bwd",
     "ssd_b200_trapezoid_ws_floats", "ssd_b200_trapezoid_fwd", "ssd_b200_trapezoid_bwd",
     "ssd_b200_rmsnorm_ws_floats", "ssd_b200_rmsnorm_fwd", "ssd_b200_rmsnorm_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status",
@@ -38,7 +38,7 @@ class FwdArgs(C.Structure):
                 ("D", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("init", C.c_void_p), ("y", C.c_void_p),
                 ("final_state", C.c_void_p), ("a_cumsum", C.c_void_p), ("cumsum_is_input", C.c_int32),
                 ("flags", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("states", C.c_void_p)]
+                ("states", C.c_void_p), ("logdecay_total", C.c_void_p)]
 
 
 class BwdArgs(C.Structure):
@@ -83,9 +83,8 @@ def load() -> C.CDLL:
     lib.ssd_b200_materialize_cache.restype = C.c_int
     lib.ssd_b200_materialize_cache.argtypes = [C.POINTER(Shape), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                                C.c_void_p]
-    lib.ssd_b200_state_prefix.restype = C.c_int
-    lib.ssd_b200_state_prefix.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
-                                          C.c_int64, C.c_int64, C.c_int32, C.c_void_p]
+    lib.ssd_b200_state_prefix_all.restype = C.c_int
+    lib.ssd_b200_state_prefix_all.argtypes = [C.c_void_p] * 4 + [C.c_int64] * 8 + [C.c_int32, C.c_void_p]
     lib.ssd_b200_m3_prologue_fwd.restype = C.c_int
     lib.ssd_b200_m3_prologue_fwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 15
     lib.ssd_b200_rope_fwd.restype = C.c_int

@@ -20,7 +20,7 @@ namespace prof {
 const char* const kNames[K_COUNT] = {
     "chunk_cumsum", "chunk_state", "state_passing", "chunk_scan", "chunk_dstate", "state_passing_rev",
     "bwd_row", "bwd_col", "decay_grad", "reduce_batch", "cache_L", "cache_decay_chunk", "state_prefix",
-    "tc_fwd_walk", "tc_bwd_state", "tc_bwd_walk", "tc_aux"};
+    "tc_fwd_walk", "tc_bwd_state", "tc_bwd_walk", "tc_aux", "tc_summary"};
 std::atomic<long long> g_launches{0};
 bool g_enabled = false;
 struct Rec {
@@ -214,6 +214,10 @@ int simt_fwd(const ssd_b200_fwd_args* a, cudaStream_t st) {
     if (!a->cumsum_is_input)
         if (int rc = launch_cumsum(P, st)) return rc;
     if (int rc = simt_forward_states<T>(P, st)) return rc;
+    if (a->logdecay_total) {
+        SSD_LAUNCH(ssd::prof::K_CUMSUM, st, logdecay_total_kernel<<<(d.b * d.h + 127) / 128, 128, 0, st>>>(a->a_cumsum, a->logdecay_total, d.b * d.h, d.c, d.l));
+        CUDA_LAUNCH_CHECK("logdecay_total");
+    }
     if (a->flags & SSD_B200_FWD_STATES_ONLY) return 0;
     const int PT = (d.p + TS - 1) / TS;
     const int hrows = d.p > TS ? d.p : TS;
@@ -805,17 +809,21 @@ int ssd_b200_materialize_cache(const ssd_b200_shape* shape, const float* a_cumsu
     return 0;
 }
 
-int ssd_b200_state_prefix(const float* finals, const float* logp, float* out, int64_t nranks, int64_t rank,
-                          int64_t batch, int64_t nheads, int64_t state_elems, int32_t reverse, void* stream) {
-    if (!finals || !logp || !out) return fail(SSD_B200_EINVAL, "null pointer");
-    if (nranks <= 0 || rank < 0 || rank >= nranks || batch <= 0 || nheads <= 0 || state_elems <= 0 ||
-        batch * nheads > 65535)
-        return fail(SSD_B200_EINVAL, "bad state_prefix dimensions");
+int ssd_b200_state_prefix_all(const float* pieces, const float* logp, const float* edge, float* out, int64_t nranks,
+                              int64_t rank, int64_t segments, int64_t batch, int64_t nheads, int64_t state_elems,
+                              int64_t rank_stride, int64_t logp_stride, int32_t reverse, void* stream) {
+    if (!pieces || !logp || !out) return fail(SSD_B200_EINVAL, "null pointer");
+    if (nranks <= 0 || rank < 0 || rank >= nranks || segments <= 0 || batch <= 0 || nheads <= 0 || state_elems <= 0 ||
+        batch * nheads > 65535 || nranks * segments > 2147483647LL)
+        return fail(SSD_B200_EINVAL, "bad state_prefix_all dimensions");
+    if (rank_stride < batch * segments * nheads * state_elems || logp_stride < batch * segments * nheads)
+        return fail(SSD_B200_EINVAL, "state_prefix_all: a rank's block is smaller than its (b, S, h) records");
     dim3 g((unsigned)((state_elems + 255) / 256), (unsigned)(batch * nheads));
-    SSD_LAUNCH(ssd::prof::K_PREFIX, (cudaStream_t)stream, ssd::simt::state_prefix_kernel<<<g, 256, 0, (cudaStream_t)stream>>>(finals, logp, out, (int)nranks, (int)rank,
-                                                                        (int)(batch * nheads), (size_t)state_elems,
-                                                                        reverse));
-    CUDA_LAUNCH_CHECK("state_prefix");
+    cudaStream_t st = (cudaStream_t)stream;
+    SSD_LAUNCH(ssd::prof::K_PREFIX, st, ssd::simt::state_prefix_all_kernel<<<g, 256, 0, st>>>(
+        pieces, logp, edge, out, (int)nranks, (int)rank, (int)segments, (int)nheads, (size_t)state_elems,
+        (size_t)rank_stride, (size_t)logp_stride, reverse));
+    CUDA_LAUNCH_CHECK("state_prefix_all");
     return 0;
 }
 

@@ -797,19 +797,52 @@ __global__ void cache_decay_chunk_kernel(const float* cum, T* dc, int c, int l) 
     }
 }
 
-// Sequence-parallel prefix over gathered per-rank summaries (all in this GPU's memory).
-__global__ void state_prefix_kernel(const float* finals, const float* logp, float* out, int R, int rank, int bh,
-                                    size_t pn, int reverse) {
+// Sequence-parallel prefix over gathered per-piece summaries (all in this GPU's memory).  The sequence is cut into
+// R * S consecutive pieces, piece index g = r * S + s (rank r, segment s of that rank).  Rank r's summaries sit at
+// pieces + r * rank_stride as (b, S, h, pn) and its total log-decays at logp + r * logp_stride as (b, S, h).
+// One launch writes, for the S pieces of `rank`, the state entering each piece (forward) or the state gradient
+// leaving it (reverse) into out (b, S, h, pn); every gathered piece is read once:
+//     forward   acc = edge;  for g = 0 ..        : out[g] = acc;  acc = exp(logp[g]) acc + pieces[g]
+//     reverse   acc = edge;  for g = R S - 1 .. : out[g] = acc;  acc = exp(logp[g]) acc + pieces[g]
+// `edge` (b, h, pn) or null: the state before the first piece / the gradient behind the last one.
+__global__ void state_prefix_all_kernel(const float* __restrict__ pieces, const float* __restrict__ logp,
+                                        const float* __restrict__ edge, float* __restrict__ out, int R, int rank, int S,
+                                        int h, size_t pn, size_t rank_stride, size_t logp_stride, int reverse) {
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int m = blockIdx.y;  // (b,h)
     if (e >= pn) return;
-    float acc = 0.f;
+    const int bb = m / h, hh = m - bb * h;
+    float acc = edge ? edge[(size_t)m * pn + e] : 0.f;
+    const int lo = rank * S, hi = lo + S;
+    auto rec = [&](int g) { return ((size_t)bb * S + (g % S)) * h + hh; };  // (b, S, h) record of piece g inside its rank's block
     if (!reverse) {
-        for (int q = 0; q < rank; ++q) acc = __expf(logp[(size_t)q * bh + m]) * acc + finals[((size_t)q * bh + m) * pn + e];
+#pragma unroll 4
+        for (int g = 0; g < hi; ++g) {
+            if (g >= lo) out[rec(g) * pn + e] = acc;
+            if (g + 1 < hi) {
+                const size_t r = (size_t)(g / S);
+                acc = __expf(logp[r * logp_stride + rec(g)]) * acc + pieces[r * rank_stride + rec(g) * pn + e];
+            }
+        }
     } else {
-        for (int q = R - 1; q > rank; --q) acc = __expf(logp[(size_t)q * bh + m]) * acc + finals[((size_t)q * bh + m) * pn + e];
+#pragma unroll 4
+        for (int g = R * S - 1; g >= lo; --g) {
+            if (g < hi) out[rec(g) * pn + e] = acc;
+            if (g > lo) {
+                const size_t r = (size_t)(g / S);
+                acc = __expf(logp[r * logp_stride + rec(g)]) * acc + pieces[r * rank_stride + rec(g) * pn + e];
+            }
+        }
     }
-    out[(size_t)m * pn + e] = acc;
+}
+
+// Total log-decay of every (batch, head) sequence from the within-chunk cumulative sums: sum of the chunks' last entries.
+__global__ void logdecay_total_kernel(const float* __restrict__ cum, float* __restrict__ out, int bh, int c, int l) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= bh) return;
+    float s = 0.f;
+    for (int k = 0; k < c; ++k) s += cum[((size_t)m * c + k) * l + l - 1];
+    out[m] = s;
 }
 
 }  // namespace simt

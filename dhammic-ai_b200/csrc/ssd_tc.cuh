@@ -12,7 +12,8 @@
 //                       in registers:
 //        MODE 0  forward:   Y = ((C B^T) o L) X + diag(e) C H^T (+ D x);  H <- e^{S} H + X^T diag(d) B
 //        MODE 1  states:    only the recurrence; stores H_k (state entering tile k) as bf16
-//        MODE 3  the reverse recurrence alone (gradient of the initial state only)
+//   summary_kernel      what a whole piece of the sequence adds to the state after it / to the state gradient
+//                       before it (the quantities the sequence-parallel schedule exchanges): a stream, no recurrence
 //   rev_walk_kernel     reverse walk of the backward pass, Q <- e^{S} Q + dY^T diag(e) C, software-pipelined
 //                       over tiles; stores Q_k = dH_{k+1} as bf16 and the state parts of the decay gradient
 //   bwd_tile_kernel     one CTA per (batch, tile, group), heads of the group in an inner loop so
@@ -288,9 +289,5 @@ __device__ __forceinline__ void store_row32(uint8_t* panel, int row, int col0_in
 }  // namespace ssd
 #include "ssd_tc_walk.cuh"
 #include "ssd_tc_revwalk.cuh"
-namespace ssd {
-namespace tc {
-
-}  // namespace tc
-}  // namespace ssd
+#include "ssd_tc_summary.cuh"
 #include "ssd_tc_bwd.cuh"

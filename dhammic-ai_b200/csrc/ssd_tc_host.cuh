@@ -103,7 +103,8 @@ inline int set_walk_attrs(char* err, size_t errn) {
     cudaError_t e = cudaFuncSetAttribute(walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<0>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<1>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRevSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<3>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSumSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSumSmem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem);
     if (e != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "set shared memory size: %s", cudaGetErrorString(e));
     return 0;
@@ -161,15 +162,20 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     if (!ok) SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
     P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.seed = a->init; P.out_state = a->final_state; P.status = status;
     P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = d.T / LT;
-    if (states_only) {  // the recurrence alone: final state of this slice of the sequence
-        P.save_states = 0;
-        P.D = nullptr;
-        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<1><<<dim3(d.h, d.b), 288, WalkCfg<1>::SMEM, st>>>(P));
-        SSD_TC_CHECK("tc_states_walk");
+    if (states_only) {  // what this piece of the sequence adds to the state after it (plus the decayed seed)
+        SummaryParams S{};
+        S.mU = P.mU; S.mV = P.mV; S.tcum = tcum; S.dtT = dtT; S.seed = a->init; S.out = a->final_state;
+        S.logdecay = a->logdecay_total; S.status = status; S.T = d.T; S.h = d.h; S.hpg = d.hpg; S.nt = d.T / LT;
+        SSD_LAUNCH(prof::K_TC_SUMMARY, st, summary_kernel<false><<<dim3(d.h, d.b), 288, kSumSmem, st>>>(S));
+        SSD_TC_CHECK("tc_summary_fwd");
         return 0;
     }
     SSD_LAUNCH(prof::K_TC_FWD, st, walk_kernel<0><<<dim3(d.h, d.b), 288, WalkCfg<0>::SMEM, st>>>(P));
     SSD_TC_CHECK("tc_fwd_walk");
+    if (a->logdecay_total) {
+        SSD_LAUNCH(prof::K_CUMSUM, st, simt::logdecay_total_kernel<<<(d.b * d.h + 127) / 128, 128, 0, st>>>(a->a_cumsum, a->logdecay_total, d.b * d.h, d.c, d.l));
+        SSD_TC_CHECK("logdecay_total");
+    }
     return 0;
 }
 
@@ -198,15 +204,14 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     if (int rc = set_walk_attrs(err, errn)) return rc;
     const int nt = d.T / LT;
     const uint64_t rows = (uint64_t)d.b * d.T, srows = (uint64_t)d.b * nt * d.h * DN;
-    if (a->flags & SSD_B200_BWD_DINIT_ONLY) {  // reverse recurrence alone: d(initial state) of this slice
-        WalkParams P{};
-        if (!(make_map(&P.mU, a->dy, rows, (uint64_t)d.h * HP) && make_map(&P.mV, a->C, rows, (uint64_t)d.g * DN)))
+    if (a->flags & SSD_B200_BWD_DINIT_ONLY) {  // d(initial state) of this piece for the given (or a zero) dfinal
+        SummaryParams S{};
+        if (!(make_map(&S.mU, a->dy, rows, (uint64_t)d.h * HP) && make_map(&S.mV, a->C, rows, (uint64_t)d.g * DN)))
             SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
-        P.mC = P.mV; P.mY = P.mU; P.mS = P.mU;
-        P.tcum = tcum; P.seed = a->dfinal; P.out_state = a->dinit; P.status = status;
-        P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
-        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<3><<<dim3(d.h, d.b), 288, WalkCfg<3>::SMEM, st>>>(P));
-        SSD_TC_CHECK("tc_dinit_walk");
+        S.tcum = tcum; S.dtT = nullptr; S.seed = a->dfinal; S.out = a->dinit; S.logdecay = nullptr; S.status = status;
+        S.T = d.T; S.h = d.h; S.hpg = d.hpg; S.nt = nt;
+        SSD_LAUNCH(prof::K_TC_SUMMARY, st, summary_kernel<true><<<dim3(d.h, d.b), 288, kSumSmem, st>>>(S));
+        SSD_TC_CHECK("tc_summary_rev");
         return 0;
     }
     CUtensorMap mX, mdY, mB, mC, mH, mQ, mdX, mdB, mdC;

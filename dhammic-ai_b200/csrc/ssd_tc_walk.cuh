@@ -17,9 +17,8 @@
 //   bar_m2     every MMA of the tile has completed                (control -> row warps)
 //   bar_h      accumulators read, new state written, 256 arrive   (row warps -> control)
 //
-// MODE 0 forward (writes y), MODE 1 states only (stores the state entering every tile, bf16),
-// MODE 3 the reverse recurrence over dy and C alone (for d initial-state only).  The full reverse walk of the
-// backward pass is rev_walk_kernel (ssd_tc_revwalk.cuh).
+// MODE 0 forward (writes y), MODE 1 states only (stores the state entering every tile, bf16).  The reverse walk
+// of the backward pass is rev_walk_kernel (ssd_tc_revwalk.cuh).
 #pragma once
 
 namespace ssd {
@@ -58,7 +57,7 @@ __device__ __forceinline__ void store_state_slot(__nv_bfloat16* slot, int row, i
 
 template <int MODE>
 struct WalkCfg {
-    static constexpr int NST = (MODE == 1 || MODE == 3) ? 3 : 2;              // load stages
+    static constexpr int NST = (MODE == 1) ? 3 : 2;              // load stages
     static constexpr int STAGE_PANELS = (MODE == 0) ? 5 : 3;                   // V(2) U(1) [C(2)]
     static constexpr uint32_t STAGE_BYTES = STAGE_PANELS * PANEL;
     // stages | sUd | sH | sY (mode 0) | scum2[2][128] sf[2][128] sdtc[2][128] | alignment slack
@@ -69,7 +68,6 @@ template <int MODE>
 __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ WalkParams P) {
     using Cfg = WalkCfg<MODE>;
     constexpr int NST = Cfg::NST;
-    constexpr bool REV = (MODE == 3);
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment by an offset on the __shared__ array itself, so that every access below stays a
     // shared-memory instruction (a pointer rebuilt from an integer would be a generic-address access)
@@ -133,7 +131,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
             prefetch_tmap(&P.mU);
             prefetch_tmap(&P.mV);
             auto issue_loads = [&](int it) {
-                const int k = REV ? nt - 1 - it : it;
+                const int k = it;
                 const int s = it % NST;
                 uint8_t* st = sStage + (size_t)s * Cfg::STAGE_BYTES;
                 const int grow = bb * P.T + k * LT;
@@ -157,7 +155,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 mma_commit(&bar_s);
             };
             auto state_row = [&](int it) {  // row of tile `it` of this walk in the [b*nt*h*128][64] state tensor
-                const int k = REV ? nt - 1 - it : it;
+                const int k = it;
                 return (int)((((size_t)bb * nt + k) * P.h + hh) * DN);
             };
             for (int it = 0; it < NST - 1 && it < nt; ++it) issue_loads(it);
@@ -224,11 +222,11 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
     } else {
         // ------------------------------------------------------------------ row warps
         const float* tcum = P.tcum + bh * P.T;
-        const float* dtT = (!REV && P.dtT) ? P.dtT + bh * P.T : nullptr;
+        const float* dtT = P.dtT ? P.dtT + bh * P.T : nullptr;
         const uint32_t lanes = lane_base(warp);
         const float Dh = (MODE == 0 && P.D) ? P.D[hh] : 0.f;
         // per-tile scalars are fetched one tile ahead
-        auto tile_of = [&](int it) { return REV ? nt - 1 - it : it; };
+        auto tile_of = [&](int it) { return it; };
         float c_n = tcum[(size_t)tile_of(0) * LT + row];
         float cend_n = tcum[(size_t)tile_of(0) * LT + (row | 31)];
         float dt_n = dtT ? dtT[(size_t)tile_of(0) * LT + row] : 1.f;
@@ -260,7 +258,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
             {
                 // the row weight as a bf16 pair: one packed multiply per two elements (the product is rounded to
                 // bf16 for the MMA anyway; rounding the weight first costs at most one more ulp of bf16)
-                const float w = REV ? exp2f(c_i) : exp2f(Sk - c_i) * dtv;
+                const float w = exp2f(Sk - c_i) * dtv;
                 const __nv_bfloat162 w2 = __float2bfloat162_rn(w);
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {

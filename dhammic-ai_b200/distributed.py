@@ -12,17 +12,21 @@ src/kernels/ssd_scan.py:395-397, :410, :468, :530-533).
   incoming state, ``final_r = F_r + P_r * init_r`` with F_r the zero-init final state of the slice and
   P_r = exp(sum of its log-decays).  Schedule of :func:`ssd_mamba2_sequence_parallel`:
 
-      forward   1. states-only pass over the slice            -> F_r (b,h,p,n) fp32, log P_r (b,h)
-                2. all_gather of (F_r, log P_r)                 (2 MiB + 256 B per rank at h=64, p=64, n=128)
-                3. init_r = sum_{q<r} (prod_{q<k<r} P_k) F_q    (local kernel over the gathered buffers)
+      forward   1. summary pass over the slice (a stream)       -> F_r (b,h,p,n) fp32, log P_r (b,h)
+                2. ONE all_gather of the packed (F_r | log P_r)  (2 MiB + 256 B per rank at h=64, p=64, n=128)
+                3. init_r = sum_{q<r} (prod_{q<k<r} P_k) F_q    (one local kernel, every gathered piece read once)
                 4. the full scan of the slice with init_r
-      backward  1. dinit-only pass (reverse recurrence)         -> D_r = d init_r for a zero dfinal
-                2. all_gather of (D_r, log P_r)
-                3. dfinal_r = sum_{q>r} (prod_{r<k<q} P_k) D_q  (+ the caller's d final on the last rank)
+      backward  1. reverse summary pass                          -> D_r = d init_r for a zero dfinal (the caller's
+                                                                    d final_state seeds the last piece)
+                2. ONE all_gather of D_r
+                3. dfinal_r = sum_{q>r} (prod_{r<k<q} P_k) D_q  (one local kernel)
                 4. the full backward of the slice with init_r and dfinal_r
-                5. all_reduce of dA_head and dD over the sequence group
+                5. ONE all_reduce of the packed (dA_head | dD | d initial state)
 
-  Gathered buffers live in this GPU's own memory and are read with plain loads.
+  Each collective runs on a side stream behind the pass that produces its input, so that host work and the
+  preparation kernels of the next pass (cumulative sums) are not held up by it; the kernels that need the
+  gathered states wait for it through an event.  Gathered buffers live in this GPU's own memory and are read
+  with plain loads.
 
 The arithmetic is behind a small backend interface so that the communication schedule can be tested
 with CPU processes over gloo (the tests plug in a CPU backend); the default backend calls the CUDA
@@ -45,23 +49,70 @@ from . import ssd_scan as _op
 # communicators
 # ----------------------------------------------------------------------------------------------------
 class TorchDistComm:
-    """all_gather / all_reduce over a torch.distributed process group (NCCL on GPUs, gloo on CPU)."""
+    """all_gather / all_reduce of flat fp32 buffers over a torch.distributed process group (NCCL on GPUs, gloo on
+    CPU).  On CUDA tensors the collective is enqueued on a side stream behind the work already queued on the
+    current stream, and the current stream waits for it only when :meth:`wait` is called on the handle."""
 
     def __init__(self, group=None):
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
+        self._side = None
+        self.timings = None   # set to a list to record (name, start event, end event) of every collective
 
-    def all_gather(self, t: Tensor) -> Tensor:
-        flat = t.contiguous().reshape(-1)
-        out = torch.empty(self.world * flat.numel(), dtype=t.dtype, device=t.device)
-        dist.all_gather_into_tensor(out, flat, group=self.group)
-        return out.reshape((self.world,) + tuple(t.shape))
+    def read_timings(self) -> dict[str, float]:
+        """Total milliseconds per collective kind since ``timings`` was set (synchronises)."""
+        out: dict[str, float] = {}
+        for name, e0, e1 in self.timings or []:
+            e1.synchronize()
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        return out
 
-    def all_reduce_sum(self, t: Tensor) -> Tensor:
-        c = t.contiguous()
-        dist.all_reduce(c, op=dist.ReduceOp.SUM, group=self.group)
-        return c
+    def _side_stream(self, dev):
+        if self._side is None:
+            self._side = torch.cuda.Stream(dev)
+        return self._side
+
+    def _run(self, t: Tensor, fn, name: str):
+        if not t.is_cuda:
+            fn()
+            return None
+        cur = torch.cuda.current_stream(t.device)
+        side = self._side_stream(t.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            rec = self.timings is not None
+            if rec:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e0.record(side)
+            fn()
+            ev = torch.cuda.Event(enable_timing=rec)
+            ev.record(side)
+            if rec:
+                self.timings.append((name, e0, ev))
+        return ev
+
+    def all_gather(self, flat: Tensor):
+        """flat (N,) contiguous -> (world * N,) with rank r's data at [r*N, (r+1)*N); returns (tensor, handle)."""
+        if flat.dim() != 1 or not flat.is_contiguous():
+            raise ValueError("all_gather takes a flat contiguous buffer")
+        out = torch.empty(self.world * flat.numel(), dtype=flat.dtype, device=flat.device)
+        ev = self._run(flat, lambda: dist.all_gather_into_tensor(out, flat, group=self.group), "all_gather")
+        if ev is not None:
+            out.record_stream(self._side)
+            flat.record_stream(self._side)
+        return out, ev
+
+    def all_reduce_sum(self, flat: Tensor):
+        ev = self._run(flat, lambda: dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group), "all_reduce")
+        if ev is not None:
+            flat.record_stream(self._side)
+        return flat, ev
+
+    @staticmethod
+    def wait(handle) -> None:
+        if handle is not None:
+            torch.cuda.current_stream().wait_event(handle)
 
 
 def allreduce_head_grads(dA_head: Tensor, dD: Tensor | None, group=None) -> None:
@@ -92,41 +143,44 @@ class CudaBackend:
     def _shape(self, s: Slice):
         return _op._make_shape(s.x, _cabi.F32, s.B, s.chunk)
 
-    def states_only(self, s: Slice):
-        """Zero-init final state of the slice and its total log-decay: (F (b,h,p,n) fp32, logp (b,h) fp32, cum)."""
+    def states_only(self, s: Slice, out_F: Tensor | None = None, out_logp: Tensor | None = None):
+        """Summary of the slice for a zero incoming state: (F (b,h,p,n) fp32, logp (b,h) fp32, cum); F and logp are
+        written into ``out_F`` / ``out_logp`` when given (views of a gather buffer)."""
         lib = _cabi.load()
         b, T, h, p = s.x.shape
         n = s.B.shape[3]
         dev = s.x.device
         shape = self._shape(s)
         with torch.cuda.device(dev):
-            final = torch.empty(b, h, p, n, dtype=torch.float32, device=dev)
+            final = out_F if out_F is not None else torch.empty(b, h, p, n, dtype=torch.float32, device=dev)
+            logp = out_logp if out_logp is not None else torch.empty(b, h, dtype=torch.float32, device=dev)
             cum = torch.empty(b, h, T // s.chunk, s.chunk, dtype=torch.float32, device=dev)
             ws = _op._workspace(lib, shape, _cabi.PASS_FWD, dev)
             args = _cabi.FwdArgs(shape, _op._ptr(s.x), None, _op._ptr(s.dt), _op._ptr(s.A_head), None, _op._ptr(s.B),
                                  _op._ptr(s.C), None, None, _op._ptr(final), _op._ptr(cum), 0, _cabi.FWD_STATES_ONLY,
-                                 _op._ptr(ws), ws.numel(), None)
+                                 _op._ptr(ws), ws.numel(), None, _op._ptr(logp))
             _cabi.check(lib.ssd_b200_fwd(C.byref(args), _op._stream(dev)))
             _op._status(lib, shape, ws, dev)
-        logp = cum[..., -1].sum(-1)
         return final, logp, cum
 
     def forward(self, s: Slice, init: Tensor | None, cum: Tensor):
-        y, final, cum, shape, states = _op._run_fwd(s.x, None, s.dt, s.A_head, s.D, s.B, s.C, s.chunk, init, None,
+        # the within-chunk cumulative sums of the summary pass are reused, not rebuilt
+        y, final, cum, shape, states = _op._run_fwd(s.x, None, s.dt, s.A_head, s.D, s.B, s.C, s.chunk, init, cum,
                                                     want_states=True)
         return y, final, {"cum": cum, "shape": shape, "states": states}
 
-    def dinit_only(self, s: Slice, saved: dict, dy: Tensor) -> Tensor:
+    def dinit_only(self, s: Slice, saved: dict, dy: Tensor, dfinal: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+        """d(initial state) of the slice from dy, C and the decays alone, for the given dfinal (None = zero)."""
         lib = _cabi.load()
         b, T, h, p = s.x.shape
         dev = s.x.device
         shape = saved["shape"]
         with torch.cuda.device(dev):
-            dinit = torch.empty(b, h, p, s.B.shape[3], dtype=torch.float32, device=dev)
+            dinit = out if out is not None else torch.empty(b, h, p, s.B.shape[3], dtype=torch.float32, device=dev)
             ws = _op._workspace(lib, shape, _cabi.PASS_BWD, dev)
             args = _cabi.BwdArgs(shape, None, None, None, None, None, None, _op._ptr(s.C), None, _op._ptr(saved["cum"]),
-                                 _op._ptr(dy), None, None, None, None, None, None, None, None, _op._ptr(dinit), 0,
-                                 _cabi.BWD_DINIT_ONLY, _op._ptr(ws), ws.numel(), None)
+                                 _op._ptr(dy), _op._ptr(dfinal), None, None, None, None, None, None, None,
+                                 _op._ptr(dinit), 0, _cabi.BWD_DINIT_ONLY, _op._ptr(ws), ws.numel(), None)
             _cabi.check(lib.ssd_b200_bwd(C.byref(args), _op._stream(dev)))
             _op._status(lib, shape, ws, dev)
         return dinit
@@ -152,15 +206,22 @@ class CudaBackend:
             _op._status(lib, shape, ws, dev)
         return out
 
-    def prefix(self, states: Tensor, logp: Tensor, index: int, reverse: bool) -> Tensor:
-        """states (R,b,h,p,n), logp (R,b,h) -> combination seen by position `index` (see ssd_b200_state_prefix)."""
+    def prefix_all(self, pieces: Tensor, logp: Tensor, edge: Tensor | None, rank: int, reverse: bool) -> Tensor:
+        """pieces (R,b,S,h,p,n) and logp (R,b,S,h): summaries and total log-decays of all R*S pieces (rank-major; the
+        rank dimension may be strided, the rest dense).  Returns (b*S,h,p,n): for each of rank's S pieces the state
+        entering it (forward) or the state gradient leaving it (reverse); ``edge`` (b,h,p,n) is the state before the
+        first piece / the gradient behind the last one.  One launch, every piece read once."""
         lib = _cabi.load()
-        R, b, h, p, n = states.shape
-        dev = states.device
+        R, b, S, h, p, n = pieces.shape
+        dev = pieces.device
+        assert pieces[0].is_contiguous() and logp[0].is_contiguous()
         with torch.cuda.device(dev):
-            out = torch.empty(b, h, p, n, dtype=torch.float32, device=dev)
-            _cabi.check(lib.ssd_b200_state_prefix(_op._ptr(states.contiguous()), _op._ptr(logp.contiguous()), _op._ptr(out),
-                                                  R, index, b, h, p * n, 1 if reverse else 0, _op._stream(dev)))
+            out = torch.empty(b * S, h, p, n, dtype=torch.float32, device=dev)
+            ed = None if edge is None else edge.float().contiguous()
+            _cabi.check(lib.ssd_b200_state_prefix_all(
+                _op._ptr(pieces), _op._ptr(logp), _op._ptr(ed), _op._ptr(out), R, rank, S, b, h, p * n,
+                pieces.stride(0) if R > 1 else b * S * h * p * n, logp.stride(0) if R > 1 else b * S * h,
+                1 if reverse else 0, _op._stream(dev)))
         return out
 
 
@@ -171,11 +232,15 @@ class LoopbackComm:
     """A group of one: used when the sequence is only cut into segments inside a single GPU."""
     rank, world = 0, 1
 
-    def all_gather(self, t: Tensor) -> Tensor:
-        return t.unsqueeze(0)
+    def all_gather(self, flat: Tensor):
+        return flat, None
 
-    def all_reduce_sum(self, t: Tensor) -> Tensor:
-        return t
+    def all_reduce_sum(self, flat: Tensor):
+        return flat, None
+
+    @staticmethod
+    def wait(handle) -> None:
+        pass
 
 
 class _SeqSplitSSD(torch.autograd.Function):
@@ -193,20 +258,18 @@ class _SeqSplitSSD(torch.autograd.Function):
         seg = Slice(x.contiguous().view(b * S, Ts, h, p), dt.float().contiguous().view(b * S, Ts, h),
                     A_head.float().contiguous(), B.contiguous().view(b * S, Ts, g, n),
                     C_.contiguous().view(b * S, Ts, g, n), None if D is None else D.float().contiguous(), int(chunk))
-        F_loc, logp, cum = backend.states_only(seg)                              # (b*S,h,p,n), (b*S,h)
-        Fs = F_loc.view(b, S, h, p, n).transpose(0, 1).contiguous()              # (S,b,h,p,n)
-        lps = logp.view(b, S, h).transpose(0, 1).contiguous()                    # (S,b,h)
-        allF = comm.all_gather(Fs).reshape(comm.world * S, b, h, p, n)           # piece index = rank*S + segment
-        allP = comm.all_gather(lps).reshape(comm.world * S, b, h)
-        init_g = torch.zeros_like(Fs[0]) if initial_state is None else initial_state.reshape(b, h, p, n).float()
-        # a virtual piece in front carries the caller's initial state, so piece q sits at index q + 1
-        states = torch.cat([init_g.unsqueeze(0), allF])
-        lpv = torch.cat([torch.zeros_like(allP[:1]), allP])
-        base = comm.rank * S
-        inits = torch.stack([backend.prefix(states, lpv, base + s + 1, reverse=False) for s in range(S)], dim=1)
-        inits = inits.reshape(b * S, h, p, n).contiguous()
+        # one rank's block of the gather: the S summaries (b,S,h,p,n) followed by the S total log-decays (b,S,h)
+        nF, nP = b * S * h * p * n, b * S * h
+        pack = torch.empty(nF + nP, dtype=torch.float32, device=x.device)
+        _, _, cum = backend.states_only(seg, pack[:nF].view(b * S, h, p, n), pack[nF:].view(b * S, h))
+        gathered, hnd = comm.all_gather(pack)
+        G = gathered.view(comm.world, nF + nP)
+        pieces, logp = G[:, :nF].view(comm.world, b, S, h, p, n), G[:, nF:].view(comm.world, b, S, h)
+        edge = None if initial_state is None else initial_state.reshape(b, h, p, n)
+        comm.wait(hnd)
+        inits = backend.prefix_all(pieces, logp, edge, comm.rank, reverse=False)
         y, final, saved = backend.forward(seg, inits, cum)
-        ctx.seg, ctx.saved, ctx.inits, ctx.allP = seg, saved, inits, allP
+        ctx.seg, ctx.saved, ctx.inits, ctx.logp = seg, saved, inits, logp
         ctx.comm, ctx.backend, ctx.S, ctx.dims = comm, backend, S, (b, T, h, p, n, g)
         ctx.has_init = initial_state is not None
         ctx.init_shape = None if initial_state is None else tuple(initial_state.shape)
@@ -217,26 +280,35 @@ class _SeqSplitSSD(torch.autograd.Function):
         seg, comm, backend, S = ctx.seg, ctx.comm, ctx.backend, ctx.S
         b, T, h, p, n, g = ctx.dims
         dys = dy.contiguous().to(seg.x.dtype).view(b * S, T // S, h, p)
-        Dl = backend.dinit_only(seg, ctx.saved, dys).view(b, S, h, p, n).transpose(0, 1).contiguous()
-        allD = comm.all_gather(Dl).reshape(comm.world * S, b, h, p, n)
-        # the caller's d final_state belongs to the last piece of the last rank: a virtual piece behind it
-        extra = torch.zeros_like(Dl[0])
-        if dfinal_global is not None and comm.rank == comm.world - 1:
-            extra = dfinal_global.float().contiguous()
-        extra = comm.all_reduce_sum(extra.clone())
-        dstates = torch.cat([allD, extra.unsqueeze(0)])
-        dlp = torch.cat([ctx.allP, torch.zeros_like(ctx.allP[:1])])
-        base = comm.rank * S
-        dfin = torch.stack([backend.prefix(dstates, dlp, base + s, reverse=True) for s in range(S)], dim=1)
-        gr = backend.backward(seg, ctx.saved, ctx.inits, dys, dfin.reshape(b * S, h, p, n).contiguous())
-        dAh = comm.all_reduce_sum(gr["dA_head"])
-        dD = None if gr["dD"] is None else comm.all_reduce_sum(gr["dD"])
-        dinit = None
+        # the caller's d final_state belongs to the last piece of the last rank: it seeds that piece's summary and is
+        # that piece's own dfinal
+        last = comm.rank == comm.world - 1 and dfinal_global is not None
+        seed = None
+        if last:
+            seed = torch.zeros(b, S, h, p, n, dtype=torch.float32, device=dys.device)
+            seed[:, -1] = dfinal_global.float()
+            seed = seed.view(b * S, h, p, n)
+        Dl = torch.empty(b * S * h * p * n, dtype=torch.float32, device=dys.device)
+        backend.dinit_only(seg, ctx.saved, dys, seed, Dl.view(b * S, h, p, n))
+        gathered, hnd = comm.all_gather(Dl)
+        pieces = gathered.view(comm.world, b, S, h, p, n)
+        comm.wait(hnd)
+        dfin = backend.prefix_all(pieces, ctx.logp, None, comm.rank, reverse=True)
+        if last:
+            dfin.view(b, S, h, p, n)[:, -1] += dfinal_global.float()
+        gr = backend.backward(seg, ctx.saved, ctx.inits, dys, dfin)
+        # one all_reduce: dA_head | dD | d initial state (only rank 0's first piece carries the latter)
+        parts = [gr["dA_head"].reshape(-1)]
+        if gr["dD"] is not None:
+            parts.append(gr["dD"].reshape(-1))
         if ctx.has_init:
-            d0 = gr["dinit"].view(b, S, h, p, n)[:, 0].contiguous()
-            if comm.rank != 0:
-                d0 = torch.zeros_like(d0)
-            dinit = comm.all_reduce_sum(d0).reshape(ctx.init_shape)
+            d0 = gr["dinit"].view(b, S, h, p, n)[:, 0].reshape(-1)
+            parts.append(d0 if comm.rank == 0 else torch.zeros_like(d0))
+        red, hnd = comm.all_reduce_sum(torch.cat(parts))
+        comm.wait(hnd)
+        dAh = red[:h]
+        dD = None if gr["dD"] is None else red[h:2 * h]
+        dinit = red[-b * h * p * n:].reshape(ctx.init_shape) if ctx.has_init else None
         return (gr["dx"].view(b, T, h, p), gr["ddt"].view(b, T, h), dAh, gr["dB"].view(b, T, g, n),
                 gr["dC"].view(b, T, g, n), dD, None, dinit, None, None, None)
 
@@ -258,20 +330,20 @@ def emulate_sequence_parallel(slices: list[Slice], dys: list[Tensor], initial_st
     backend = backend if backend is not None else _DEFAULT_BACKEND
     R = len(slices)
     p1 = [backend.states_only(s) for s in slices]
-    F = torch.stack([t[0] for t in p1])
-    lp = torch.stack([t[1] for t in p1])
-    init_g = torch.zeros_like(F[0]) if initial_state is None else initial_state.reshape(F[0].shape).float()
-    states = torch.cat([init_g.unsqueeze(0), F])
-    lps = torch.cat([torch.zeros_like(lp[:1]), lp])
-    inits = [backend.prefix(states, lps, r + 1, reverse=False) for r in range(R)]
+    b, h, p, n = p1[0][0].shape
+    F = torch.stack([t[0] for t in p1]).view(R, b, 1, h, p, n)   # one segment per rank
+    lp = torch.stack([t[1] for t in p1]).view(R, b, 1, h)
+    edge = None if initial_state is None else initial_state.reshape(b, h, p, n)
+    inits = [backend.prefix_all(F, lp, edge, r, reverse=False) for r in range(R)]
     fw = [backend.forward(s, inits[r], p1[r][2]) for r, s in enumerate(slices)]
-    Dl = torch.stack([backend.dinit_only(s, fw[r][2], dys[r].contiguous()) for r, s in enumerate(slices)])
-    extra = torch.zeros_like(Dl[0]) if dfinal is None else dfinal.float().contiguous()
-    dstates = torch.cat([Dl, extra.unsqueeze(0)])
-    dlps = torch.cat([lp, torch.zeros_like(lp[:1])])
+    seeds = [None] * (R - 1) + [None if dfinal is None else dfinal.float().contiguous()]
+    Dl = torch.stack([backend.dinit_only(s, fw[r][2], dys[r].contiguous(), seeds[r]) for r, s in enumerate(slices)])
+    Dl = Dl.view(R, b, 1, h, p, n)
     out = []
     for r, s in enumerate(slices):
-        dfin_r = backend.prefix(dstates, dlps, r, reverse=True)
+        dfin_r = backend.prefix_all(Dl, lp, None, r, reverse=True)
+        if r == R - 1 and dfinal is not None:
+            dfin_r = dfin_r + dfinal.float()
         g = backend.backward(s, fw[r][2], inits[r], dys[r].contiguous(), dfin_r)
         g["y"], g["final"] = fw[r][0], fw[r][1]
         out.append(g)

@@ -149,7 +149,10 @@ def kernel_algorithmic_bytes(cfg: SSDConfig) -> dict[str, int]:
     """Algorithmic HBM bytes ONE launch of each kernel moves for this workload: the operator inputs it
     must read and the operator outputs it must write, each once at storage width.  Intermediates
     (chunk states, cumulative decays, partial sums) count zero, so a kernel that re-reads or spills
-    shows up as a lower achieved bandwidth."""
+    shows up as a lower achieved bandwidth.  The backward of the tensor-core path is two kernels that both
+    need dy and C (the reverse walk for the state gradients, the tile kernel for everything else): each is
+    charged what it must read itself, so those two add up to `ex + eb` more than the backward's share of
+    ``bytes_per_token``; whole-step figures always use ``bytes_per_token``."""
     w = 2 if cfg.dtype == "bf16" else 4
     ex = cfg.nheads * cfg.headdim * w
     eb = cfg.ngroups * cfg.d_state * w
@@ -164,7 +167,8 @@ def kernel_algorithmic_bytes(cfg: SSDConfig) -> dict[str, int]:
         "bwd_col": 3 * ex + 3 * eb + edt,
         "decay_grad": 2 * edt,
         "tc_fwd_walk": 2 * ex + 2 * eb + edt,
-        "tc_bwd_state": 2 * ex + 2 * eb + edt,
+        "tc_bwd_state": ex + eb,
+        "tc_summary": ex + eb,
         "tc_bwd_walk": 3 * ex + 4 * eb + 2 * edt,
     }
     return {k: v * tok for k, v in per_token.items()}

@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define SSD_B200_ABI_VERSION 1
+#define SSD_B200_ABI_VERSION 2
 
 enum {
     SSD_B200_OK = 0,
@@ -58,9 +58,9 @@ enum { SSD_B200_PATH_AUTO = 0, SSD_B200_PATH_SIMT = 1, SSD_B200_PATH_TC = 2 };
 
 /* Partial passes used by the sequence-parallel schedule (each rank holds a contiguous slice of the
  * sequence and only per-rank states cross NVLink):
- *   SSD_B200_FWD_STATES_ONLY  forward: write final_state (and a_cumsum) only; y may be NULL.
- *   SSD_B200_BWD_DINIT_ONLY   backward: from dy, C and a_cumsum alone write dinit, the gradient of the
- *                             initial state for a zero dfinal; every other output may be NULL. */
+ *   SSD_B200_FWD_STATES_ONLY  forward: write final_state (and a_cumsum, logdecay_total) only; y may be NULL.
+ *   SSD_B200_BWD_DINIT_ONLY   backward: from dy, C, a_cumsum (and dfinal, NULL = zero) alone write dinit, the
+ *                             gradient of the initial state; every other output may be NULL. */
 enum { SSD_B200_FWD_STATES_ONLY = 1 };
 enum { SSD_B200_BWD_DINIT_ONLY = 1 };
 
@@ -108,6 +108,8 @@ typedef struct ssd_b200_fwd_args {
                      128-position tile and the per-position decay arrays of the tile kernels, in the layout
                      the backward wants.  Passing the same buffer to ssd_b200_bwd (same inputs) saves it the
                      state walk and the rebuild of those arrays; NULL = do not save. */
+    float *logdecay_total; /* optional output (b,h) fp32: the sum of the sequence's log-decays per (batch, head),
+                              i.e. log of the factor by which the whole sequence scales an incoming state */
 } ssd_b200_fwd_args;
 
 /*
@@ -216,17 +218,28 @@ int ssd_b200_materialize_cache(const ssd_b200_shape *shape, const float *a_cumsu
                                void *decay_chunk, int32_t dtype, void *stream);
 
 /*
- * Sequence-parallel state prefix (no counterpart in the reference, which has no multi-GPU
- * path; it builds on the operator's initial_states / final_state contract,
- * src/kernels/ssd_scan.py:395-397, :410).  `finals` (R,b,h,p,n) fp32 holds every rank's
- * zero-init final state and `logp` (R,b,h) fp32 every rank's total log-decay, both already
- * gathered into THIS GPU's memory.  Writes
- *   out[b,h,p,n] = sum_{q<rank} exp(sum_{q<k<rank} logp[k]) * finals[q]      (reverse == 0)
- *   out[b,h,p,n] = sum_{q>rank} exp(sum_{rank<k<q} logp[k]) * finals[q]      (reverse != 0)
+ * Sequence-parallel state prefix (no counterpart in the reference, which has no multi-GPU path; it builds on
+ * the operator's initial_states / final_state contract, src/kernels/ssd_scan.py:395-397, :410, and on
+ * d final_state in / d initial_states out, :468, :530-533).
+ *
+ * The sequence is cut into nranks * segments consecutive pieces, piece g = r * segments + s.  Every piece has a
+ * summary (what it adds to the state after it for a zero state before it -- ssd_b200_fwd with
+ * SSD_B200_FWD_STATES_ONLY -- or, in reverse, what it adds to the gradient of the state before it --
+ * ssd_b200_bwd with SSD_B200_BWD_DINIT_ONLY) and a total log-decay (logdecay_total of the forward).  All of
+ * them are already in THIS GPU's memory (e.g. after an all_gather): rank r's summaries at
+ * pieces + r * rank_stride as (batch, segments, h, state_elems) fp32, its log-decays at
+ * logp + r * logp_stride as (batch, segments, h) fp32 (strides in floats).  One launch writes into
+ * out (batch, segments, h, state_elems), for each of the `segments` pieces of `rank`,
+ *   reverse == 0:  the state entering the piece,       acc_0 = edge,    acc_{g+1} = exp(logp_g) acc_g + pieces_g
+ *   reverse != 0:  the state gradient leaving the piece, acc_last = edge, acc_{g-1} = exp(logp_g) acc_g + pieces_g
+ * with edge (batch, h, state_elems) the caller's initial state / final-state gradient, or NULL for zero.  Every
+ * piece is read once.  The outputs are in the layout ssd_b200_fwd / _bwd take as init / dfinal when the
+ * segments run as batch entries (entry = batch index * segments + s).
  */
-int ssd_b200_state_prefix(const float *finals, const float *logp, float *out, int64_t nranks,
-                          int64_t rank, int64_t batch, int64_t nheads, int64_t state_elems,
-                          int32_t reverse, void *stream);
+int ssd_b200_state_prefix_all(const float *pieces, const float *logp, const float *edge, float *out,
+                              int64_t nranks, int64_t rank, int64_t segments, int64_t batch, int64_t nheads,
+                              int64_t state_elems, int64_t rank_stride, int64_t logp_stride, int32_t reverse,
+                              void *stream);
 
 /*
  * Element-wise kernels of the Mamba-3 style variant (no counterpart in the reference's operator file: its

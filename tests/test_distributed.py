@@ -31,21 +31,31 @@ class OracleBackend:
         return self.O.mamba2_operator(s.x, s.dt, s.A_head, s.B, s.C, s.D, s.chunk,
                                       None if init is None else init.unsqueeze(1))
 
-    def states_only(self, s):
+    def states_only(self, s, out_F=None, out_logp=None):
         with torch.no_grad():
             _, final = self._run(s, None)
-        return final, (s.dt * s.A_head).sum(1), None
+        logp = (s.dt * s.A_head).sum(1)
+        if out_F is not None:
+            out_F.copy_(final)
+            out_logp.copy_(logp)
+        return final, logp, None
 
     def forward(self, s, init, cum):
         with torch.no_grad():
             y, final = self._run(s, init)
         return y, final, {}
 
-    def dinit_only(self, s, saved, dy):
+    def dinit_only(self, s, saved, dy, dfinal=None, out=None):
         init0 = torch.zeros(s.x.shape[0], s.x.shape[2], s.x.shape[3], s.B.shape[3], dtype=s.x.dtype, requires_grad=True)
         with torch.enable_grad():
-            y, _ = self._run(s, init0)
-        return torch.autograd.grad([y], [init0], [dy])[0]
+            y, final = self._run(s, init0)
+        if dfinal is None:
+            d = torch.autograd.grad([y], [init0], [dy])[0]
+        else:
+            d = torch.autograd.grad([y, final], [init0], [dy, dfinal])[0]
+        if out is not None:
+            out.copy_(d)
+        return d
 
     def backward(self, s, saved, init, dy, dfinal):
         lv = {k: getattr(s, k).detach().clone().requires_grad_(True) for k in ("x", "dt", "A_head", "B", "C", "D")}
@@ -58,12 +68,18 @@ class OracleBackend:
         out["dinit"] = g[-1]
         return out
 
-    def prefix(self, states, logp, index, reverse):
-        acc = torch.zeros_like(states[0])
-        rng = range(states.shape[0] - 1, index, -1) if reverse else range(index)
-        for q in rng:
-            acc = torch.exp(logp[q])[..., None, None] * acc + states[q]
-        return acc
+    def prefix_all(self, pieces, logp, edge, rank, reverse):
+        R, b, S, h, p, n = pieces.shape
+        P = pieces.transpose(1, 2).reshape(R * S, b, h, p, n)   # piece-major
+        L = logp.transpose(1, 2).reshape(R * S, b, h)
+        acc = torch.zeros_like(P[0]) if edge is None else edge.reshape(P[0].shape).to(P.dtype).clone()
+        out = [None] * S
+        order = range(R * S - 1, rank * S - 1, -1) if reverse else range(rank * S + S)
+        for g in order:
+            if rank * S <= g < rank * S + S:
+                out[g - rank * S] = acc
+            acc = torch.exp(L[g])[..., None, None] * acc + P[g]
+        return torch.stack(out, dim=1).reshape(b * S, h, p, n)
 
 
 def _small_cfg(pkg):
