@@ -20,7 +20,7 @@ namespace prof {
 const char* const kNames[K_COUNT] = {
     "chunk_cumsum", "chunk_state", "state_passing", "chunk_scan", "chunk_dstate", "state_passing_rev",
     "bwd_row", "bwd_col", "decay_grad", "reduce_batch", "cache_L", "cache_decay_chunk", "state_prefix",
-    "tc_fwd_walk", "tc_bwd_state", "tc_bwd_walk", "tc_aux", "tc_summary"};
+    "tc_fwd_walk", "tc_bwd_state", "tc_bwd_walk", "tc_aux", "tc_summary", "tc_bwd_walk_alt", "tc_fwd_walk_alt"};
 std::atomic<long long> g_launches{0};
 bool g_enabled = false;
 struct Rec {

@@ -15,7 +15,7 @@
 //   summary_kernel      what a whole piece of the sequence adds to the state after it / to the state gradient
 //                       before it (the quantities the sequence-parallel schedule exchanges): a stream, no recurrence
 //   rev_walk_kernel     reverse walk of the backward pass, Q <- e^{S} Q + dY^T diag(e) C, software-pipelined
-//                       over tiles; stores Q_k = dH_{k+1} as bf16 and the state parts of the decay gradient
+//                       over tiles; reads dY and C only, stores Q_k = dH_{k+1} as bf16
 //   bwd_tile_kernel     one CTA per (batch, tile, group), heads of the group in an inner loop so
 //                       that dB and dC accumulate over heads in TMEM:
 //        dG = dY X^T, dS = dG o L, dX = G^T dY + diag(d) B Q^T, dC += dS B + diag(e) dY H,
@@ -39,7 +39,9 @@ constexpr int PANEL = 16384;  // bytes of one [128 rows][64 bf16] swizzled panel
 // The decay mask of a 32-column block is the product of a per-row and a per-column factor taken relative to the
 // block's last column.  Below the diagonal both are <= 1.  Inside the diagonal block the row factor is
 // 2^(decay from the row to the block end) >= 1 and the column factor its inverse scale; beyond this many log2
-// units across the block one of them would leave the fp32 range, and the block is evaluated entry by entry.
+// units across a block one of them would leave the fp32 range.  tile_cumsum_kernel raises a flag when any block
+// of the call exceeds it, and the kernels that build the mask carry two bodies: the factorised one, and one that
+// evaluates diagonal blocks entry by entry (one exp2 per entry); the flag selects the body on the device.
 constexpr float kMaskSafeLog2 = 100.f;
 
 inline bool supported(int dtype, int T, int h, int p, int n, int g, int l) {
@@ -52,8 +54,8 @@ inline bool supported(int dtype, int T, int h, int p, int n, int g, int l) {
 // Tile-cumulative log2 decay and dt in (b,h,T) order, one block per (128-tile, 32 heads, batch): dt arrives in the
 // caller's (b,T,h) order and goes through a shared-memory transpose, so reads and writes are both 128-byte rows.
 __global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restrict__ cum, const float* __restrict__ dt,
-                                                          float* __restrict__ tcum, float* __restrict__ dtT, int b, int T,
-                                                          int h, int l) {
+                                                          float* __restrict__ tcum, float* __restrict__ dtT,
+                                                          int* __restrict__ extreme, int b, int T, int h, int l) {
     __shared__ float sdt[LT][33];
     const int kt = blockIdx.x, hg = blockIdx.y, bb = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -85,7 +87,11 @@ __global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restric
                 const int k0 = kt * (LT / l);
                 for (int kk = k0; kk < k; ++kk) v += cu[(size_t)kk * l + l - 1];
             }
-            tcum[o + tt] = v * 1.4426950408889634f;  // stored in log2 units: every consumer uses exp2
+            v *= 1.4426950408889634f;  // stored in log2 units: every consumer uses exp2
+            tcum[o + tt] = v;
+            // decay across this 32-position block (lane 0 to lane 31)
+            const float span = __shfl_sync(0xffffffffu, v, 0) - __shfl_sync(0xffffffffu, v, 31);
+            if (lane == 0 && !(span <= kMaskSafeLog2)) atomicOr(extreme, 1);
             if (dt) dtT[o + tt] = sdt[tt][hl];
         }
     }
@@ -94,7 +100,7 @@ __global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restric
 // ------------------------------------------------------------------------------------------
 // Decay gradient of the tensor-core backward, one block per (128-tile, 32 heads, batch).
 // Inputs in (b,h,T) layout (coalesced along t): the per-row gradients g w.r.t. the tile-cumulative
-// log-decay, ddtx = sum_p dX x, dyx = sum_p dy x, and gS / gS2, the terms that act through the tile's last row.  Within a tile
+// log-decay, ddtx = sum_p dX x, dyx = sum_p dy x, and gS, the terms that act through the tile's last row.  Within a tile
 //   dA[t] = sum_{t' >= t} g[t']      (a suffix sum, four 32-lane segments per warp and head)
 // and  ddt = ddtx + dA A_head,  dA_head += dA dt,  dD += dyx.  dt is read and ddt / da written in the
 // caller's (b,T,h) layout through a shared-memory transpose, so both sides are 128-byte rows.
@@ -102,8 +108,7 @@ struct DecayTileParams {
     const float* g;      // (b,h,T)
     const float* ddtx;   // (b,h,T)
     const float* dyx;    // (b,h,T) or null
-    const float* gS;     // (b,h,nt,8) from the reverse walk
-    const float* gS2;    // (b,h,nt,8) from the backward tile kernel
+    const float* gS;     // (b,h,nt,8) from the backward tile kernel: terms that act through the tile's last row
     const float* dt;     // (b,T,h) or null (operator form)
     const float* A_head; // (h) or null
     float* ddt;          // (b,T,h) or null
@@ -143,10 +148,8 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
                 dxa[i][s4] = P.ddtx[base + t];
                 if (P.dyx) yxa[i] += P.dyx[base + t];
             }
-            if (lane < 16) {  // the 2 x 8 terms that act through the tile's last row, one per lane
-                const size_t so = ((((size_t)bb * P.h + hh) * P.nt) + k) * 8;
-                gsa[i] = lane < 8 ? P.gS[so + lane] : P.gS2[so + lane - 8];
-            }
+            if (lane < 8)  // the eight terms that act through the tile's last row, one per lane
+                gsa[i] = P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + lane];
         }
     }
     __syncthreads();
@@ -161,10 +164,9 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
             dx[s4] = dxa[i][s4];
         }
         {
-            float gs = gsa[i];  // fixed-order sum of the sixteen terms, result in every lane
+            float gs = gsa[i];  // fixed-order sum of the eight terms (the other lanes hold zero), result in every lane
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
-            gs += __shfl_xor_sync(0xffffffffu, gs, 16);
+            for (int o = 16; o > 0; o >>= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
             if (lane == 31) v[3] += gs;
         }
         // suffix sums: inside each 32-lane segment by shuffles, then the totals of the later segments
@@ -231,7 +233,7 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restric
 struct WalkParams {
     CUtensorMap mU;   // x (modes 0,1) or dy (reverse walks): 2D [b*T][h*64]
     CUtensorMap mV;   // B (modes 0,1) or C (reverse walks):  2D [b*T][g*128]
-    CUtensorMap mC;   // C (mode 0); rev_walk_kernel: the stored forward states, 2D [b*nt*h*128][64]
+    CUtensorMap mC;   // C (mode 0)
     const float* tcum;
     const float* dtT;
     const float* D;
@@ -240,8 +242,7 @@ struct WalkParams {
     CUtensorMap mY;   // y store (mode 0)
     CUtensorMap mS;   // state store: 2D [b*nt*h*128][64]
     int save_states;  // store the state entering every tile of the walk through mS
-    float* gS;           // rev_walk_kernel: (b,h,nt,8) per warp exp(S_k) <Q_k, H_k>
-    float* rterm;        // rev_walk_kernel: (2,b,h,T) halves of e_i * sum_p dY[i,p] (C_i . H_k[p,:])
+    const int* extreme;  // see kMaskSafeLog2 (forward only)
     int* status;
     int T, h, hpg, nt;
 };

@@ -7,8 +7,9 @@
 //   phase 1   S = C B^T,  dG = dY x^T                                     (TMEM, 2 x 128 columns)
 //   mask      G = S o L (bf16 -> smem),  dS_h = dG o L o dt  (summed over heads in registers),
 //             Xd = d dt x (in place in smem),  dYe = e dY (bf16 pairs -> TMEM)
-//   phase 2   dX1 = G^T dY,  dX2 = B Q^T,  dC += dYe H,  dB += Xd Q       (dC, dB persist in TMEM)
-//   rows      dx = dt (dX1 + d dX2) + D dy,  and the decay-gradient terms of the row
+//   phase 2   dX1 = G^T dY,  dX2 = B Q^T,  Yo = C H^T,  dC += dYe H,  dB += Xd Q   (dC, dB persist in TMEM)
+//   rows      dx = dt (dX1 + d dX2) + D dy,  and the decay-gradient terms of the row, among them the two that
+//             come from the state entering the tile: e_i <dY_i, Yo_i> for the row and exp(S) <Q, H> for the tile
 // and once per group, after the heads:  dC += (sum_h dS_h) B,  dB += (sum_h dS_h)^T C.
 //
 // 512 threads: thread = (row, column quarter).  TMEM lanes are tied to warp % 4, so the rows 96-127, whose
@@ -34,12 +35,11 @@ struct BwdParams {
     const float* tcum;             // (b,h,T) tile-cumulative log2-decay
     const float* dtT;              // (b,h,T) or null
     const float* D;                // (h) or null
-    const float* rterm;            // (2,b,h,T) state part of d/dcum from the reverse walk
     float* g;                      // (b,h,T) gradient w.r.t. the tile-cumulative log-decay
     float* ddtx;                   // (b,h,T) sum_p dX * x
     float* dyx;                    // (b,h,T) sum_p dy * x
-    float* gS;                     // (b,h,nt,8): this kernel's terms that act through S = cum[127] of the
-                                   // tile (the reverse walk writes its own array of the same shape)
+    float* gS;                     // (b,h,nt,8): the terms that act through S = cum[127] of the tile
+    const int* extreme;            // nonzero: the decay across some 32-position block is beyond the factorised mask
     int* status;
     int T, h, hpg, nt, b;
     int items;                     // nt * groups * b work items (tile, group, batch), tile fastest
@@ -49,7 +49,12 @@ struct BwdParams {
 // 13 operand panels | scum2, sfL, sdt [2][128] | row partials [3][4][128] | warp partials [16] | alignment slack
 constexpr size_t kBwdSmem = 13 * PANEL + 6 * LT * 4 + 12 * LT * 4 + 64 + 1024;
 
+// Two instantiations (EXACT: diagonal mask blocks entry by entry, see kMaskSafeLog2); both are launched and the
+// extreme-decay flag decides on the device which of the two does the work (kept as separate kernels: as an
+// out-of-line body this kernel loses registers to the call and spills).
+template <bool EXACT>
 __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant__ BwdParams P) {
+    if ((P.extreme[0] != 0) != EXACT) return;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sC = sm;                  // 2 panels [pos][n]
@@ -113,7 +118,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
         tma_load_2d(sH, &P.mH, &bar_hq, 0, srow);
         tma_load_2d(sQ, &P.mQ, &bar_hq, 0, srow);
     };
-    const size_t bhT = (size_t)P.b * P.h * P.T;
     auto pos_of = [&](int hl) { return ((size_t)bb * P.h + gg * hpg + hl) * P.T + (size_t)k * LT; };
     // per-head row scalars are fetched one head ahead; the shared per-column arrays of head hl + 1 are
     // written before the last block-wide barrier of head hl
@@ -145,8 +149,9 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
     }
     const uint32_t tm = tmem_slot;
     // phase 1: S [0,128) dG [128,256); after the mask loop (barrier A) dX1 [0,64) and dX2 [64,128) take the S
-    // columns and dYe (bf16 pairs) the dG columns [128,160); persistent over heads: dC [256,384) dB [384,512)
-    const uint32_t tS = tm, tdG = tm + 128, tX1 = tm, tX2 = tm + 64, tdC = tm + 256, tdB = tm + 384;
+    // columns, dYe (bf16 pairs) the dG columns [128,160) and Yo = C H^T the dG columns [160,224); persistent over
+    // heads: dC [256,384) dB [384,512)
+    const uint32_t tS = tm, tdG = tm + 128, tX1 = tm, tX2 = tm + 64, tYo = tm + 160, tdC = tm + 256, tdB = tm + 384;
     const uint32_t lanes = lane_base(warp);
     const uint32_t c0a = smem_u32(sC), b0a = smem_u32(sB), g0a = smem_u32(sG), h0a = smem_u32(sH), q0a = smem_u32(sQ);
     auto issue_phase1 = [&](int hl, bool commit) {  // S = C B^T (K = n) and dG = dY x^T (K = p) of head hl
@@ -201,12 +206,6 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             dt_n = P.dtT ? P.dtT[o + row] : 1.f;
             D_n = P.D ? P.D[ngg * hpg] : 0.f;
         }
-        // state part of the gradient of this row (from the reverse walk): needed once per row, after the barrier (C)
-        float rt0 = 0.f, rt1 = 0.f;  // loaded here, first used after the barrier (C): no stall on the loads
-        if (qc == 0) {
-            rt0 = P.rterm[tpos];
-            rt1 = P.rterm[bhT + tpos];
-        }
         mbar_wait(&bar_xy[xb], (hcur >> 1) & 1, &failed);
         uint8_t* sX = sXY + (2 * xb) * PANEL;
         uint8_t* sdY = sX + PANEL;
@@ -243,14 +242,11 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
                 const float2* S2 = reinterpret_cast<const float2*>(rs);
                 const float2* G2 = reinterpret_cast<const float2*>(rg);
                 uint32_t gp[8];
-                // see the forward walk: inside the diagonal block the factorised mask is only used while the decay
-                // across the block stays inside the fp32 range (warp-uniform test)
-                const bool exact = diag && scum2[buf * LT + qc * 32] - scum2[buf * LT + qc * 32 + 31] > kMaskSafeLog2;
                 const float2* C2 = reinterpret_cast<const float2*>(scum2 + buf * LT + c0);
 #pragma unroll
                 for (int q2 = 0; q2 < 8; ++q2) {
                     float2 l;
-                    if (exact) {
+                    if (EXACT && diag) {  // see the forward walk: the diagonal block entry by entry
                         const float2 cj = C2[q2];
                         l.x = exp2f(c_i - cj.x);
                         l.y = exp2f(c_i - cj.y);
@@ -298,7 +294,12 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
                 const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
                 mma_ss(tX2, smem_desc(b0a + off, 16, 1024), smem_desc(q0a + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
             }
-            mma_commit(&bar_m2);  // the row epilogue only needs dX1 and dX2
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {  // Yo = C H^T : A = C K-major (K = n), B = H^T [n][p] MN-major
+                const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
+                mma_ss(tYo, smem_desc(c0a + off, 16, 1024), smem_desc(h0a + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
+            }
+            mma_commit(&bar_m2);  // the row epilogue needs dX1, dX2 and Yo
         }
         {   // Xd = d dt x in place (A operand of dB += Xd Q); dYe = e dY as bf16 pairs in TMEM
             uint32_t a[8];
@@ -337,7 +338,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
         }
         mbar_wait(&bar_m2, ph, &failed);
         tc_fence_after();
-        float ddt_acc, st_acc;
+        float ddt_acc, st_acc, qh_acc, yo_acc;
         {
             // fp32 pairs throughout: e = dX1 + d dX2, dx = dt e + D dy, and the two row sums <e, x>, <dX2, x>
             float2 ddt2 = make_float2(0.f, 0.f), st2 = make_float2(0.f, 0.f);
@@ -368,14 +369,45 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             *reinterpret_cast<uint4*>(sdX + sw128(row, qc * 2 + 1)) = make_uint4(dxp[4], dxp[5], dxp[6], dxp[7]);
             ddt_acc = ddt2.x + ddt2.y;
             st_acc = st2.x + st2.y;
+            // <Q, H> over this thread's 16 columns of state row n = `row` (both panels are [n][p] bf16; they stay put
+            // until the products that read them have completed, which is after the closing barrier of the head)
+            {
+                mbar_wait(&bar_hq, ph, &failed);  // long complete; every reader of the panels observes the barrier itself
+                float2 q2 = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    const uint4 hv = *reinterpret_cast<const uint4*>(sH + sw128(row, qc * 2 + ch));
+                    const uint4 qv = *reinterpret_cast<const uint4*>(sQ + sw128(row, qc * 2 + ch));
+                    const uint32_t* hu = reinterpret_cast<const uint32_t*>(&hv);
+                    const uint32_t* qu = reinterpret_cast<const uint32_t*>(&qv);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        q2 = fma2(__bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hu[q])),
+                                  __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu[q])), q2);
+                }
+                qh_acc = q2.x + q2.y;
+            }
+            // e_i <dY_i, Yo_i> over this thread's 16 columns (Yo = C H^T came with dX1 and dX2)
+            {
+                uint32_t o[16];
+                tmem_ld16(tYo + lanes + qc * 16, o);
+                tmem_ld_wait();
+                float2 r2 = make_float2(0.f, 0.f);
+                const float2* O2 = reinterpret_cast<const float2*>(o);
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    r2 = fma2(O2[q], __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&yr[q])), r2);
+                yo_acc = ei * (r2.x + r2.y);
+            }
         }
         {
             // gradient w.r.t. the tile-cumulative log-decay of this row, one partial per quarter, summed after the
-            // barrier; the terms that act through S = cum[127] (state weights d_j) are summed per warp
-            sred[(0 * 4 + qc) * LT + row] = rowacc - dtv * ddt_acc;
+            // barrier; the terms that act through S = cum[127] (state weights d_j, and the decay of the entering
+            // state) are summed per warp
+            sred[(0 * 4 + qc) * LT + row] = (rowacc - dtv * ddt_acc) + yo_acc;
             sred[(1 * 4 + qc) * LT + row] = ddt_acc;
             sred[(2 * 4 + qc) * LT + row] = dyx;
-            float red = dj * dtv * st_acc;
+            float red = dj * dtv * st_acc + exp2f(Sk) * qh_acc;
 #pragma unroll
             for (int of = 16; of > 0; of >>= 1) red += __shfl_xor_sync(0xffffffffu, red, of);
             if (lane == 0) swred[warp] = red;
@@ -386,7 +418,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
         __syncthreads();  // (C) dx staged, TMEM reads done, partial sums and next head's column arrays visible
         if (qc == 0) {
             // fixed order: deterministic
-            P.g[tpos] = ((sred[0 * LT + row] + sred[1 * LT + row]) + (sred[2 * LT + row] + sred[3 * LT + row])) + (rt0 + rt1);
+            P.g[tpos] = (sred[0 * LT + row] + sred[1 * LT + row]) + (sred[2 * LT + row] + sred[3 * LT + row]);
             P.ddtx[tpos] = (sred[4 * LT + row] + sred[5 * LT + row]) + (sred[6 * LT + row] + sred[7 * LT + row]);
             P.dyx[tpos] = (sred[8 * LT + row] + sred[9 * LT + row]) + (sred[10 * LT + row] + sred[11 * LT + row]);
             if (row < 8) P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + row] = swred[row] + swred[row + 8];

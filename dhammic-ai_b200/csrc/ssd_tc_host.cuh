@@ -1,5 +1,6 @@
 // Host side of the tensor-core path: tensor maps, workspace layout and launches.
 #pragma once
+#include <atomic>
 #include <cstdio>
 
 #include "../../include/ssd_b200.h"
@@ -38,7 +39,7 @@ inline bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t c
 }
 
 struct Ws {
-    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, rterm, gS, gS2, dAh_part, dD_part, total;
+    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, gS, dAh_part, dD_part, total;
 };
 
 inline Ws ws_layout(const Dims& d, int pass) {
@@ -63,9 +64,7 @@ inline Ws ws_layout(const Dims& d, int pass) {
         w.g = take(bht);
         w.ddtx = take(bht);
         w.dyx = take(bht);
-        w.rterm = take(2 * bht);
         w.gS = take((size_t)d.b * d.h * (d.T / LT) * 8 * 4);
-        w.gS2 = take((size_t)d.b * d.h * (d.T / LT) * 8 * 4);
         w.dAh_part = take((size_t)d.b * (d.T / LT) * d.h * 4);
         w.dD_part = take((size_t)d.b * (d.T / LT) * d.h * 4);
     }
@@ -76,9 +75,10 @@ inline Ws ws_layout(const Dims& d, int pass) {
 inline size_t workspace_bytes(const Dims& d, int pass) { return ws_layout(d, pass).total; }
 // The `states` buffer a forward call may fill for the backward call of the same inputs: the bf16 state entering
 // every tile, followed by the two (b,h,T) fp32 arrays the tile kernels read (tile-cumulative log2 decay, dt in
-// (b,h,T) order), so that the backward neither walks the states nor rebuilds those arrays.
+// (b,h,T) order) and the extreme-decay flag of tile_cumsum_kernel, so that the backward neither walks the states
+// nor rebuilds those arrays.
 inline size_t tile_states_bytes(const Dims& d) { return (size_t)d.b * (d.T / LT) * d.h * DN * HP * 2; }
-inline size_t states_bytes(const Dims& d) { return tile_states_bytes(d) + 2 * ((size_t)d.b * d.h * d.T * 4); }
+inline size_t states_bytes(const Dims& d) { return tile_states_bytes(d) + 2 * ((size_t)d.b * d.h * d.T * 4) + 256; }
 
 #define SSD_TC_FAIL(code, ...)              \
     do {                                    \
@@ -99,21 +99,33 @@ inline int sm_count() {  // SMs of the current device (one persistent CTA each)
     return n;
 }
 
+// Opt-in shared-memory sizes of the tensor-core kernels: set once per device and process (a function attribute
+// lives as long as the device's context; after cudaDeviceReset a launch fails with an error code, it does not misbehave).
 inline int set_walk_attrs(char* err, size_t errn) {
-    cudaError_t e = cudaFuncSetAttribute(walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<0>::SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WalkCfg<1>::SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRevSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSumSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSumSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem);
+    static std::atomic<unsigned long long> done{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return 0;
+    const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    cudaError_t e = cudaFuncSetAttribute(walk_kernel<0, false>, attr, (int)WalkCfg<0>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<0, true>, attr, (int)WalkCfg<0>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1, false>, attr, (int)WalkCfg<1>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel<1>, attr, (int)RevCfg<1>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel<2>, attr, (int)RevCfg<2>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<false>, attr, (int)kSumSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<true>, attr, (int)kSumSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel<false>, attr, (int)kBwdSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel<true>, attr, (int)kBwdSmem);
     if (e != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "set shared memory size: %s", cudaGetErrorString(e));
+    done.fetch_or(bit, std::memory_order_release);
     return 0;
 }
 
-inline int launch_tile_cumsum(const Dims& d, const float* cum, const float* dt, float* tcum, float* dtT,
+inline int launch_tile_cumsum(const Dims& d, const float* cum, const float* dt, float* tcum, float* dtT, int* extreme,
                               cudaStream_t st, char* err, size_t errn) {
     dim3 g(d.T / LT, (d.h + 31) / 32, d.b);
-    SSD_LAUNCH(prof::K_TC_AUX, st, tile_cumsum_kernel<<<g, 256, 0, st>>>(cum, dt, tcum, dtT, d.b, d.T, d.h, d.l));
+    SSD_LAUNCH(prof::K_TC_AUX, st, tile_cumsum_kernel<<<g, 256, 0, st>>>(cum, dt, tcum, dtT, extreme, d.b, d.T, d.h, d.l));
     SSD_TC_CHECK("tile_cumsum");
     return 0;
 }
@@ -129,11 +141,14 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     int* status = (int*)(ws + w.status);
     float* tcum = (float*)(ws + w.tcum);
     float* dtT = a->dt ? (float*)(ws + w.dtT) : nullptr;
+    int* extreme = status + 1;  // raised by tile_cumsum_kernel (see kMaskSafeLog2)
     if (a->states && !states_only) {  // kept for the backward call, behind the tile states
         tcum = (float*)((char*)a->states + tile_states_bytes(d));
         if (a->dt) dtT = tcum + (size_t)d.b * d.h * d.T;
+        extreme = (int*)(tcum + 2 * (size_t)d.b * d.h * d.T);
+        if (cudaMemsetAsync(extreme, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     }
-    if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
+    if (cudaMemsetAsync(status, 0, 8, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     if (!a->cumsum_is_input) {
         simt::Params P{};
         P.d = d; P.a = a->a; P.dt = a->dt; P.A_head = a->A_head; P.cum = a->a_cumsum;
@@ -145,9 +160,10 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
         SSD_LAUNCH(prof::K_CUMSUM, st, simt::chunk_cumsum_kernel<<<dim3(d.c, d.b), simt::NTHR, sm, st>>>(P));
         SSD_TC_CHECK("chunk_cumsum");
     }
-    if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, st, err, errn)) return rc;
+    if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, extreme, st, err, errn)) return rc;
     if (int rc = set_walk_attrs(err, errn)) return rc;
     WalkParams P{};
+    P.extreme = extreme;
     const uint64_t rows = (uint64_t)d.b * d.T;
     bool ok = make_map(&P.mU, a->x, rows, (uint64_t)d.h * HP) && make_map(&P.mV, a->B, rows, (uint64_t)d.g * DN) &&
               make_map(&P.mC, a->C, rows, (uint64_t)d.g * DN) &&
@@ -170,7 +186,8 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
         SSD_TC_CHECK("tc_summary_fwd");
         return 0;
     }
-    SSD_LAUNCH(prof::K_TC_FWD, st, walk_kernel<0><<<dim3(d.h, d.b), 288, WalkCfg<0>::SMEM, st>>>(P));
+    SSD_LAUNCH(prof::K_TC_FWD, st, (walk_kernel<0, false><<<dim3(d.h, d.b), 288, WalkCfg<0>::SMEM, st>>>(P)));
+    SSD_LAUNCH(prof::K_TC_FWD_ALT, st, (walk_kernel<0, true><<<dim3(d.h, d.b), 288, WalkCfg<0>::SMEM, st>>>(P)));
     SSD_TC_CHECK("tc_fwd_walk");
     if (a->logdecay_total) {
         SSD_LAUNCH(prof::K_CUMSUM, st, simt::logdecay_total_kernel<<<(d.b * d.h + 127) / 128, 128, 0, st>>>(a->a_cumsum, a->logdecay_total, d.b * d.h, d.c, d.l));
@@ -194,11 +211,13 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     void* Qst = ws + w.Qst;
     float* fin = (float*)(ws + w.final_state);
     float* dinit = a->dinit ? a->dinit : (float*)(ws + w.dinit);
-    if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
-    if (a->states && !(a->flags & SSD_B200_BWD_DINIT_ONLY)) {  // the forward left both arrays behind the tile states
+    if (cudaMemsetAsync(status, 0, 8, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
+    int* extreme = status + 1;
+    if (a->states && !(a->flags & SSD_B200_BWD_DINIT_ONLY)) {  // the forward left both arrays and the flag behind the tile states
         tcum = (float*)((uintptr_t)a->states + tile_states_bytes(d));
         dtT = a->dt ? tcum + (size_t)d.b * d.h * d.T : nullptr;
-    } else if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, st, err, errn)) {
+        extreme = (int*)(tcum + 2 * (size_t)d.b * d.h * d.T);
+    } else if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, extreme, st, err, errn)) {
         return rc;
     }
     if (int rc = set_walk_attrs(err, errn)) return rc;
@@ -226,31 +245,36 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.mU = mX; P.mV = mB; P.mC = mC; P.mY = mdX; P.mS = mH; P.save_states = 1;
         P.tcum = tcum; P.dtT = dtT; P.D = nullptr; P.seed = a->init; P.out_state = fin; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
-        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, walk_kernel<1><<<dim3(d.h, d.b), 288, WalkCfg<1>::SMEM, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, (walk_kernel<1, false><<<dim3(d.h, d.b), 288, WalkCfg<1>::SMEM, st>>>(P)));
         SSD_TC_CHECK("tc_bwd_state");
     }
     {   // reverse walk: gradient of the state leaving every tile, and d(initial state)
         WalkParams P{};
-        P.mU = mdY; P.mV = mC; P.mC = mH; P.mY = mdX; P.mS = mQ; P.save_states = 1;
-        P.rterm = (float*)(ws + w.rterm); P.gS = (float*)(ws + w.gS);
+        P.mU = mdY; P.mV = mC; P.mC = mC; P.mY = mdX; P.mS = mQ; P.save_states = 1;
         P.tcum = tcum; P.dtT = nullptr; P.D = nullptr; P.seed = a->dfinal; P.out_state = dinit; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
-        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, rev_walk_kernel<<<dim3(d.h, d.b), 288, kRevSmem, st>>>(P));
+        if (d.hpg % 2 == 0)  // two heads of a group per CTA: shared C panels, one N = 128 product per tile
+            SSD_LAUNCH(prof::K_TC_BWD_STATE, st, rev_walk_kernel<2><<<dim3(d.h / 2, d.b), RevCfg<2>::THREADS, RevCfg<2>::SMEM, st>>>(P));
+        else
+            SSD_LAUNCH(prof::K_TC_BWD_STATE, st, rev_walk_kernel<1><<<dim3(d.h, d.b), RevCfg<1>::THREADS, RevCfg<1>::SMEM, st>>>(P));
         SSD_TC_CHECK("tc_bwd_dstate");
     }
     {
         BwdParams P{};
         P.mX = mX; P.mdY = mdY; P.mB = mB; P.mC = mC; P.mH = mH; P.mQ = mQ; P.mdX = mdX; P.mdB = mdB; P.mdC = mdC;
         P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
-        P.dyx = (float*)(ws + w.dyx); P.rterm = (const float*)(ws + w.rterm); P.status = status; P.T = d.T; P.h = d.h;
-        P.hpg = d.hpg; P.nt = nt; P.b = d.b; P.gS = (float*)(ws + w.gS2);
+        P.dyx = (float*)(ws + w.dyx); P.status = status; P.T = d.T; P.h = d.h;
+        P.hpg = d.hpg; P.nt = nt; P.b = d.b; P.gS = (float*)(ws + w.gS);
         P.items = nt * d.g * d.b;
-        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<<<dim3(std::min(P.items, sm_count())), 512, kBwdSmem, st>>>(P));
+        P.extreme = extreme;
+        const dim3 grid(std::min(P.items, sm_count()));
+        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<false><<<grid, 512, kBwdSmem, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD_ALT, st, bwd_tile_kernel<true><<<grid, 512, kBwdSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_walk");
     }
     {
         DecayTileParams P{};
-        P.g = (const float*)(ws + w.g); P.ddtx = (const float*)(ws + w.ddtx); P.gS = (const float*)(ws + w.gS); P.gS2 = (const float*)(ws + w.gS2);
+        P.g = (const float*)(ws + w.g); P.ddtx = (const float*)(ws + w.ddtx); P.gS = (const float*)(ws + w.gS);
         P.dyx = (a->dt && a->D) ? (const float*)(ws + w.dyx) : nullptr;
         P.dt = a->dt; P.A_head = a->A_head; P.ddt = a->ddt; P.da = a->cumsum_is_input ? nullptr : a->da;
         P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = P.dyx ? (float*)(ws + w.dD_part) : nullptr;

@@ -64,8 +64,12 @@ struct WalkCfg {
     static constexpr size_t SMEM = (size_t)NST * STAGE_BYTES + 2 * PANEL + (MODE == 0 ? PANEL : 0) + 6 * LT * 4 + 1024;
 };
 
-template <int MODE>
+// MODE 0 exists in two instantiations (EXACT: diagonal mask blocks entry by entry, see kMaskSafeLog2); both are
+// launched and the flag raised by tile_cumsum_kernel decides on the device which of the two does the work.  (As
+// one kernel with two out-of-line bodies the walk was a quarter slower: the call boundary costs it registers.)
+template <int MODE, bool EXACT = false>
 __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ WalkParams P) {
+    if (MODE == 0 && (P.extreme[0] != 0) != EXACT) return;
     using Cfg = WalkCfg<MODE>;
     constexpr int NST = Cfg::NST;
     extern __shared__ uint8_t smem_raw[];
@@ -78,7 +82,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
     uint8_t* sY = sH + PANEL;                              // y staging (mode 0 only)
     float* scum2 = reinterpret_cast<float*>(sH + PANEL + (MODE == 0 ? PANEL : 0));  // [2][128]
     float* sf = scum2 + 2 * LT;                            // [2][128] column factors dt_j 2^(cend - c_j)
-    float* sdtc = sf + 2 * LT;                             // [2][128] dt_j (only read when a block's decay is extreme)
+    float* sdtc = sf + 2 * LT;                             // [2][128] dt_j (EXACT instantiation only)
     __shared__ uint64_t bar_ld[3], bar_s, bar_u, bar_g, bar_m2, bar_h;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
@@ -245,7 +249,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
             if (hf == 0) {
                 scum2[buf * LT + row] = c_i;
                 sf[buf * LT + row] = dtv * exp2f(cend - c_i);
-                sdtc[buf * LT + row] = dtv;
+                if (EXACT) sdtc[buf * LT + row] = dtv;
             }
             mbar_wait(&bar_ld[s], (it / NST) & 1, &failed);
             named_barrier(1, 256);
@@ -298,10 +302,10 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                         const float2* S2 = reinterpret_cast<const float2*>(r);
                         const float2* F2 = reinterpret_cast<const float2*>(f4);
                         const float2 rf2 = make_float2(rf, rf);
-                        // Inside the diagonal block the row factor is >= 1 and the column factor <= 1; their
-                        // exponents are bounded by the decay across the block.  When that leaves the fp32 range the
-                        // entries of the block are evaluated one by one instead (warp-uniform branch).
-                        if (diag && scum2[buf * LT + c0] - scum2[buf * LT + c0 + 31] > kMaskSafeLog2) {
+                        if (EXACT && diag) {
+                            // inside the diagonal block the two factors are 2^(+-decay across the block); this
+                            // instantiation runs when that leaves the fp32 range somewhere and evaluates the block
+                            // entry by entry
                             const float2* C2 = reinterpret_cast<const float2*>(scum2 + buf * LT + c0);
                             const float2* T2 = reinterpret_cast<const float2*>(sdtc + buf * LT + c0);
 #pragma unroll
