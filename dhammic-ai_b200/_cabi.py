@@ -21,7 +21,7 @@ EXPORTS = (
     "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix_all",
     "ssd_b200_m3_prologue_fwd", "ssd_b200_m3_skip_fwd", "ssd_b200_m3_prologue_bwd", "ssd_b200_m3_chain_ws_floats", "ssd_b200_m3_chain_bwd", "ssd_b200_rope_fwd", "ssd_b200_rope_bwd",
     "ssd_b200_trapezoid_ws_floats", "ssd_b200_trapezoid_fwd", "ssd_b200_trapezoid_bwd",
-    "ssd_b200_rmsnorm_ws_floats", "ssd_b200_rmsnorm_fwd", "ssd_b200_rmsnorm_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status",
+    "ssd_b200_rmsnorm_ws_floats", "ssd_b200_rmsnorm_fwd", "ssd_b200_rmsnorm_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status", "ssd_b200_selftest_bounded_wait",
     "ssd_b200_launch_count", "ssd_b200_profile_enable", "ssd_b200_profile_kernels", "ssd_b200_profile_kernel_name",
     "ssd_b200_profile_read",
 )
@@ -84,7 +84,7 @@ def load() -> C.CDLL:
     lib.ssd_b200_materialize_cache.argtypes = [C.POINTER(Shape), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                                C.c_void_p]
     lib.ssd_b200_state_prefix_all.restype = C.c_int
-    lib.ssd_b200_state_prefix_all.argtypes = [C.c_void_p] * 4 + [C.c_int64] * 8 + [C.c_int32, C.c_void_p]
+    lib.ssd_b200_state_prefix_all.argtypes = [C.c_void_p] * 6 + [C.c_int64] * 8 + [C.c_int32, C.c_void_p]
     lib.ssd_b200_m3_prologue_fwd.restype = C.c_int
     lib.ssd_b200_m3_prologue_fwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 15
     lib.ssd_b200_rope_fwd.restype = C.c_int
@@ -116,6 +116,8 @@ def load() -> C.CDLL:
     lib.ssd_b200_static_scratch_bytes.restype = C.c_size_t
     lib.ssd_b200_device_status.restype = C.c_int
     lib.ssd_b200_device_status.argtypes = [C.POINTER(Shape), C.c_void_p, C.c_void_p]
+    lib.ssd_b200_selftest_bounded_wait.restype = C.c_int
+    lib.ssd_b200_selftest_bounded_wait.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
     lib.ssd_b200_launch_count.restype = C.c_longlong
     lib.ssd_b200_profile_enable.argtypes = [C.c_int]
     lib.ssd_b200_profile_kernel_name.restype = C.c_char_p

@@ -634,6 +634,16 @@ int ssd_b200_device_status(const ssd_b200_shape* shape, const void* workspace, v
     return 0;
 }
 
+int ssd_b200_selftest_bounded_wait(void* workspace, int32_t polls, void* stream) {
+    if (!workspace || ((uintptr_t)workspace & 3)) return fail(SSD_B200_EWORKSPACE, "workspace null or misaligned");
+    if (polls <= 0 || polls > (1 << 20)) return fail(SSD_B200_EINVAL, "polls must be in [1, 2^20]");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemsetAsync(workspace, 0, 4, st) != cudaSuccess) return fail(SSD_B200_ECUDA, "memset failed");
+    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, ssd::tc::bounded_wait_selftest_kernel<<<1, 32, 0, st>>>((int*)workspace, polls));
+    CUDA_LAUNCH_CHECK("bounded_wait_selftest");
+    return 0;
+}
+
 int ssd_b200_m3_prologue_fwd(const ssd_b200_shape* shape, const void* x, const float* dt, const float* lam,
                              const float* A_head, const void* B, const void* C, const void* raw_angles, void* xw,
                              float* dA, void* Br, void* Cr, float* sdot, float* cum, float* segsum_ws, void* stream) {
@@ -809,10 +819,11 @@ int ssd_b200_materialize_cache(const ssd_b200_shape* shape, const float* a_cumsu
     return 0;
 }
 
-int ssd_b200_state_prefix_all(const float* pieces, const float* logp, const float* edge, float* out, int64_t nranks,
-                              int64_t rank, int64_t segments, int64_t batch, int64_t nheads, int64_t state_elems,
-                              int64_t rank_stride, int64_t logp_stride, int32_t reverse, void* stream) {
-    if (!pieces || !logp || !out) return fail(SSD_B200_EINVAL, "null pointer");
+int ssd_b200_state_prefix_all(const float* pieces, const float* logp, const float* edge, float* out, float* total,
+                              float* total_logp, int64_t nranks, int64_t rank, int64_t segments, int64_t batch,
+                              int64_t nheads, int64_t state_elems, int64_t rank_stride, int64_t logp_stride, int32_t reverse,
+                              void* stream) {
+    if (!pieces || !logp || (!out && !total)) return fail(SSD_B200_EINVAL, "null pointer");
     if (nranks <= 0 || rank < 0 || rank >= nranks || segments <= 0 || batch <= 0 || nheads <= 0 || state_elems <= 0 ||
         batch * nheads > 65535 || nranks * segments > 2147483647LL)
         return fail(SSD_B200_EINVAL, "bad state_prefix_all dimensions");
@@ -821,7 +832,7 @@ int ssd_b200_state_prefix_all(const float* pieces, const float* logp, const floa
     dim3 g((unsigned)((state_elems + 255) / 256), (unsigned)(batch * nheads));
     cudaStream_t st = (cudaStream_t)stream;
     SSD_LAUNCH(ssd::prof::K_PREFIX, st, ssd::simt::state_prefix_all_kernel<<<g, 256, 0, st>>>(
-        pieces, logp, edge, out, (int)nranks, (int)rank, (int)segments, (int)nheads, (size_t)state_elems,
+        pieces, logp, edge, out, total, total_logp, (int)nranks, (int)rank, (int)segments, (int)nheads, (size_t)state_elems,
         (size_t)rank_stride, (size_t)logp_stride, reverse));
     CUDA_LAUNCH_CHECK("state_prefix_all");
     return 0;

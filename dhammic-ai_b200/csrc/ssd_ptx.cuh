@@ -42,8 +42,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false (and leaves *failed set) when the limit is reached or when another
 // wait of this block has already given up, so a broken pipeline drains quickly instead of spinning.
 constexpr uint32_t kSpinLimit = 4u << 20;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed, uint32_t limit = kSpinLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *failed) return false;
     }

@@ -797,17 +797,20 @@ __global__ void cache_decay_chunk_kernel(const float* cum, T* dc, int c, int l) 
     }
 }
 
-// Sequence-parallel prefix over gathered per-piece summaries (all in this GPU's memory).  The sequence is cut into
+// Sequence-parallel prefix over per-piece summaries (all in this GPU's memory).  The sequence is cut into
 // R * S consecutive pieces, piece index g = r * S + s (rank r, segment s of that rank).  Rank r's summaries sit at
 // pieces + r * rank_stride as (b, S, h, pn) and its total log-decays at logp + r * logp_stride as (b, S, h).
 // One launch writes, for the S pieces of `rank`, the state entering each piece (forward) or the state gradient
-// leaving it (reverse) into out (b, S, h, pn); every gathered piece is read once:
+// leaving it (reverse) into out (b, S, h, pn); every piece is read once:
 //     forward   acc = edge;  for g = 0 ..        : out[g] = acc;  acc = exp(logp[g]) acc + pieces[g]
 //     reverse   acc = edge;  for g = R S - 1 .. : out[g] = acc;  acc = exp(logp[g]) acc + pieces[g]
-// `edge` (b, h, pn) or null: the state before the first piece / the gradient behind the last one.
+// `edge` (b, h, pn) or null: the state before the first piece / the gradient behind the last one.  `total` (b, h, pn)
+// or null receives acc after the last of rank's pieces has been folded in (the summary of everything walked so far)
+// and `total_logp` (b, h) or null the sum of the log-decays of rank's own S pieces.
 __global__ void state_prefix_all_kernel(const float* __restrict__ pieces, const float* __restrict__ logp,
-                                        const float* __restrict__ edge, float* __restrict__ out, int R, int rank, int S,
-                                        int h, size_t pn, size_t rank_stride, size_t logp_stride, int reverse) {
+                                        const float* __restrict__ edge, float* __restrict__ out, float* __restrict__ total,
+                                        float* __restrict__ total_logp, int R, int rank, int S, int h, size_t pn,
+                                        size_t rank_stride, size_t logp_stride, int reverse) {
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int m = blockIdx.y;  // (b,h)
     if (e >= pn) return;
@@ -815,25 +818,28 @@ __global__ void state_prefix_all_kernel(const float* __restrict__ pieces, const 
     float acc = edge ? edge[(size_t)m * pn + e] : 0.f;
     const int lo = rank * S, hi = lo + S;
     auto rec = [&](int g) { return ((size_t)bb * S + (g % S)) * h + hh; };  // (b, S, h) record of piece g inside its rank's block
+    float lsum = 0.f;
     if (!reverse) {
 #pragma unroll 4
         for (int g = 0; g < hi; ++g) {
-            if (g >= lo) out[rec(g) * pn + e] = acc;
-            if (g + 1 < hi) {
-                const size_t r = (size_t)(g / S);
-                acc = __expf(logp[r * logp_stride + rec(g)]) * acc + pieces[r * rank_stride + rec(g) * pn + e];
-            }
+            if (g >= lo && out) out[rec(g) * pn + e] = acc;
+            const size_t r = (size_t)(g / S);
+            const float lp = logp[r * logp_stride + rec(g)];
+            if (g >= lo) lsum += lp;
+            acc = __expf(lp) * acc + pieces[r * rank_stride + rec(g) * pn + e];
         }
     } else {
 #pragma unroll 4
         for (int g = R * S - 1; g >= lo; --g) {
-            if (g < hi) out[rec(g) * pn + e] = acc;
-            if (g > lo) {
-                const size_t r = (size_t)(g / S);
-                acc = __expf(logp[r * logp_stride + rec(g)]) * acc + pieces[r * rank_stride + rec(g) * pn + e];
-            }
+            if (g < hi && out) out[rec(g) * pn + e] = acc;
+            const size_t r = (size_t)(g / S);
+            const float lp = logp[r * logp_stride + rec(g)];
+            if (g < hi) lsum += lp;
+            acc = __expf(lp) * acc + pieces[r * rank_stride + rec(g) * pn + e];
         }
     }
+    if (total) total[(size_t)m * pn + e] = acc;
+    if (total_logp && e == 0) total_logp[m] = lsum;
 }
 
 // Total log-decay of every (batch, head) sequence from the within-chunk cumulative sums: sum of the chunks' last entries.

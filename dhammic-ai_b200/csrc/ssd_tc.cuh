@@ -230,6 +230,23 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restric
 }
 
 // ------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one warp waits (a few thousand polls) on an mbarrier that nothing ever arrives at,
+// gives up, records it in the status word exactly as the tile kernels do, and returns.  The context stays usable.
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(int* status, int polls) {
+    __shared__ uint64_t bar;
+    __shared__ int failed;
+    if (threadIdx.x == 0) {
+        failed = 0;
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    mbar_wait(&bar, 0, &failed, (uint32_t)polls);
+    __syncwarp();
+    if (threadIdx.x == 0 && failed) atomicExch(status, 1);
+}
+
+// ------------------------------------------------------------------------------------------
 struct WalkParams {
     CUtensorMap mU;   // x (modes 0,1) or dy (reverse walks): 2D [b*T][h*64]
     CUtensorMap mV;   // B (modes 0,1) or C (reverse walks):  2D [b*T][g*128]

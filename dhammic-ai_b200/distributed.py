@@ -23,6 +23,11 @@ src/kernels/ssd_scan.py:395-397, :410, :468, :530-533).
                 4. the full backward of the slice with init_r and dfinal_r
                 5. ONE all_reduce of the packed (dA_head | dD | d initial state)
 
+  When a rank also cuts its slice into S segments (run as batch entries of one launch, see below), the segments'
+  summaries are first folded into the one summary of the slice on the GPU, so that what crosses NVLink stays one
+  state per rank whatever S is; the states entering the segments then come from a second local fold that starts
+  from init_r.
+
   Each collective runs on a side stream behind the pass that produces its input, so that host work and the
   preparation kernels of the next pass (cumulative sums) are not held up by it; the kernels that need the
   gathered states wait for it through an event.  Gathered buffers live in this GPU's own memory and are read
@@ -206,23 +211,30 @@ class CudaBackend:
             _op._status(lib, shape, ws, dev)
         return out
 
-    def prefix_all(self, pieces: Tensor, logp: Tensor, edge: Tensor | None, rank: int, reverse: bool) -> Tensor:
+    def prefix_all(self, pieces: Tensor, logp: Tensor, edge: Tensor | None, rank: int, reverse: bool, total: bool = False):
         """pieces (R,b,S,h,p,n) and logp (R,b,S,h): summaries and total log-decays of all R*S pieces (rank-major; the
         rank dimension may be strided, the rest dense).  Returns (b*S,h,p,n): for each of rank's S pieces the state
         entering it (forward) or the state gradient leaving it (reverse); ``edge`` (b,h,p,n) is the state before the
-        first piece / the gradient behind the last one.  One launch, every piece read once."""
+        first piece / the gradient behind the last one.  One launch, every piece read once.  With ``total`` it returns
+        instead (fold of everything walked including rank's own pieces (b,h,p,n), sum of rank's log-decays (b,h))."""
         lib = _cabi.load()
         R, b, S, h, p, n = pieces.shape
         dev = pieces.device
         assert pieces[0].is_contiguous() and logp[0].is_contiguous()
         with torch.cuda.device(dev):
-            out = torch.empty(b * S, h, p, n, dtype=torch.float32, device=dev)
             ed = None if edge is None else edge.float().contiguous()
+            if total:
+                out = None
+                tot = torch.empty(b, h, p, n, dtype=torch.float32, device=dev)
+                tlp = torch.empty(b, h, dtype=torch.float32, device=dev)
+            else:
+                out = torch.empty(b * S, h, p, n, dtype=torch.float32, device=dev)
+                tot = tlp = None
             _cabi.check(lib.ssd_b200_state_prefix_all(
-                _op._ptr(pieces), _op._ptr(logp), _op._ptr(ed), _op._ptr(out), R, rank, S, b, h, p * n,
-                pieces.stride(0) if R > 1 else b * S * h * p * n, logp.stride(0) if R > 1 else b * S * h,
+                _op._ptr(pieces), _op._ptr(logp), _op._ptr(ed), _op._ptr(out), _op._ptr(tot), _op._ptr(tlp), R, rank, S,
+                b, h, p * n, pieces.stride(0) if R > 1 else b * S * h * p * n, logp.stride(0) if R > 1 else b * S * h,
                 1 if reverse else 0, _op._stream(dev)))
-        return out
+        return (tot, tlp) if total else out
 
 
 _DEFAULT_BACKEND = CudaBackend()
@@ -243,6 +255,14 @@ class LoopbackComm:
         pass
 
 
+def _check_gathered(t: Tensor, want: int) -> None:
+    """A gathered buffer of the wrong size (ranks that disagree on the shape of their slices, a communicator for a
+    different group) must end in an exception here, not in a kernel reading past the buffer."""
+    if t.dim() != 1 or t.numel() != want or t.dtype != torch.float32:
+        raise ValueError(f"all_gather returned {tuple(t.shape)} {t.dtype}, expected ({want},) float32: the ranks of this "
+                         "group do not hold slices of the same shape")
+
+
 class _SeqSplitSSD(torch.autograd.Function):
     """The scan over a sequence cut into world * S contiguous pieces: `world` ranks (one per GPU, each holding
     a contiguous slice) times S segments per rank.  The S segments of a rank run as extra batch entries of one
@@ -258,18 +278,25 @@ class _SeqSplitSSD(torch.autograd.Function):
         seg = Slice(x.contiguous().view(b * S, Ts, h, p), dt.float().contiguous().view(b * S, Ts, h),
                     A_head.float().contiguous(), B.contiguous().view(b * S, Ts, g, n),
                     C_.contiguous().view(b * S, Ts, g, n), None if D is None else D.float().contiguous(), int(chunk))
-        # one rank's block of the gather: the S summaries (b,S,h,p,n) followed by the S total log-decays (b,S,h)
-        nF, nP = b * S * h * p * n, b * S * h
+        # the S segment summaries (b,S,h,p,n) and their total log-decays (b,S,h) of this rank's slice
+        nF, nP, nR = b * S * h * p * n, b * S * h, b * h * p * n
         pack = torch.empty(nF + nP, dtype=torch.float32, device=x.device)
         _, _, cum = backend.states_only(seg, pack[:nF].view(b * S, h, p, n), pack[nF:].view(b * S, h))
-        gathered, hnd = comm.all_gather(pack)
-        G = gathered.view(comm.world, nF + nP)
-        pieces, logp = G[:, :nF].view(comm.world, b, S, h, p, n), G[:, nF:].view(comm.world, b, S, h)
-        edge = None if initial_state is None else initial_state.reshape(b, h, p, n)
-        comm.wait(hnd)
-        inits = backend.prefix_all(pieces, logp, edge, comm.rank, reverse=False)
+        loc_pieces, loc_logp = pack[:nF].view(1, b, S, h, p, n), pack[nF:].view(1, b, S, h)
+        init_rank = None if initial_state is None else initial_state.reshape(b, h, p, n)
+        rank_logp = None
+        if comm.world > 1:
+            # fold the segments into the one summary of the slice; only that crosses ranks
+            F_rank, lp_rank = backend.prefix_all(loc_pieces, loc_logp, None, 0, reverse=False, total=True)
+            gathered, hnd = comm.all_gather(torch.cat([F_rank.reshape(-1), lp_rank.reshape(-1)]))
+            _check_gathered(gathered, comm.world * (nR + b * h))
+            G = gathered.view(comm.world, nR + b * h)
+            rank_pieces, rank_logp = G[:, :nR].view(comm.world, b, 1, h, p, n), G[:, nR:].view(comm.world, b, 1, h)
+            comm.wait(hnd)
+            init_rank = backend.prefix_all(rank_pieces, rank_logp, init_rank, comm.rank, reverse=False)
+        inits = backend.prefix_all(loc_pieces, loc_logp, init_rank, 0, reverse=False)
         y, final, saved = backend.forward(seg, inits, cum)
-        ctx.seg, ctx.saved, ctx.inits, ctx.logp = seg, saved, inits, logp
+        ctx.seg, ctx.saved, ctx.inits, ctx.loc_logp, ctx.rank_logp = seg, saved, inits, loc_logp, rank_logp
         ctx.comm, ctx.backend, ctx.S, ctx.dims = comm, backend, S, (b, T, h, p, n, g)
         ctx.has_init = initial_state is not None
         ctx.init_shape = None if initial_state is None else tuple(initial_state.shape)
@@ -290,10 +317,16 @@ class _SeqSplitSSD(torch.autograd.Function):
             seed = seed.view(b * S, h, p, n)
         Dl = torch.empty(b * S * h * p * n, dtype=torch.float32, device=dys.device)
         backend.dinit_only(seg, ctx.saved, dys, seed, Dl.view(b * S, h, p, n))
-        gathered, hnd = comm.all_gather(Dl)
-        pieces = gathered.view(comm.world, b, S, h, p, n)
-        comm.wait(hnd)
-        dfin = backend.prefix_all(pieces, ctx.logp, None, comm.rank, reverse=True)
+        loc_pieces = Dl.view(1, b, S, h, p, n)
+        dfin_rank = None
+        if comm.world > 1:
+            D_rank, _ = backend.prefix_all(loc_pieces, ctx.loc_logp, None, 0, reverse=True, total=True)
+            gathered, hnd = comm.all_gather(D_rank.reshape(-1))
+            _check_gathered(gathered, comm.world * b * h * p * n)
+            comm.wait(hnd)
+            dfin_rank = backend.prefix_all(gathered.view(comm.world, b, 1, h, p, n), ctx.rank_logp, None, comm.rank,
+                                           reverse=True)
+        dfin = backend.prefix_all(loc_pieces, ctx.loc_logp, dfin_rank, 0, reverse=True)
         if last:
             dfin.view(b, S, h, p, n)[:, -1] += dfinal_global.float()
         gr = backend.backward(seg, ctx.saved, ctx.inits, dys, dfin)
@@ -302,15 +335,15 @@ class _SeqSplitSSD(torch.autograd.Function):
         if gr["dD"] is not None:
             parts.append(gr["dD"].reshape(-1))
         if ctx.has_init:
-            d0 = gr["dinit"].view(b, S, h, p, n)[:, 0].reshape(-1)
+            d0 = gr["dinit"].reshape(b, S, h, p, n)[:, 0].reshape(-1)
             parts.append(d0 if comm.rank == 0 else torch.zeros_like(d0))
         red, hnd = comm.all_reduce_sum(torch.cat(parts))
         comm.wait(hnd)
         dAh = red[:h]
         dD = None if gr["dD"] is None else red[h:2 * h]
         dinit = red[-b * h * p * n:].reshape(ctx.init_shape) if ctx.has_init else None
-        return (gr["dx"].view(b, T, h, p), gr["ddt"].view(b, T, h), dAh, gr["dB"].view(b, T, g, n),
-                gr["dC"].view(b, T, g, n), dD, None, dinit, None, None, None)
+        return (gr["dx"].reshape(b, T, h, p), gr["ddt"].reshape(b, T, h), dAh, gr["dB"].reshape(b, T, g, n),
+                gr["dC"].reshape(b, T, g, n), dD, None, dinit, None, None, None)
 
 
 def pick_segments(batch: int, nheads: int, seqlen: int, n_sm: int = 148) -> int:

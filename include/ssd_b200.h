@@ -207,6 +207,14 @@ size_t ssd_b200_static_scratch_bytes(void);
 int ssd_b200_device_status(const ssd_b200_shape *shape, const void *workspace, void *stream);
 
 /*
+ * Self-test of the error path above (no counterpart in the reference): launches one warp that waits `polls`
+ * polls on a barrier nothing arrives at, gives up and sets the status word at the start of `workspace` (>= 4
+ * bytes, device memory) the way the tile kernels do; ssd_b200_device_status(shape, workspace, stream) for a
+ * tensor-core shape then returns SSD_B200_EDEVICE.  Nothing faults or hangs and the context stays usable.
+ */
+int ssd_b200_selftest_bounded_wait(void *workspace, int32_t polls, void *stream);
+
+/*
  * The reference operator also returns its decay masks as a cache
  * (src/kernels/ssd_scan.py:420, :465; shapes pinned by tests/kernels/test_ssd_scan.py:107-110).
  * This builds them from a_cumsum on demand:
@@ -234,12 +242,16 @@ int ssd_b200_materialize_cache(const ssd_b200_shape *shape, const float *a_cumsu
  *   reverse != 0:  the state gradient leaving the piece, acc_last = edge, acc_{g-1} = exp(logp_g) acc_g + pieces_g
  * with edge (batch, h, state_elems) the caller's initial state / final-state gradient, or NULL for zero.  Every
  * piece is read once.  The outputs are in the layout ssd_b200_fwd / _bwd take as init / dfinal when the
- * segments run as batch entries (entry = batch index * segments + s).
+ * segments run as batch entries (entry = batch index * segments + s).  Optional outputs (NULL = skip; `out` may
+ * be NULL when only these are wanted): total (batch, h, state_elems) = acc after the last of rank's pieces has been
+ * folded in, total_logp (batch, h) = sum of the log-decays of rank's own pieces -- with nranks = 1 these are the
+ * summary and log-decay of the rank's whole slice, i.e. what the ranks exchange (one state per rank, not one per
+ * segment).
  */
-int ssd_b200_state_prefix_all(const float *pieces, const float *logp, const float *edge, float *out,
-                              int64_t nranks, int64_t rank, int64_t segments, int64_t batch, int64_t nheads,
-                              int64_t state_elems, int64_t rank_stride, int64_t logp_stride, int32_t reverse,
-                              void *stream);
+int ssd_b200_state_prefix_all(const float *pieces, const float *logp, const float *edge, float *out, float *total,
+                              float *total_logp, int64_t nranks, int64_t rank, int64_t segments, int64_t batch,
+                              int64_t nheads, int64_t state_elems, int64_t rank_stride, int64_t logp_stride,
+                              int32_t reverse, void *stream);
 
 /*
  * Element-wise kernels of the Mamba-3 style variant (no counterpart in the reference's operator file: its

@@ -68,17 +68,21 @@ class OracleBackend:
         out["dinit"] = g[-1]
         return out
 
-    def prefix_all(self, pieces, logp, edge, rank, reverse):
+    def prefix_all(self, pieces, logp, edge, rank, reverse, total=False):
         R, b, S, h, p, n = pieces.shape
         P = pieces.transpose(1, 2).reshape(R * S, b, h, p, n)   # piece-major
         L = logp.transpose(1, 2).reshape(R * S, b, h)
         acc = torch.zeros_like(P[0]) if edge is None else edge.reshape(P[0].shape).to(P.dtype).clone()
         out = [None] * S
         order = range(R * S - 1, rank * S - 1, -1) if reverse else range(rank * S + S)
+        lsum = torch.zeros_like(L[0])
         for g in order:
             if rank * S <= g < rank * S + S:
                 out[g - rank * S] = acc
+                lsum = lsum + L[g]
             acc = torch.exp(L[g])[..., None, None] * acc + P[g]
+        if total:
+            return acc, lsum
         return torch.stack(out, dim=1).reshape(b * S, h, p, n)
 
 
@@ -92,7 +96,7 @@ def _free_port():
         return sk.getsockname()[1]
 
 
-def _gloo_worker(rank, world, port, result_file):
+def _gloo_worker(rank, world, port, result_file, segments=1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -113,7 +117,7 @@ def _gloo_worker(rank, world, port, result_file):
         lv = {k: v.clone().requires_grad_(True) for k, v in lv.items()}
         il = init.clone().requires_grad_(True)
         y, final = D.ssd_mamba2_sequence_parallel(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk,
-                                                  il, backend=OracleBackend())
+                                                  il, backend=OracleBackend(), segments=segments)
         # the caller's d final_state acts on the last rank's final state only
         outs, gouts = [y], [inp["dy"][:, sl]]
         if rank == world - 1:
@@ -138,11 +142,13 @@ def _gloo_worker(rank, world, port, result_file):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_sequence_parallel_schedule_gloo(tmp_path, world):
+@pytest.mark.parametrize("world,segments", [(2, 1), (4, 1), (2, 2)])
+def test_sequence_parallel_schedule_gloo(tmp_path, world, segments):
+    """segments > 1: every rank also cuts its slice into segments; their summaries are folded into one state per
+    rank before the exchange."""
     port = _free_port()
     res = str(tmp_path / "res")
-    mp.spawn(_gloo_worker, args=(world, port, res), nprocs=world, join=True)
+    mp.spawn(_gloo_worker, args=(world, port, res, segments), nprocs=world, join=True)
     for r in range(world):
         assert Path(f"{res}.{r}").read_text() == "ok", Path(f"{res}.{r}").read_text()
 
@@ -261,3 +267,103 @@ def test_segmented_scan_inside_one_gpu(pkg, cabi, idx, segments, tol):
     bad = {k: v for k, v in errs.items() if not v < tol}
     assert not bad, errs
     assert D.pick_segments(1, 64, 131072) == 8 and D.pick_segments(16, 64, 4096) == 1
+
+
+# ---------------------------------------------------------------------------------------------------------
+# failures made on the host: no GPU is involved, nothing hangs
+# ---------------------------------------------------------------------------------------------------------
+def _leaving_worker(rank, world, port, result_file):
+    """Rank 1 takes part in the first step and then leaves (between steps, nothing of it in flight).  Rank 0's
+    next step must end in an exception from its first collective, within the group's short timeout."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    pkg = importlib.import_module("dhammic-ai_b200")
+    D = importlib.import_module("dhammic-ai_b200.distributed")
+    torch.set_num_threads(2)
+    cfg = _small_cfg(pkg)
+    inp = pkg.make_inputs(cfg)
+    Tl = cfg.seqlen // world
+    sl = slice(rank * Tl, (rank + 1) * Tl)
+
+    def step():
+        return D.ssd_mamba2_sequence_parallel(inp["x"][:, sl], inp["dt"][:, sl], inp["A_head"], inp["B"][:, sl],
+                                              inp["C"][:, sl], inp["D"], cfg.chunk, backend=OracleBackend())
+
+    step()
+    dist.barrier()
+    outcome = "left"
+    if rank == 0:
+        t0 = time.time()
+        try:
+            step()
+            outcome = "no error"
+        except Exception as e:  # the collective reports the missing peer
+            outcome = f"raised {type(e).__name__} after {time.time() - t0:.1f}s"
+    with open(f"{result_file}.{rank}", "w") as f:
+        f.write(outcome)
+    if rank == 0:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+    # rank 1 simply returns: its process ends without another collective
+
+
+def test_rank_that_leaves_between_steps_ends_in_an_exception(tmp_path):
+    port = _free_port()
+    res = str(tmp_path / "res")
+    mp.spawn(_leaving_worker, args=(2, port, res), nprocs=2, join=True)
+    assert Path(f"{res}.1").read_text() == "left"
+    out = Path(f"{res}.0").read_text()
+    assert out.startswith("raised"), out
+    assert float(out.split("after ")[1].rstrip("s")) < 60.0, out
+
+
+class _WrongSizeComm:
+    """A communicator whose gather comes back one element short (ranks that disagree on their slice shape)."""
+    rank, world = 0, 2
+
+    def all_gather(self, flat):
+        return torch.zeros(self.world * flat.numel() - 1, dtype=flat.dtype), None
+
+    def all_reduce_sum(self, flat):
+        return flat, None
+
+    @staticmethod
+    def wait(handle):
+        pass
+
+
+def test_wrong_sized_gathered_buffer_is_rejected(pkg):
+    D = importlib.import_module("dhammic-ai_b200.distributed")
+    cfg = _small_cfg(pkg)
+    inp = pkg.make_inputs(cfg)
+    with pytest.raises(ValueError, match="all_gather returned"):
+        D.ssd_mamba2_sequence_parallel(inp["x"], inp["dt"], inp["A_head"], inp["B"], inp["C"], inp["D"], cfg.chunk,
+                                       comm=_WrongSizeComm(), backend=OracleBackend())
+
+
+@pytest.mark.gpu
+def test_bounded_wait_that_runs_out_is_reported(pkg, cabi):
+    """A wait on a barrier nothing arrives at gives up after its poll limit; the kernel returns normally, the status
+    word is set and ssd_b200_device_status turns it into SSD_B200_EDEVICE.  The context stays usable afterwards."""
+    import ctypes as C
+    lib = cabi.load()
+    ws = torch.zeros(64, dtype=torch.int32, device="cuda")
+    shape = cabi.Shape(cabi.ABI_VERSION, cabi.BF16, cabi.F32, cabi.PATH_TC, 1, 256, 8, 64, 128, 1, 128)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.ssd_b200_device_status(C.byref(shape), C.c_void_p(ws.data_ptr()), stream) == 0
+    cabi.check(lib.ssd_b200_selftest_bounded_wait(C.c_void_p(ws.data_ptr()), 4096, stream))
+    assert lib.ssd_b200_device_status(C.byref(shape), C.c_void_p(ws.data_ptr()), stream) == cabi.EDEVICE
+    assert "bounded wait" in cabi.last_error()
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        cabi.check(cabi.EDEVICE)
+    # the context is intact: a normal call still works and reports a clean status
+    cfg = pkg.shrink(pkg.CONFIGS[2], 1, 256)
+    inp = pkg.make_inputs(cfg)
+    y, _ = pkg.ssd_mamba2(*[inp[k].cuda() for k in ("x", "dt", "A_head", "B", "C", "D")], cfg.chunk)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y).all()
