@@ -200,6 +200,29 @@ def run_elementwise(args, cfg, pkg):
     # gate norm: fwd reads y, z, writes out; bwd reads y, z, dout, writes dy, dz (the dw pass re-reads three of them)
     gate_bytes = 8 * b * T * h * cfg.headdim * es
     ms_r, ms_t, ms_g = timed(rope_step), timed(trap_step), timed(gate_step)
+    # forward of the gated norm alone, with its own row statistic (two reads of y) and with the partial sums the scan's
+    # forward leaves behind (one read of y), through the C ABI
+    import ctypes as C
+    cabi = importlib.import_module("dhammic-ai_b200._cabi")
+    lib = cabi.load()
+    rows, Dn = b * T, h * cfg.headdim
+    ysq = torch.rand(rows // 128 * h * 2 * 128, device=dev)
+    out_n = torch.empty_like(yg)
+    rstd = torch.empty(rows, device=dev)
+    code = cabi.BF16 if cfg.dtype == "bf16" else cabi.F32
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    stream = lambda: C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    wf = wg.detach().float().contiguous()
+
+    def norm_fwd_own():
+        cabi.check(lib.ssd_b200_rmsnorm_fwd(code, rows, Dn, 1e-6, ptr(yg), ptr(wf), ptr(zg), ptr(out_n), ptr(rstd), stream()))
+
+    def norm_fwd_presummed():
+        cabi.check(lib.ssd_b200_rmsnorm_fwd_presummed(code, rows, Dn, 1e-6, ptr(yg), ptr(wf), ptr(zg), ptr(ysq), h, ptr(out_n),
+                                                      ptr(rstd), stream()))
+
+    ms_n1, ms_n2 = timed(norm_fwd_own), timed(norm_fwd_presummed)
+    fwd_bytes = 3 * rows * Dn * es
     line = {"metric": "elementwise_fwd_bwd_GBps", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "dtype": "bf16" if cfg.dtype == "bf16" else "f32", "data": "synthetic", "higher_is_better": True,
             "config": {"workload": cfg.name, "rope": [b, T, h, n], "trapezoid": [b, T, h],
@@ -208,6 +231,9 @@ def run_elementwise(args, cfg, pkg):
             "trapezoid": {"ms": ms_t, "GBps": trap_bytes / ms_t / 1e6, "frac_of_hbm": trap_bytes / ms_t / 1e6 / hbm_peak},
             "gate_norm": {"ms": ms_g, "GBps": gate_bytes / ms_g / 1e6, "frac_of_hbm": gate_bytes / ms_g / 1e6 / hbm_peak,
                           "shape": [b * T, h * cfg.headdim]},
+            "gate_norm_forward": {"own_statistic_ms": ms_n1, "presummed_ms": ms_n2, "algorithmic_GB": fwd_bytes / 1e9,
+                                  "own_statistic_frac_of_hbm": fwd_bytes / ms_n1 / 1e6 / hbm_peak,
+                                  "presummed_frac_of_hbm": fwd_bytes / ms_n2 / 1e6 / hbm_peak},
             "peak": hbm_peak, "peak_kind": peak_kind}
     line["value"] = line["rope"]["GBps"]
     print(json.dumps(line))

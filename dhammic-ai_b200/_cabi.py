@@ -21,7 +21,7 @@ EXPORTS = (
     "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix_all",
     "ssd_b200_m3_prologue_fwd", "ssd_b200_m3_skip_fwd", "ssd_b200_m3_prologue_bwd", "ssd_b200_m3_chain_ws_floats", "ssd_b200_m3_chain_bwd", "ssd_b200_rope_fwd", "ssd_b200_rope_bwd",
     "ssd_b200_trapezoid_ws_floats", "ssd_b200_trapezoid_fwd", "ssd_b200_trapezoid_bwd",
-    "ssd_b200_rmsnorm_ws_floats", "ssd_b200_rmsnorm_fwd", "ssd_b200_rmsnorm_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status", "ssd_b200_selftest_bounded_wait",
+    "ssd_b200_rmsnorm_ws_floats", "ssd_b200_rmsnorm_fwd", "ssd_b200_rmsnorm_fwd_presummed", "ssd_b200_rmsnorm_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status", "ssd_b200_selftest_bounded_wait",
     "ssd_b200_launch_count", "ssd_b200_profile_enable", "ssd_b200_profile_kernels", "ssd_b200_profile_kernel_name",
     "ssd_b200_profile_read",
 )
@@ -38,7 +38,7 @@ class FwdArgs(C.Structure):
                 ("D", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("init", C.c_void_p), ("y", C.c_void_p),
                 ("final_state", C.c_void_p), ("a_cumsum", C.c_void_p), ("cumsum_is_input", C.c_int32),
                 ("flags", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("states", C.c_void_p), ("logdecay_total", C.c_void_p)]
+                ("states", C.c_void_p), ("logdecay_total", C.c_void_p), ("ysq", C.c_void_p)]
 
 
 class BwdArgs(C.Structure):
@@ -101,6 +101,8 @@ def load() -> C.CDLL:
     lib.ssd_b200_rmsnorm_ws_floats.argtypes = [C.c_int64, C.c_int64]
     lib.ssd_b200_rmsnorm_fwd.restype = C.c_int
     lib.ssd_b200_rmsnorm_fwd.argtypes = [C.c_int32, C.c_int64, C.c_int64, C.c_float] + [C.c_void_p] * 6
+    lib.ssd_b200_rmsnorm_fwd_presummed.restype = C.c_int
+    lib.ssd_b200_rmsnorm_fwd_presummed.argtypes = [C.c_int32, C.c_int64, C.c_int64, C.c_float] + [C.c_void_p] * 4 + [C.c_int64] + [C.c_void_p] * 3
     lib.ssd_b200_rmsnorm_bwd.restype = C.c_int
     lib.ssd_b200_rmsnorm_bwd.argtypes = [C.c_int32, C.c_int64, C.c_int64] + [C.c_void_p] * 10
     lib.ssd_b200_m3_skip_fwd.restype = C.c_int

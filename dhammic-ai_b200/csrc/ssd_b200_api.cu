@@ -447,14 +447,15 @@ int trapezoid_impl(bool backward, size_t M, int H, const void* dt_raw, const voi
 
 template <class T>
 int rmsnorm_impl(bool backward, size_t M, int D, float eps, const void* x, const float* w, const void* z, const void* dout,
-                 void* out, void* dz, float* rstd, float* dw, float* part_ws, cudaStream_t st) {
+                 void* out, void* dz, float* rstd, float* dw, float* part_ws, cudaStream_t st, const float* ysq = nullptr,
+                 int ysq_heads = 0) {
     using namespace ssd::ew;
     constexpr int V = VecOf<T>::N;
     const bool vec = D % V == 0;
     const unsigned blocks = (unsigned)((M + 7) / 8);
     if (!backward) {
-        if (vec) SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_fwd_kernel<T, V><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (T*)out, rstd, M, D, eps)));
-        else SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_fwd_kernel<T, 1><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (T*)out, rstd, M, D, eps)));
+        if (vec) SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_fwd_kernel<T, V><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (T*)out, rstd, M, D, eps, ysq, ysq_heads)));
+        else SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_fwd_kernel<T, 1><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (T*)out, rstd, M, D, eps, ysq, ysq_heads)));
     } else {
         if (vec) SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_bwd_kernel<T, V><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (const T*)dout, rstd, (T*)out, (T*)dz, M, D)));
         else SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rmsnorm_bwd_kernel<T, 1><<<blocks, 256, 0, st>>>((const T*)x, w, (const T*)z, (const T*)dout, rstd, (T*)out, (T*)dz, M, D)));
@@ -538,6 +539,7 @@ int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
     if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(SSD_B200_EWORKSPACE, "workspace null or not 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     if (a->states && path != SSD_B200_PATH_TC) return fail(SSD_B200_EINVAL, "`states` is only used by the tensor-core path");
+    if (a->ysq && path != SSD_B200_PATH_TC) return fail(SSD_B200_EINVAL, "`ysq` is only written by the tensor-core path");
     if (path == SSD_B200_PATH_TC) return ssd::tc::forward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
     return a->shape.dtype == SSD_B200_BF16 ? simt_fwd<__nv_bfloat16>(a, st) : simt_fwd<float>(a, st);
 }
@@ -778,6 +780,17 @@ int ssd_b200_rmsnorm_fwd(int32_t dtype, int64_t rows, int64_t D, float eps, cons
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == SSD_B200_BF16) return rmsnorm_impl<__nv_bfloat16>(false, (size_t)rows, (int)D, eps, x, weight, z, nullptr, out, nullptr, rstd, nullptr, nullptr, st);
     if (dtype == SSD_B200_F32) return rmsnorm_impl<float>(false, (size_t)rows, (int)D, eps, x, weight, z, nullptr, out, nullptr, rstd, nullptr, nullptr, st);
+    return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
+}
+
+int ssd_b200_rmsnorm_fwd_presummed(int32_t dtype, int64_t rows, int64_t D, float eps, const void* x, const float* weight,
+                                   const void* z, const float* ysq, int64_t nheads, void* out, float* rstd, void* stream) {
+    if (!x || !weight || !out || !rstd || !ysq) return fail(SSD_B200_EINVAL, "null pointer");
+    if (rows <= 0 || D <= 0 || D > 2147483647LL || (rows + 7) / 8 > 2147483647LL || nheads <= 0 || nheads > 32767 || rows % 128)
+        return fail(SSD_B200_EINVAL, "bad rmsnorm dimensions (rows must be a multiple of 128)");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SSD_B200_BF16) return rmsnorm_impl<__nv_bfloat16>(false, (size_t)rows, (int)D, eps, x, weight, z, nullptr, out, nullptr, rstd, nullptr, nullptr, st, ysq, (int)nheads);
+    if (dtype == SSD_B200_F32) return rmsnorm_impl<float>(false, (size_t)rows, (int)D, eps, x, weight, z, nullptr, out, nullptr, rstd, nullptr, nullptr, st, ysq, (int)nheads);
     return fail(SSD_B200_EUNSUPPORTED, "dtype %d", dtype);
 }
 

@@ -242,18 +242,26 @@ __device__ __forceinline__ float silu_grad_f(float z) {
 template <class T, int V>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
                                                           const T* __restrict__ z, T* __restrict__ out,
-                                                          float* __restrict__ rstd, size_t M, int D, float eps) {
+                                                          float* __restrict__ rstd, size_t M, int D, float eps,
+                                                          const float* __restrict__ ysq, int ysq_heads) {
     const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= M) return;
     const int lane = threadIdx.x & 31;
     const T* xr = x + row * D;
     float ss = 0.f;
+    if (ysq) {
+        // partial sums left by the scan's forward, [row / 128][head][half][row % 128]: the eight rows of a block are
+        // neighbours, so the warps of the block share the sectors they read
+        const float* pr = ysq + (row >> 7) * (size_t)(2 * ysq_heads) * 128 + (row & 127);
+        for (int i = lane; i < 2 * ysq_heads; i += 32) ss += pr[(size_t)i * 128];
+    } else {
 #pragma unroll 4
-    for (int c = lane * V; c < D; c += 32 * V) {
-        float v[V];
-        load_elems1<T, V>(xr + c, v);
+        for (int c = lane * V; c < D; c += 32 * V) {
+            float v[V];
+            load_elems1<T, V>(xr + c, v);
 #pragma unroll
-        for (int q = 0; q < V; ++q) ss += v[q] * v[q];
+            for (int q = 0; q < V; ++q) ss += v[q] * v[q];
+        }
     }
 #pragma unroll
     for (int of = 16; of > 0; of >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, of);

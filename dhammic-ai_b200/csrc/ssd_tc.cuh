@@ -260,6 +260,7 @@ struct WalkParams {
     CUtensorMap mS;   // state store: 2D [b*nt*h*128][64]
     int save_states;  // store the state entering every tile of the walk through mS
     const int* extreme;  // see kMaskSafeLog2 (forward only)
+    float* ysq;          // (b, T/128, h, 2, 128) per half row sum_p y^2 (forward only), or null
     int* status;
     int T, h, hpg, nt;
 };

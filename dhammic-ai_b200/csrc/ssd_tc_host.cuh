@@ -164,6 +164,7 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     if (int rc = set_walk_attrs(err, errn)) return rc;
     WalkParams P{};
     P.extreme = extreme;
+    P.ysq = a->ysq;
     const uint64_t rows = (uint64_t)d.b * d.T;
     bool ok = make_map(&P.mU, a->x, rows, (uint64_t)d.h * HP) && make_map(&P.mV, a->B, rows, (uint64_t)d.g * DN) &&
               make_map(&P.mC, a->C, rows, (uint64_t)d.g * DN) &&

@@ -362,6 +362,13 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     }
                 }
                 store_half_row(sY, row, hf * 4, y);
+                if (P.ysq) {  // sum of squares of this half row, for the norm over all heads that follows the scan
+                    float2 q2 = make_float2(0.f, 0.f);
+                    const float2* Y2 = reinterpret_cast<const float2*>(y);
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) q2 = fma2(Y2[q], Y2[q], q2);
+                    P.ysq[((((size_t)bb * nt + k) * P.h + hh) * 2 + hf) * LT + row] = q2.x + q2.y;
+                }
             }
             {
                 uint32_t r[32];

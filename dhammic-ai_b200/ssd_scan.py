@@ -160,8 +160,9 @@ class LazySSDCache(dict):
         return dict.get(self, key)
 
 
-def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=False):
-    """Common forward launcher.  Returns (y, final_state fp32 (b,h,p,n), a_cumsum, shape, states or None)."""
+def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=False, ysq=None):
+    """Common forward launcher.  Returns (y, final_state fp32 (b,h,p,n), a_cumsum, shape, states or None).
+    ``ysq``: optional fp32 buffer (b, T/128, h, 2, 128) for the per-half-row sums of y^2 (tensor-core path)."""
     lib = _cabi.load()
     b, T, h, p = x.shape
     n = B.shape[3]
@@ -188,7 +189,7 @@ def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=
                 states = torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
         args = _cabi.FwdArgs(shape, _ptr(x), _ptr(a), _ptr(dt), _ptr(A_head), _ptr(D), _ptr(B), _ptr(Cm), _ptr(init4),
                              _ptr(y), _ptr(final), _ptr(cum), 1 if a_cumsum_in is not None else 0, 0, _ptr(ws),
-                             ws.numel(), _ptr(states))
+                             ws.numel(), _ptr(states), None, _ptr(ysq))
         _cabi.check(lib.ssd_b200_fwd(C.byref(args), _stream(dev)))
         _status(lib, shape, ws, dev)
     return y, final, cum, shape, states
@@ -356,6 +357,117 @@ def ssd_mamba2(x: Tensor, dt: Tensor, A_head: Tensor, B: Tensor, C: Tensor, D: T
     initial_states (b,h,p,n) or (b,1,h,p,n).  Returns (Y, final_state fp32 (b,h,p,n)).
     """
     return _SSDMamba2.apply(x, dt, A_head, B, C, D, int(chunk_size), initial_states)
+
+
+def _mamba2_backward(ctx_shape, x, dt, Ah, B, Cm, cum, D, init4, states, dY, dfinal, has_D, has_init):
+    """Backward launcher of the Mamba-2 form; returns (dx, ddt, dA_head, dB, dC, dD or None, dinit or None), fp32
+    for the small ones."""
+    lib = _cabi.load()
+    dev = x.device
+    b, T, h, p = x.shape
+    with torch.cuda.device(dev):
+        dy = dY.contiguous().to(x.dtype)
+        dfin = None if dfinal is None else dfinal.float().contiguous()
+        dx = torch.empty_like(x)
+        dB = torch.empty_like(B)
+        dC = torch.empty_like(Cm)
+        ddt = torch.empty(b, T, h, dtype=torch.float32, device=dev)
+        dAh = torch.empty(h, dtype=torch.float32, device=dev)
+        dD = torch.empty(h, dtype=torch.float32, device=dev) if has_D else None
+        dinit = torch.empty(b, h, p, B.shape[3], dtype=torch.float32, device=dev) if has_init else None
+        ws = _workspace(lib, ctx_shape, _cabi.PASS_BWD, dev)
+        args = _cabi.BwdArgs(ctx_shape, _ptr(x), None, _ptr(dt), _ptr(Ah), _ptr(D) if has_D else None, _ptr(B),
+                             _ptr(Cm), _ptr(init4) if has_init else None, _ptr(cum), _ptr(dy), _ptr(dfin),
+                             _ptr(dx), _ptr(dB), _ptr(dC), None, _ptr(ddt), _ptr(dAh), _ptr(dD), _ptr(dinit),
+                             0, 0, _ptr(ws), ws.numel(), _ptr(states))
+        _cabi.check(lib.ssd_b200_bwd(C.byref(args), _stream(dev)))
+        _status(lib, ctx_shape, ws, dev)
+    return dx, ddt, dAh, dB, dC, dD, dinit
+
+
+class _SSDMamba2Gated(torch.autograd.Function):
+    """The scan followed by the block's output stage, out = rmsnorm(y over all heads) * silu(z)
+    (src/mamba_base_engine.py:189-191), as one operator.  The forward walk leaves the per-half-row sums of y^2
+    behind, so the norm reads y once; y itself is kept (the norm's backward needs it)."""
+
+    @staticmethod
+    def forward(ctx, x, dt, A_head, B, C_, D, z, norm_weight, eps, chunk_size, initial_states):
+        _check_inputs(x, B, C_)
+        lib = _cabi.load()
+        chunk = int(chunk_size)
+        xc, Bc, Cc = x.contiguous(), B.contiguous(), C_.contiguous()
+        dtc = dt.float().contiguous()
+        Ah = A_head.float().contiguous()
+        Dc = None if D is None else D.float().contiguous()
+        b, T, h, p = xc.shape
+        n = Bc.shape[3]
+        dev = x.device
+        assert z.is_cuda and z.shape[:2] == x.shape[:2] and z.numel() == x.numel(), \
+            f"the gate must have the size of y: {tuple(z.shape)} vs {tuple(x.shape)}"
+        init4 = None if initial_states is None else initial_states.reshape(b, h, p, n).float().contiguous()
+        shape = _make_shape(xc, _cabi.F32, Bc, chunk)
+        path = lib.ssd_b200_resolve_path(C.byref(shape))
+        _cabi.check(path)
+        with torch.cuda.device(dev):
+            ysq = None
+            if path == _cabi.PATH_TC:
+                ysq = torch.empty(b * (T // 128) * h * 2 * 128, dtype=torch.float32, device=dev)
+            y, final, cum, shape, states = _run_fwd(xc, None, dtc, Ah, Dc, Bc, Cc, chunk, init4, None,
+                                                    want_states=any(ctx.needs_input_grad), ysq=ysq)
+            zc = z.contiguous().to(xc.dtype).reshape(b * T, h * p)
+            w = norm_weight.contiguous().float()
+            out = torch.empty_like(y)
+            rstd = torch.empty(b * T, dtype=torch.float32, device=dev)
+            if ysq is not None:
+                _cabi.check(lib.ssd_b200_rmsnorm_fwd_presummed(_dt_code(y), b * T, h * p, float(eps), _ptr(y), _ptr(w),
+                                                               _ptr(zc), _ptr(ysq), h, _ptr(out), _ptr(rstd), _stream(dev)))
+            else:
+                _cabi.check(lib.ssd_b200_rmsnorm_fwd(_dt_code(y), b * T, h * p, float(eps), _ptr(y), _ptr(w), _ptr(zc),
+                                                     _ptr(out), _ptr(rstd), _stream(dev)))
+        ctx.states = states
+        ctx.save_for_backward(xc, dtc, Ah, Bc, Cc, cum,
+                              Dc if Dc is not None else torch.empty(0, device=dev),
+                              init4 if init4 is not None else torch.empty(0, device=dev), y, zc, w, rstd)
+        ctx.has_D = D is not None
+        ctx.has_init = initial_states is not None
+        ctx.init_shape = None if initial_states is None else tuple(initial_states.shape)
+        ctx.shape_struct = shape
+        ctx.in_dtypes = (dt.dtype, A_head.dtype, None if D is None else D.dtype, z.dtype, norm_weight.dtype)
+        ctx.z_shape = tuple(z.shape)
+        return out, final
+
+    @staticmethod
+    def backward(ctx, dout, dfinal):
+        x, dt, Ah, B, Cm, cum, D, init4, y, zc, w, rstd = ctx.saved_tensors
+        lib = _cabi.load()
+        dev = x.device
+        b, T, h, p = x.shape
+        rows, Dn = b * T, h * p
+        with torch.cuda.device(dev):
+            do = dout.contiguous().to(x.dtype).reshape(rows, Dn)
+            dy = torch.empty_like(y)
+            dz = torch.empty_like(zc)
+            dw = torch.empty(Dn, dtype=torch.float32, device=dev)
+            ws = torch.empty(int(lib.ssd_b200_rmsnorm_ws_floats(rows, Dn)), dtype=torch.float32, device=dev)
+            _cabi.check(lib.ssd_b200_rmsnorm_bwd(_dt_code(y), rows, Dn, _ptr(y), _ptr(w), _ptr(zc), _ptr(do), _ptr(rstd),
+                                                 _ptr(dy), _ptr(dz), _ptr(dw), _ptr(ws), _stream(dev)))
+        dx, ddt, dAh, dB, dC, dD, dinit = _mamba2_backward(ctx.shape_struct, x, dt, Ah, B, Cm, cum, D, init4, ctx.states,
+                                                           dy, dfinal, ctx.has_D, ctx.has_init)
+        dtd, ahd, dd, zd, wd = ctx.in_dtypes
+        return (dx, ddt.to(dtd), dAh.to(ahd), dB, dC, None if dD is None else dD.to(dd), dz.reshape(ctx.z_shape).to(zd),
+                dw.to(wd), None, None, None if dinit is None else dinit.reshape(ctx.init_shape))
+
+
+def ssd_mamba2_gated(x: Tensor, dt: Tensor, A_head: Tensor, B: Tensor, C: Tensor, D: Tensor | None, z: Tensor,
+                     norm_weight: Tensor, eps: float, chunk_size: int, initial_states: Tensor | None = None):
+    """``rmsnorm(Y) * silu(z)`` with ``Y = SSD(x*dt, dt*A_head, B, C) + D*x``: the scan and the block's output stage
+    (src/mamba_base_engine.py:170-173, :187, :189-191; norm as src/kernels/rmsnorm.py:75-150) in one operator.
+
+    z has the size of Y ((b,T,h,p) or (b,T,h*p)); norm_weight (h*p,); the norm runs over all heads of a position.
+    Returns (out in x's shape, final_state fp32 (b,h,p,n)).  Gradients: x, dt, A_head, B, C, D, z, norm_weight,
+    initial_states.
+    """
+    return _SSDMamba2Gated.apply(x, dt, A_head, B, C, D, z, norm_weight, float(eps), int(chunk_size), initial_states)
 
 
 def resolved_path_name(cfg) -> str:

@@ -110,6 +110,11 @@ typedef struct ssd_b200_fwd_args {
                      state walk and the rebuild of those arrays; NULL = do not save. */
     float *logdecay_total; /* optional output (b,h) fp32: the sum of the sequence's log-decays per (batch, head),
                               i.e. log of the factor by which the whole sequence scales an incoming state */
+    float *ysq;            /* optional output, tensor-core path only (must be NULL otherwise), T a multiple of 128:
+                              (b, T/128, h, 2, 128) fp32, sum over one half (32 values) of the head's row of y^2 for
+                              position 128 * tile + i, stored [b][tile][h][half][i].  Summed over h and half it is the
+                              row's sum of squares that the RMS norm after the scan needs
+                              (ssd_b200_rmsnorm_fwd_presummed), which then reads y once instead of twice. */
 } ssd_b200_fwd_args;
 
 /*
@@ -322,6 +327,10 @@ int ssd_b200_trapezoid_bwd(int32_t dtype, int64_t rows, int64_t H, const void *d
  * ssd_b200_rmsnorm_ws_floats(rows, D) floats of scratch.
  */
 size_t ssd_b200_rmsnorm_ws_floats(int64_t rows, int64_t D);
+/* The same forward with the row's sum of squares given as partial sums written by the scan's forward (`ysq` of
+ * ssd_b200_fwd_args; rows = b * T with T a multiple of 128, D = nheads * 64): one pass over x (and z). */
+int ssd_b200_rmsnorm_fwd_presummed(int32_t dtype, int64_t rows, int64_t D, float eps, const void *x, const float *weight,
+                                   const void *z, const float *ysq, int64_t nheads, void *out, float *rstd, void *stream);
 int ssd_b200_rmsnorm_fwd(int32_t dtype, int64_t rows, int64_t D, float eps, const void *x, const float *weight,
                          const void *z, void *out, float *rstd, void *stream);
 int ssd_b200_rmsnorm_bwd(int32_t dtype, int64_t rows, int64_t D, const void *x, const float *weight, const void *z,

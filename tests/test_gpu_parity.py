@@ -351,3 +351,38 @@ def test_sequence_streamer_is_exact_across_slices(pkg, cabi, idx, batch, seqlen,
     errs = {k: rel_err(got[k], want[k]) for k in ("y", "dx", "ddt", "dB", "dC", "dA_head", "dD")}
     bad = {k: v for k, v in errs.items() if not v < tol}
     assert not bad, errs
+
+
+@pytest.mark.parametrize("idx,batch,seqlen,tol", [(2, 2, 512, TOL_BF16), (1, 2, 256, TOL_BF16), (0, 2, 256, TOL_FP32)])
+def test_scan_with_gated_norm_output_stage(pkg, cabi, oracle, idx, batch, seqlen, tol):
+    """ssd_mamba2_gated = scan + the block's output stage norm(y) * silu(z) (src/mamba_base_engine.py:189-191): on the
+    tensor-core path the norm takes its row statistic from the partial sums the forward walk leaves behind (config 2
+    and 1 shapes); on the fp32 path it computes it itself.  Against the oracle scan followed by the eager norm."""
+    cfg = pkg.shrink(pkg.CONFIGS[idx], batch, seqlen)
+    inp = pkg.make_inputs(cfg)
+    b, T, h, p = inp["x"].shape
+    g = torch.Generator().manual_seed(123)
+    z = torch.randn(b, T, h * p, generator=g).to(inp["x"].dtype)
+    w = 1.0 + 0.1 * torch.randn(h * p, generator=g)
+    dout = torch.randn(b, T, h, p, generator=g).to(inp["x"].dtype)
+    names = ("x", "dt", "A_head", "B", "C", "D")
+    lv = {k: inp[k].to(DEV).requires_grad_(True) for k in names}
+    zl, wl = z.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
+    out, fs = pkg.ssd_mamba2_gated(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], zl, wl, 1e-6, cfg.chunk)
+    grads = torch.autograd.grad([out], list(lv.values()) + [zl, wl], [dout.to(DEV)])
+    torch.cuda.synchronize()
+    ol = {k: inp[k].float().requires_grad_(True) for k in names}
+    zo, wo = z.float().requires_grad_(True), w.clone().requires_grad_(True)
+    yo, fo = oracle.mamba2_operator(ol["x"], ol["dt"], ol["A_head"], ol["B"], ol["C"], ol["D"], cfg.chunk)
+    yf = yo.reshape(b, T, h * p)
+    oo = (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + 1e-6) * wo * torch.nn.functional.silu(zo)).reshape(b, T, h, p)
+    go = torch.autograd.grad([oo], list(ol.values()) + [zo, wo], [dout.float()])
+    errs = {"out": rel_err(out, oo), "final": rel_err(fs, fo)}
+    for k, a, c in zip(list(names) + ["z", "w"], grads, go):
+        errs["d" + k] = rel_err(a, c)
+    bad = {k: v for k, v in errs.items() if not v < tol}
+    assert not bad, errs
+    # and equal to the two-call composition of this package (same kernels apart from where the statistic comes from)
+    y2, _ = pkg.ssd_mamba2(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
+    o2 = pkg.fused_gate_norm(y2.reshape(b, T, h * p), zl, wl, 1e-6).reshape(b, T, h, p)
+    assert rel_err(out, o2) < (1e-2 if cfg.dtype == "bf16" else 1e-5)
