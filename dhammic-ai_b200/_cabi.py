@@ -7,7 +7,7 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 F32, BF16 = 0, 1
 PASS_FWD, PASS_BWD = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
@@ -38,7 +38,7 @@ class FwdArgs(C.Structure):
                 ("D", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("init", C.c_void_p), ("y", C.c_void_p),
                 ("final_state", C.c_void_p), ("a_cumsum", C.c_void_p), ("cumsum_is_input", C.c_int32),
                 ("flags", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("states", C.c_void_p), ("logdecay_total", C.c_void_p), ("ysq", C.c_void_p)]
+                ("states", C.c_void_p), ("logdecay_total", C.c_void_p), ("ysq", C.c_void_p), ("skip", C.c_void_p)]
 
 
 class BwdArgs(C.Structure):
@@ -48,7 +48,7 @@ class BwdArgs(C.Structure):
                 ("dB", C.c_void_p), ("dC", C.c_void_p), ("da", C.c_void_p), ("ddt", C.c_void_p),
                 ("dA_head", C.c_void_p), ("dD", C.c_void_p), ("dinit", C.c_void_p),
                 ("cumsum_is_input", C.c_int32), ("flags", C.c_int32), ("workspace", C.c_void_p),
-                ("workspace_bytes", C.c_size_t), ("states", C.c_void_p)]
+                ("workspace_bytes", C.c_size_t), ("states", C.c_void_p), ("skip", C.c_void_p), ("dskip", C.c_void_p)]
 
 
 _lib = None
@@ -86,7 +86,7 @@ def load() -> C.CDLL:
     lib.ssd_b200_state_prefix_all.restype = C.c_int
     lib.ssd_b200_state_prefix_all.argtypes = [C.c_void_p] * 6 + [C.c_int64] * 8 + [C.c_int32, C.c_void_p]
     lib.ssd_b200_m3_prologue_fwd.restype = C.c_int
-    lib.ssd_b200_m3_prologue_fwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 15
+    lib.ssd_b200_m3_prologue_fwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 7 + [C.c_int32] + [C.c_void_p] * 11
     lib.ssd_b200_rope_fwd.restype = C.c_int
     lib.ssd_b200_rope_fwd.argtypes = [C.c_int32] + [C.c_int64] * 4 + [C.c_int32] + [C.c_void_p] * 4
     lib.ssd_b200_rope_bwd.restype = C.c_int
@@ -108,7 +108,7 @@ def load() -> C.CDLL:
     lib.ssd_b200_m3_skip_fwd.restype = C.c_int
     lib.ssd_b200_m3_skip_fwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 8
     lib.ssd_b200_m3_prologue_bwd.restype = C.c_int
-    lib.ssd_b200_m3_prologue_bwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 21
+    lib.ssd_b200_m3_prologue_bwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 18 + [C.c_int32] + [C.c_void_p] * 3
     lib.ssd_b200_m3_chain_ws_floats.restype = C.c_size_t
     lib.ssd_b200_m3_chain_ws_floats.argtypes = [C.POINTER(Shape)]
     lib.ssd_b200_m3_chain_bwd.restype = C.c_int

@@ -316,13 +316,19 @@ int simt_bwd(const ssd_b200_bwd_args* a, cudaStream_t st) {
     return 0;
 }
 
-int check_forms(const void* a, const float* dt, const float* A_head, const float* D) {
-    if (a) {
-        if (dt || A_head || D) return fail(SSD_B200_EINVAL, "give either a, or dt and A_head (and D), not both");
-    } else {
-        if (!dt || !A_head) return fail(SSD_B200_EINVAL, "need a, or both dt and A_head");
+// 1 = operator form (a), 2 = Mamba-2 form (dt, A_head[, D]), 3 = scaled operator form (a and dt[, skip]); < 0 = error
+int check_forms(const void* a, const float* dt, const float* A_head, const float* D, const float* skip) {
+    if (a && dt) {
+        if (A_head || D) return fail(SSD_B200_EINVAL, "scaled operator form takes a and dt (and skip), not A_head or D");
+        return 3;
     }
-    return 0;
+    if (skip) return fail(SSD_B200_EINVAL, "skip belongs to the scaled operator form (a and dt both given)");
+    if (a) {
+        if (A_head || D) return fail(SSD_B200_EINVAL, "give either a, or dt and A_head (and D), not both");
+        return 1;
+    }
+    if (!dt || !A_head) return fail(SSD_B200_EINVAL, "need a, or both dt and A_head");
+    return 2;
 }
 
 }  // namespace
@@ -356,20 +362,29 @@ int m3_row_threads(int p) {
 
 template <class T>
 int m3_fwd_impl(const ssd::Dims& d, const void* x, const float* dt, const float* lam, const float* A_head, const void* B,
-                const void* C, const void* ang, void* xw, float* dA, void* Br, void* Cr, float* sdot, float* cum,
-                float* segsum, cudaStream_t st) {
+                const void* C, const void* ang, bool ang_f32, void* xw, float* dA, void* Br, void* Cr, float* sdot, float* cum,
+                float* segsum, const float* D, float* wout, float* skip, cudaStream_t st) {
     using namespace ssd::m3;
     const int E = d.h * (d.n / 2), nseg = (d.T + SEG - 1) / SEG;
     dim3 gs(nseg, (E + 255) / 256, d.b);
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<T><<<gs, 256, 0, st>>>((const T*)ang, segsum, d.T, E));
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<T, float><<<gs, 256, 0, st>>>((const T*)ang, segsum, cum, d.T, E, 0, -1.f)));
+    if (ang_f32) {  // angles keep their own precision whatever the storage type of x, B and C
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<float><<<gs, 256, 0, st>>>((const float*)ang, segsum, d.T, E));
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<float, float><<<gs, 256, 0, st>>>((const float*)ang, segsum, cum, d.T, E, 0, -1.f)));
+    } else {
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<T><<<gs, 256, 0, st>>>((const T*)ang, segsum, d.T, E));
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<T, float><<<gs, 256, 0, st>>>((const T*)ang, segsum, cum, d.T, E, 0, -1.f)));
+    }
     if (d.n % VecOf<T>::N == 0)
         SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_fwd_kernel<T, VecOf<T>::N><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n)));
     else
         SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_fwd_kernel<T, 2><<<dim3(d.T, d.b), 256, 0, st>>>((const T*)B, (const T*)C, cum, (T*)Br, (T*)Cr, d.T, d.h, d.g, d.n)));
     const size_t grows = (size_t)d.b * d.T * d.g, rows = (size_t)d.b * d.T * d.h;
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, bc_dot_kernel<T><<<(unsigned)((grows + 7) / 8), 256, 0, st>>>((const T*)B, (const T*)C, sdot, d.n, grows));
-    M3_ROW_DISPATCH(xw_fwd_kernel, (const T*)x, dt, lam, A_head, (T*)xw, dA, d.T, d.h, d.p, rows);
+    if (xw) {
+        M3_ROW_DISPATCH(xw_fwd_kernel, (const T*)x, dt, lam, A_head, (T*)xw, dA, d.T, d.h, d.p, rows);
+    } else {  // the scan takes the weight and the skip coefficient per position: x is not touched here
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, coef_fwd_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(dt, lam, A_head, D, sdot, wout, dA, skip, d.T, d.h, d.hpg, rows));
+    }
     CUDA_LAUNCH_CHECK("mamba3 prologue forward");
     return 0;
 }
@@ -387,12 +402,13 @@ int m3_skip_impl(const ssd::Dims& d, const void* y_scan, const void* x, const fl
 template <class T>
 int m3_bwd_impl(const ssd::Dims& d, const void* x, const void* dy, const float* dt, const float* lam, const float* D,
                 const void* B, const void* C, const float* cum, const float* sdot, const void* dxw, const void* dBr,
-                const void* dCr, void* dx, float* dw, float* dyx, void* dB, void* dC, void* dang, float* dcum, float* segsum,
-                cudaStream_t st) {
+                const void* dCr, void* dx, float* dw, float* dyx, void* dB, void* dC, void* dang, bool ang_f32, float* dcum,
+                float* segsum, cudaStream_t st) {
     using namespace ssd::m3;
     const int E = d.h * (d.n / 2), nseg = (d.T + SEG - 1) / SEG;
     const size_t rows = (size_t)d.b * d.T * d.h;
-    M3_ROW_DISPATCH(xw_bwd_kernel, (const T*)x, (const T*)dy, (const T*)dxw, dt, lam, D, sdot, (T*)dx, dw, dyx, d.T, d.h, d.hpg, d.p, rows);
+    if (dxw)  // otherwise the scan's backward has already produced dx, dw and dyx (scaled operator form)
+        M3_ROW_DISPATCH(xw_bwd_kernel, (const T*)x, (const T*)dy, (const T*)dxw, dt, lam, D, sdot, (T*)dx, dw, dyx, d.T, d.h, d.hpg, d.p, rows);
     if (d.n % VecOf<T>::N == 0) {
         const size_t items = (size_t)d.b * d.T * d.g * (d.n / VecOf<T>::N);
         SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (rope_bwd_kernel<T, VecOf<T>::N><<<(unsigned)((items + 255) / 256), 256, 0, st>>>((const T*)B, (const T*)C, cum, (const T*)dBr, (const T*)dCr, dyx, dt, lam, (T*)dB, (T*)dC, dcum, d.T, d.h, d.g, d.n, items)));
@@ -403,7 +419,10 @@ int m3_bwd_impl(const ssd::Dims& d, const void* x, const void* dy, const float* 
     dim3 gs(nseg, (E + 255) / 256, d.b);
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, scanT_segsum_kernel<float><<<gs, 256, 0, st>>>(dcum, segsum, d.T, E));
     // d raw_angles[t] = - sum_{s >= t} d cum[s]
-    SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<float, T><<<gs, 256, 0, st>>>(dcum, segsum, (T*)dang, d.T, E, 1, -1.f)));
+    if (ang_f32)
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<float, float><<<gs, 256, 0, st>>>(dcum, segsum, (float*)dang, d.T, E, 1, -1.f)));
+    else
+        SSD_LAUNCH(ssd::prof::K_TC_AUX, st, (scanT_apply_kernel<float, T><<<gs, 256, 0, st>>>(dcum, segsum, (T*)dang, d.T, E, 1, -1.f)));
     CUDA_LAUNCH_CHECK("mamba3 prologue backward");
     return 0;
 }
@@ -530,7 +549,8 @@ size_t ssd_b200_states_bytes(const ssd_b200_shape* shape) {
 int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
     if (!a) return fail(SSD_B200_EINVAL, "args is null");
     if (int rc = check_shape(&a->shape)) return rc;
-    if (int rc = check_forms(a->a, a->dt, a->A_head, a->D)) return rc;
+    const int form = check_forms(a->a, a->dt, a->A_head, a->D, a->skip);
+    if (form < 0) return form;
     const bool states_only = (a->flags & SSD_B200_FWD_STATES_ONLY) != 0;
     if (!a->x || !a->B || !a->C || !a->a_cumsum || (!a->y && !states_only)) return fail(SSD_B200_EINVAL, "null tensor pointer");
     if (states_only && !a->final_state) return fail(SSD_B200_EINVAL, "STATES_ONLY needs final_state");
@@ -540,6 +560,7 @@ int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (a->states && path != SSD_B200_PATH_TC) return fail(SSD_B200_EINVAL, "`states` is only used by the tensor-core path");
     if (a->ysq && path != SSD_B200_PATH_TC) return fail(SSD_B200_EINVAL, "`ysq` is only written by the tensor-core path");
+    if (form == 3 && path != SSD_B200_PATH_TC) return fail(SSD_B200_EUNSUPPORTED, "the scaled operator form needs the tensor-core path");
     if (path == SSD_B200_PATH_TC) return ssd::tc::forward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
     return a->shape.dtype == SSD_B200_BF16 ? simt_fwd<__nv_bfloat16>(a, st) : simt_fwd<float>(a, st);
 }
@@ -547,15 +568,19 @@ int ssd_b200_fwd(const ssd_b200_fwd_args* a, void* stream) {
 int ssd_b200_bwd(const ssd_b200_bwd_args* a, void* stream) {
     if (!a) return fail(SSD_B200_EINVAL, "args is null");
     if (int rc = check_shape(&a->shape)) return rc;
-    if (!(a->flags & SSD_B200_BWD_DINIT_ONLY))
-        if (int rc = check_forms(a->a, a->dt, a->A_head, a->D)) return rc;
+    int form = 0;
+    if (!(a->flags & SSD_B200_BWD_DINIT_ONLY)) {
+        form = check_forms(a->a, a->dt, a->A_head, a->D, a->skip);
+        if (form < 0) return form;
+    }
     const bool dinit_only = (a->flags & SSD_B200_BWD_DINIT_ONLY) != 0;
     if (dinit_only) {
         if (!a->C || !a->dy || !a->a_cumsum || !a->dinit) return fail(SSD_B200_EINVAL, "DINIT_ONLY needs C, dy, a_cumsum and dinit");
     } else {
         if (!a->x || !a->B || !a->C || !a->dy || !a->a_cumsum || !a->dx || !a->dB || !a->dC)
             return fail(SSD_B200_EINVAL, "null tensor pointer");
-        if (a->dt && (!a->ddt || !a->dA_head || (a->D && !a->dD))) return fail(SSD_B200_EINVAL, "Mamba-2 form needs ddt, dA_head (and dD)");
+        if (form == 2 && (!a->ddt || !a->dA_head || (a->D && !a->dD))) return fail(SSD_B200_EINVAL, "Mamba-2 form needs ddt, dA_head (and dD)");
+        if (form == 3 && (!a->ddt || (a->skip && !a->dskip))) return fail(SSD_B200_EINVAL, "scaled operator form needs ddt (and dskip)");
         if (a->a && !a->cumsum_is_input && !a->da) return fail(SSD_B200_EINVAL, "operator form needs da");
     }
     int path = resolve_path(a->shape);
@@ -563,6 +588,7 @@ int ssd_b200_bwd(const ssd_b200_bwd_args* a, void* stream) {
     if (!a->workspace || ((uintptr_t)a->workspace & 255)) return fail(SSD_B200_EWORKSPACE, "workspace null or not 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     if (a->states && path != SSD_B200_PATH_TC) return fail(SSD_B200_EINVAL, "`states` is only used by the tensor-core path");
+    if (form == 3 && path != SSD_B200_PATH_TC) return fail(SSD_B200_EUNSUPPORTED, "the scaled operator form needs the tensor-core path");
     if (path == SSD_B200_PATH_TC) return ssd::tc::backward(a, dims_of(a->shape), st, g_err, sizeof(g_err));
     return a->shape.dtype == SSD_B200_BF16 ? simt_bwd<__nv_bfloat16>(a, st) : simt_bwd<float>(a, st);
 }
@@ -647,18 +673,22 @@ int ssd_b200_selftest_bounded_wait(void* workspace, int32_t polls, void* stream)
 }
 
 int ssd_b200_m3_prologue_fwd(const ssd_b200_shape* shape, const void* x, const float* dt, const float* lam,
-                             const float* A_head, const void* B, const void* C, const void* raw_angles, void* xw,
-                             float* dA, void* Br, void* Cr, float* sdot, float* cum, float* segsum_ws, void* stream) {
+                             const float* A_head, const void* B, const void* C, const void* raw_angles, int32_t angles_dtype,
+                             void* xw, float* dA, void* Br, void* Cr, float* sdot, float* cum, float* segsum_ws, const float* D,
+                             float* w_out, float* skip_out, void* stream) {
     if (int rc = check_shape(shape)) return rc;
-    if (!x || !dt || !lam || !A_head || !B || !C || !raw_angles || !xw || !dA || !Br || !Cr || !sdot || !cum || !segsum_ws)
+    if (!dt || !lam || !A_head || !B || !C || !raw_angles || !dA || !Br || !Cr || !sdot || !cum || !segsum_ws)
         return fail(SSD_B200_EINVAL, "null pointer");
+    if (xw ? !x : (!w_out || !skip_out)) return fail(SSD_B200_EINVAL, "give x and xw, or w_out and skip_out");
+    if (angles_dtype != SSD_B200_F32 && angles_dtype != shape->dtype) return fail(SSD_B200_EINVAL, "raw_angles must be fp32 or in the storage dtype");
     if (shape->dstate % 2) return fail(SSD_B200_EINVAL, "d_state must be even for the pairwise rotation");
     ssd::Dims d = dims_of(*shape);
     if (d.T > 65535 || d.b > 65535) return fail(SSD_B200_EUNSUPPORTED, "grid dimension too large");
     cudaStream_t st = (cudaStream_t)stream;
+    const bool af = angles_dtype == SSD_B200_F32;
     return shape->dtype == SSD_B200_BF16
-               ? m3_fwd_impl<__nv_bfloat16>(d, x, dt, lam, A_head, B, C, raw_angles, xw, dA, Br, Cr, sdot, cum, segsum_ws, st)
-               : m3_fwd_impl<float>(d, x, dt, lam, A_head, B, C, raw_angles, xw, dA, Br, Cr, sdot, cum, segsum_ws, st);
+               ? m3_fwd_impl<__nv_bfloat16>(d, x, dt, lam, A_head, B, C, raw_angles, af, xw, dA, Br, Cr, sdot, cum, segsum_ws, D, w_out, skip_out, st)
+               : m3_fwd_impl<float>(d, x, dt, lam, A_head, B, C, raw_angles, af, xw, dA, Br, Cr, sdot, cum, segsum_ws, D, w_out, skip_out, st);
 }
 
 int ssd_b200_m3_skip_fwd(const ssd_b200_shape* shape, const void* y_scan, const void* x, const float* D, const float* dt,
@@ -699,18 +729,22 @@ int ssd_b200_m3_chain_bwd(const ssd_b200_shape* shape, const float* dw, const fl
 int ssd_b200_m3_prologue_bwd(const ssd_b200_shape* shape, const void* x, const void* dy, const float* dt, const float* lam,
                              const float* D, const void* B, const void* C, const float* cum, const float* sdot,
                              const void* dxw, const void* dBr, const void* dCr, void* dx, float* dw, float* dyx, void* dB,
-                             void* dC, void* d_raw_angles, float* dcum_ws, float* segsum_ws, void* stream) {
+                             void* dC, void* d_raw_angles, int32_t angles_dtype, float* dcum_ws, float* segsum_ws,
+                             void* stream) {
     if (int rc = check_shape(shape)) return rc;
-    if (!x || !dy || !dt || !lam || !B || !C || !cum || !sdot || !dxw || !dBr || !dCr || !dx || !dw || !dyx || !dB || !dC ||
-        !d_raw_angles || !dcum_ws || !segsum_ws)
+    if (!dt || !lam || !B || !C || !cum || !sdot || !dBr || !dCr || !dw || !dyx || !dB || !dC || !d_raw_angles || !dcum_ws ||
+        !segsum_ws)
         return fail(SSD_B200_EINVAL, "null pointer");
+    if (dxw && (!x || !dy || !dx)) return fail(SSD_B200_EINVAL, "with dxw given, x, dy and dx are needed");
+    if (angles_dtype != SSD_B200_F32 && angles_dtype != shape->dtype) return fail(SSD_B200_EINVAL, "d_raw_angles must be fp32 or in the storage dtype");
     if (shape->dstate % 2) return fail(SSD_B200_EINVAL, "d_state must be even for the pairwise rotation");
     ssd::Dims d = dims_of(*shape);
     if (d.T > 65535 || d.b > 65535) return fail(SSD_B200_EUNSUPPORTED, "grid dimension too large");
     cudaStream_t st = (cudaStream_t)stream;
+    const bool af = angles_dtype == SSD_B200_F32;
     return shape->dtype == SSD_B200_BF16
-               ? m3_bwd_impl<__nv_bfloat16>(d, x, dy, dt, lam, D, B, C, cum, sdot, dxw, dBr, dCr, dx, dw, dyx, dB, dC, d_raw_angles, dcum_ws, segsum_ws, st)
-               : m3_bwd_impl<float>(d, x, dy, dt, lam, D, B, C, cum, sdot, dxw, dBr, dCr, dx, dw, dyx, dB, dC, d_raw_angles, dcum_ws, segsum_ws, st);
+               ? m3_bwd_impl<__nv_bfloat16>(d, x, dy, dt, lam, D, B, C, cum, sdot, dxw, dBr, dCr, dx, dw, dyx, dB, dC, d_raw_angles, af, dcum_ws, segsum_ws, st)
+               : m3_bwd_impl<float>(d, x, dy, dt, lam, D, B, C, cum, sdot, dxw, dBr, dCr, dx, dw, dyx, dB, dC, d_raw_angles, af, dcum_ws, segsum_ws, st);
 }
 
 int ssd_b200_rope_fwd(int32_t dtype, int64_t B, int64_t T, int64_t H, int64_t D, int32_t broadcast_h, const void* x,

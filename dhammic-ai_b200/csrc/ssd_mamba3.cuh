@@ -317,6 +317,24 @@ __global__ void __launch_bounds__(256) xw_fwd_kernel(const T* __restrict__ x, co
     }
 }
 
+// The (b,T,h) coefficients of the single-scan form without touching x:  w = lam dt + u (input weight), a = dt A_head
+// (log-decay), skip = D - u s (coefficient of the direct x term; s = <B, C> of the head's group).
+__global__ void __launch_bounds__(256) coef_fwd_kernel(const float* __restrict__ dt, const float* __restrict__ lam,
+                                                       const float* __restrict__ A_head, const float* __restrict__ D,
+                                                       const float* __restrict__ sdot, float* __restrict__ wout,
+                                                       float* __restrict__ dA, float* __restrict__ skip, int Tlen, int h, int hpg,
+                                                       size_t total) {
+    const size_t w = (size_t)blockIdx.x * 256 + threadIdx.x;  // (b, t, h) flattened
+    if (w >= total) return;
+    const int hh = (int)(w % h);
+    const int t = (int)((w / h) % Tlen);
+    const float d = dt[w];
+    const float u = u_of(dt, lam, w, t, Tlen, h);
+    wout[w] = lam[w] * d + u;
+    dA[w] = d * A_head[hh];
+    skip[w] = (D ? D[hh] : 0.f) - u * sdot[(w / h) * (h / hpg) + hh / hpg];
+}
+
 // y = y_scan + (D - u s) x   (y may be y_scan itself)
 template <class T, int V, int TPR>
 __global__ void __launch_bounds__(256) skip_fwd_kernel(const T* y_scan, const T* __restrict__ x, const float* __restrict__ D,

@@ -55,8 +55,10 @@ inline bool supported(int dtype, int T, int h, int p, int n, int g, int l) {
 // caller's (b,T,h) order and goes through a shared-memory transpose, so reads and writes are both 128-byte rows.
 __global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restrict__ cum, const float* __restrict__ dt,
                                                           float* __restrict__ tcum, float* __restrict__ dtT,
+                                                          const float* __restrict__ skip, float* __restrict__ skipT,
                                                           int* __restrict__ extreme, int b, int T, int h, int l) {
     __shared__ float sdt[LT][33];
+    __shared__ float ssk[LT][33];
     const int kt = blockIdx.x, hg = blockIdx.y, bb = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h0 = hg * 32;
@@ -66,6 +68,12 @@ __global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restric
 #pragma unroll
         for (int t = warp; t < LT; t += 8)
             sdt[t][lane] = head_ok ? dt[((size_t)bb * T + (size_t)kt * LT + t) * h + h0 + lane] : 0.f;
+    }
+    if (skip) {  // per-position skip coefficient of the scaled operator form, same transpose
+        const bool head_ok = h0 + lane < h;
+#pragma unroll
+        for (int t = warp; t < LT; t += 8)
+            ssk[t][lane] = head_ok ? skip[((size_t)bb * T + (size_t)kt * LT + t) * h + h0 + lane] : 0.f;
     }
     __syncthreads();
     const int c = T / l;
@@ -93,6 +101,7 @@ __global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restric
             const float span = __shfl_sync(0xffffffffu, v, 0) - __shfl_sync(0xffffffffu, v, 31);
             if (lane == 0 && !(span <= kMaskSafeLog2)) atomicOr(extreme, 1);
             if (dt) dtT[o + tt] = sdt[tt][hl];
+            if (skip) skipT[o + tt] = ssk[tt][hl];
         }
     }
 }
@@ -110,9 +119,10 @@ struct DecayTileParams {
     const float* dyx;    // (b,h,T) or null
     const float* gS;     // (b,h,nt,8) from the backward tile kernel: terms that act through the tile's last row
     const float* dt;     // (b,T,h) or null (operator form)
-    const float* A_head; // (h) or null
+    const float* A_head; // (h) or null; null with dt given = scaled operator form (outputs ddt = ddtx, da, dskip = dyx)
     float* ddt;          // (b,T,h) or null
     float* da;           // (b,T,h) or null
+    float* dskip;        // (b,T,h) or null (scaled operator form)
     float* dAh_part;     // (b*nt, h)
     float* dD_part;      // (b*nt, h) or null
     int b, T, h, nt;
@@ -131,14 +141,14 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
             sdt[t][lane] = head_ok ? P.dt[((size_t)bb * P.T + (size_t)k * LT + t) * P.h + h0 + lane] : 0.f;
     }
     // every load of the warp's four heads is issued before any of them is used
-    float va[4][4], dxa[4][4], yxa[4], gsa[4];
+    const bool scaled = P.dt && !P.A_head;  // scaled operator form: three per-position outputs
+    float va[4][4], dxa[4][4], yxp[4][4], gsa[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int hh = h0 + warp * 4 + i;
-        yxa[i] = 0.f;
         gsa[i] = 0.f;
 #pragma unroll
-        for (int s4 = 0; s4 < 4; ++s4) va[i][s4] = dxa[i][s4] = 0.f;
+        for (int s4 = 0; s4 < 4; ++s4) va[i][s4] = dxa[i][s4] = yxp[i][s4] = 0.f;
         if (hh < P.h) {
             const size_t base = ((size_t)bb * P.h + hh) * P.T + (size_t)k * LT;
 #pragma unroll
@@ -146,7 +156,7 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
                 const int t = s4 * 32 + lane;
                 va[i][s4] = P.g[base + t];
                 dxa[i][s4] = P.ddtx[base + t];
-                if (P.dyx) yxa[i] += P.dyx[base + t];
+                if (P.dyx) yxp[i][s4] = P.dyx[base + t];
             }
             if (lane < 8)  // the eight terms that act through the tile's last row, one per lane
                 gsa[i] = P.gS[((((size_t)bb * P.h + hh) * P.nt) + k) * 8 + lane];
@@ -157,12 +167,9 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
     for (int i = 0; i < 4; ++i) {
         const int hl = warp * 4 + i, hh = h0 + hl;
         if (hh >= P.h) break;  // warp-uniform
-        float v[4], dx[4], yx = yxa[i];
+        float v[4];
 #pragma unroll
-        for (int s4 = 0; s4 < 4; ++s4) {
-            v[s4] = va[i][s4];
-            dx[s4] = dxa[i][s4];
-        }
+        for (int s4 = 0; s4 < 4; ++s4) v[s4] = va[i][s4];
         {
             float gs = gsa[i];  // fixed-order sum of the eight terms (the other lanes hold zero), result in every lane
 #pragma unroll
@@ -185,34 +192,55 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
         v[2] += tot[3];
         v[1] += tot[3] + tot[2];
         v[0] += (tot[3] + tot[2]) + tot[1];
-        float dAh = 0.f;
-        const float Ah = P.A_head ? P.A_head[hh] : 0.f;
 #pragma unroll
-        for (int s4 = 0; s4 < 4; ++s4) {
-            const int t = s4 * 32 + lane;
-            if (P.dt) {
-                sout[t][hl] = dx[s4] + v[s4] * Ah;
-                dAh += v[s4] * sdt[t][hl];
-            } else {
-                sout[t][hl] = v[s4];
+        for (int s4 = 0; s4 < 4; ++s4) va[i][s4] = v[s4];  // d a[t] of this head and tile
+        if (P.dt && !scaled) {
+            float dAh = 0.f, yx = 0.f;
+#pragma unroll
+            for (int s4 = 0; s4 < 4; ++s4) {
+                dAh += v[s4] * sdt[s4 * 32 + lane][hl];
+                yx += yxp[i][s4];
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                dAh += __shfl_xor_sync(0xffffffffu, dAh, o);
+                yx += __shfl_xor_sync(0xffffffffu, yx, o);
+            }
+            if (lane == 0) {
+                const size_t po = ((size_t)bb * P.nt + k) * P.h + hh;
+                P.dAh_part[po] = dAh;
+                if (P.dD_part) P.dD_part[po] = yx;
             }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            dAh += __shfl_xor_sync(0xffffffffu, dAh, o);
-            yx += __shfl_xor_sync(0xffffffffu, yx, o);
-        }
-        if (lane == 0) {
-            const size_t po = ((size_t)bb * P.nt + k) * P.h + hh;
-            if (P.dt) P.dAh_part[po] = dAh;
-            if (P.dD_part) P.dD_part[po] = yx;
-        }
     }
-    __syncthreads();
-    float* out = P.dt ? P.ddt : P.da;
-    if (out && head_ok) {
+    // per-position outputs in the caller's (b,T,h) layout, one transpose through shared memory each:
+    //   Mamba-2 form: ddt = ddtx + da A_head;  operator form: da;  scaled operator form: ddt = ddtx, da, dskip = dyx
+    for (int pass = 0; pass < 3; ++pass) {
+        float* out = nullptr;
+        if (pass == 0) out = P.dt ? P.ddt : P.da;
+        else if (pass == 1) out = scaled ? P.da : nullptr;
+        else out = scaled ? P.dskip : nullptr;
+        if (!out) continue;  // block-uniform
+        __syncthreads();
 #pragma unroll
-        for (int t = warp; t < LT; t += 8) out[((size_t)bb * P.T + (size_t)k * LT + t) * P.h + h0 + lane] = sout[t][lane];
+        for (int i = 0; i < 4; ++i) {
+            const int hl = warp * 4 + i, hh = h0 + hl;
+            if (hh >= P.h) break;
+            const float Ah = (P.A_head && pass == 0) ? P.A_head[hh] : 0.f;
+#pragma unroll
+            for (int s4 = 0; s4 < 4; ++s4) {
+                float val;
+                if (pass == 0) val = P.dt ? dxa[i][s4] + va[i][s4] * Ah : va[i][s4];
+                else if (pass == 1) val = va[i][s4];
+                else val = yxp[i][s4];
+                sout[s4 * 32 + lane][hl] = val;
+            }
+        }
+        __syncthreads();
+        if (head_ok) {
+#pragma unroll
+            for (int t = warp; t < LT; t += 8) out[((size_t)bb * P.T + (size_t)k * LT + t) * P.h + h0 + lane] = sout[t][lane];
+        }
     }
 }
 
@@ -254,6 +282,7 @@ struct WalkParams {
     const float* tcum;
     const float* dtT;
     const float* D;
+    const float* skipT;  // (b,h,T) per-position skip coefficient (replaces D), or null
     const float* seed;   // init (modes 0,1) or dfinal (reverse walks), (b,h,p,n) fp32, may be null
     float* out_state;    // final_state (modes 0,1) or dinit (reverse walks), may be null
     CUtensorMap mY;   // y store (mode 0)

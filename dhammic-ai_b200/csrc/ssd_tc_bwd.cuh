@@ -35,6 +35,7 @@ struct BwdParams {
     const float* tcum;             // (b,h,T) tile-cumulative log2-decay
     const float* dtT;              // (b,h,T) or null
     const float* D;                // (h) or null
+    const float* skipT;            // (b,h,T) per-position skip coefficient (replaces D), or null
     float* g;                      // (b,h,T) gradient w.r.t. the tile-cumulative log-decay
     float* ddtx;                   // (b,h,T) sum_p dX * x
     float* dyx;                    // (b,h,T) sum_p dy * x
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
     // written before the last block-wide barrier of head hl
     float c_n = P.tcum[pos_of(0) + row], cend_n = P.tcum[pos_of(0) + (row | 31)];
     float dt_n = P.dtT ? P.dtT[pos_of(0) + row] : 1.f;
-    float D_n = P.D ? P.D[gg * hpg] : 0.f;
+    float D_n = P.skipT ? P.skipT[pos_of(0) + row] : (P.D ? P.D[gg * hpg] : 0.f);
     auto publish_columns = [&](int buf) {
         if (qc == 0) {
             scum2[buf * LT + row] = c_n;
@@ -198,13 +199,13 @@ __global__ void __launch_bounds__(512, 1) bwd_tile_kernel(const __grid_constant_
             c_n = P.tcum[o + row];
             cend_n = P.tcum[o + (row | 31)];
             dt_n = P.dtT ? P.dtT[o + row] : 1.f;
-            D_n = P.D ? P.D[hh + 1] : 0.f;
+            D_n = P.skipT ? P.skipT[o + row] : (P.D ? P.D[hh + 1] : 0.f);
         } else if (more) {
             const size_t o = ((size_t)nbb * P.h + ngg * hpg) * P.T + (size_t)nk * LT;
             c_n = P.tcum[o + row];
             cend_n = P.tcum[o + (row | 31)];
             dt_n = P.dtT ? P.dtT[o + row] : 1.f;
-            D_n = P.D ? P.D[ngg * hpg] : 0.f;
+            D_n = P.skipT ? P.skipT[o + row] : (P.D ? P.D[ngg * hpg] : 0.f);
         }
         mbar_wait(&bar_xy[xb], (hcur >> 1) & 1, &failed);
         uint8_t* sX = sXY + (2 * xb) * PANEL;

@@ -39,7 +39,7 @@ inline bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t c
 }
 
 struct Ws {
-    size_t status, tcum, dtT, Hst, Qst, final_state, dinit, g, ddtx, dyx, gS, dAh_part, dD_part, total;
+    size_t status, tcum, dtT, skipT, Hst, Qst, final_state, dinit, g, ddtx, dyx, gS, dAh_part, dD_part, total;
 };
 
 inline Ws ws_layout(const Dims& d, int pass) {
@@ -56,6 +56,7 @@ inline Ws ws_layout(const Dims& d, int pass) {
     w.status = take(256);
     w.tcum = take(bht);
     w.dtT = take(bht);
+    w.skipT = take(bht);
     if (pass == SSD_B200_PASS_BWD) {
         w.Hst = take(st);
         w.Qst = take(st);
@@ -74,11 +75,11 @@ inline Ws ws_layout(const Dims& d, int pass) {
 
 inline size_t workspace_bytes(const Dims& d, int pass) { return ws_layout(d, pass).total; }
 // The `states` buffer a forward call may fill for the backward call of the same inputs: the bf16 state entering
-// every tile, followed by the two (b,h,T) fp32 arrays the tile kernels read (tile-cumulative log2 decay, dt in
-// (b,h,T) order) and the extreme-decay flag of tile_cumsum_kernel, so that the backward neither walks the states
+// every tile, followed by the three (b,h,T) fp32 arrays the tile kernels read (tile-cumulative log2 decay, dt and
+// the per-position skip coefficient in (b,h,T) order) and the extreme-decay flag of tile_cumsum_kernel, so that the backward neither walks the states
 // nor rebuilds those arrays.
 inline size_t tile_states_bytes(const Dims& d) { return (size_t)d.b * (d.T / LT) * d.h * DN * HP * 2; }
-inline size_t states_bytes(const Dims& d) { return tile_states_bytes(d) + 2 * ((size_t)d.b * d.h * d.T * 4) + 256; }
+inline size_t states_bytes(const Dims& d) { return tile_states_bytes(d) + 3 * ((size_t)d.b * d.h * d.T * 4) + 256; }
 
 #define SSD_TC_FAIL(code, ...)              \
     do {                                    \
@@ -122,10 +123,10 @@ inline int set_walk_attrs(char* err, size_t errn) {
     return 0;
 }
 
-inline int launch_tile_cumsum(const Dims& d, const float* cum, const float* dt, float* tcum, float* dtT, int* extreme,
-                              cudaStream_t st, char* err, size_t errn) {
+inline int launch_tile_cumsum(const Dims& d, const float* cum, const float* dt, float* tcum, float* dtT, const float* skip,
+                              float* skipT, int* extreme, cudaStream_t st, char* err, size_t errn) {
     dim3 g(d.T / LT, (d.h + 31) / 32, d.b);
-    SSD_LAUNCH(prof::K_TC_AUX, st, tile_cumsum_kernel<<<g, 256, 0, st>>>(cum, dt, tcum, dtT, extreme, d.b, d.T, d.h, d.l));
+    SSD_LAUNCH(prof::K_TC_AUX, st, tile_cumsum_kernel<<<g, 256, 0, st>>>(cum, dt, tcum, dtT, skip, skipT, extreme, d.b, d.T, d.h, d.l));
     SSD_TC_CHECK("tile_cumsum");
     return 0;
 }
@@ -141,17 +142,19 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     int* status = (int*)(ws + w.status);
     float* tcum = (float*)(ws + w.tcum);
     float* dtT = a->dt ? (float*)(ws + w.dtT) : nullptr;
+    float* skipT = a->skip ? (float*)(ws + w.skipT) : nullptr;
     int* extreme = status + 1;  // raised by tile_cumsum_kernel (see kMaskSafeLog2)
     if (a->states && !states_only) {  // kept for the backward call, behind the tile states
         tcum = (float*)((char*)a->states + tile_states_bytes(d));
         if (a->dt) dtT = tcum + (size_t)d.b * d.h * d.T;
-        extreme = (int*)(tcum + 2 * (size_t)d.b * d.h * d.T);
+        if (a->skip) skipT = tcum + 2 * (size_t)d.b * d.h * d.T;
+        extreme = (int*)(tcum + 3 * (size_t)d.b * d.h * d.T);
         if (cudaMemsetAsync(extreme, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     }
     if (cudaMemsetAsync(status, 0, 8, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     if (!a->cumsum_is_input) {
         simt::Params P{};
-        P.d = d; P.a = a->a; P.dt = a->dt; P.A_head = a->A_head; P.cum = a->a_cumsum;
+        P.d = d; P.a = a->a; P.dt = a->a ? nullptr : a->dt; P.A_head = a->A_head; P.cum = a->a_cumsum;
         P.a_is_bf16 = a->shape.a_dtype == SSD_B200_BF16;
         size_t sm = (size_t)d.l * (d.h + 1) * 4;
         if (sm > 48 * 1024 &&
@@ -160,9 +163,10 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
         SSD_LAUNCH(prof::K_CUMSUM, st, simt::chunk_cumsum_kernel<<<dim3(d.c, d.b), simt::NTHR, sm, st>>>(P));
         SSD_TC_CHECK("chunk_cumsum");
     }
-    if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, extreme, st, err, errn)) return rc;
+    if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, a->skip, skipT, extreme, st, err, errn)) return rc;
     if (int rc = set_walk_attrs(err, errn)) return rc;
     WalkParams P{};
+    P.skipT = skipT;
     P.extreme = extreme;
     P.ysq = a->ysq;
     const uint64_t rows = (uint64_t)d.b * d.T;
@@ -214,11 +218,13 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     float* dinit = a->dinit ? a->dinit : (float*)(ws + w.dinit);
     if (cudaMemsetAsync(status, 0, 8, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     int* extreme = status + 1;
-    if (a->states && !(a->flags & SSD_B200_BWD_DINIT_ONLY)) {  // the forward left both arrays and the flag behind the tile states
+    float* skipT = a->skip ? (float*)(ws + w.skipT) : nullptr;
+    if (a->states && !(a->flags & SSD_B200_BWD_DINIT_ONLY)) {  // the forward left the arrays and the flag behind the tile states
         tcum = (float*)((uintptr_t)a->states + tile_states_bytes(d));
         dtT = a->dt ? tcum + (size_t)d.b * d.h * d.T : nullptr;
-        extreme = (int*)(tcum + 2 * (size_t)d.b * d.h * d.T);
-    } else if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, extreme, st, err, errn)) {
+        skipT = a->skip ? tcum + 2 * (size_t)d.b * d.h * d.T : nullptr;
+        extreme = (int*)(tcum + 3 * (size_t)d.b * d.h * d.T);
+    } else if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, a->skip, skipT, extreme, st, err, errn)) {
         return rc;
     }
     if (int rc = set_walk_attrs(err, errn)) return rc;
@@ -263,7 +269,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     {
         BwdParams P{};
         P.mX = mX; P.mdY = mdY; P.mB = mB; P.mC = mC; P.mH = mH; P.mQ = mQ; P.mdX = mdX; P.mdB = mdB; P.mdC = mdC;
-        P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
+        P.tcum = tcum; P.dtT = dtT; P.D = a->D; P.skipT = skipT; P.g = (float*)(ws + w.g); P.ddtx = (float*)(ws + w.ddtx);
         P.dyx = (float*)(ws + w.dyx); P.status = status; P.T = d.T; P.h = d.h;
         P.hpg = d.hpg; P.nt = nt; P.b = d.b; P.gS = (float*)(ws + w.gS);
         P.items = nt * d.g * d.b;
@@ -276,13 +282,14 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     {
         DecayTileParams P{};
         P.g = (const float*)(ws + w.g); P.ddtx = (const float*)(ws + w.ddtx); P.gS = (const float*)(ws + w.gS);
-        P.dyx = (a->dt && a->D) ? (const float*)(ws + w.dyx) : nullptr;
+        P.dyx = (a->dt && (a->D || a->skip)) ? (const float*)(ws + w.dyx) : nullptr;
         P.dt = a->dt; P.A_head = a->A_head; P.ddt = a->ddt; P.da = a->cumsum_is_input ? nullptr : a->da;
+        P.dskip = a->skip ? a->dskip : nullptr;
         P.dAh_part = (float*)(ws + w.dAh_part); P.dD_part = P.dyx ? (float*)(ws + w.dD_part) : nullptr;
         P.b = d.b; P.T = d.T; P.h = d.h; P.nt = nt;
         SSD_LAUNCH(prof::K_DECAY, st, decay_tile_kernel<<<dim3(nt, (d.h + 31) / 32, d.b), 256, 0, st>>>(P));
         SSD_TC_CHECK("decay_grad");
-        if (a->dt) {
+        if (a->dt && a->A_head) {
             SSD_LAUNCH(prof::K_REDUCE, st, reduce_rows_kernel<<<d.h, 256, 0, st>>>(P.dAh_part, a->dA_head, d.b * nt, d.h));
             if (a->D) SSD_LAUNCH(prof::K_REDUCE, st, reduce_rows_kernel<<<d.h, 256, 0, st>>>(P.dD_part, a->dD, d.b * nt, d.h));
             SSD_TC_CHECK("reduce_batch");

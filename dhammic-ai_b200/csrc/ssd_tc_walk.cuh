@@ -228,23 +228,27 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
         const float* tcum = P.tcum + bh * P.T;
         const float* dtT = P.dtT ? P.dtT + bh * P.T : nullptr;
         const uint32_t lanes = lane_base(warp);
-        const float Dh = (MODE == 0 && P.D) ? P.D[hh] : 0.f;
+        const float Dhead = (MODE == 0 && P.D) ? P.D[hh] : 0.f;
+        const float* skipT = (MODE == 0 && P.skipT) ? P.skipT + bh * P.T : nullptr;  // per-position skip instead of D
+        const bool has_skip = MODE == 0 && (P.D || P.skipT);
         // per-tile scalars are fetched one tile ahead
         auto tile_of = [&](int it) { return it; };
         float c_n = tcum[(size_t)tile_of(0) * LT + row];
         float cend_n = tcum[(size_t)tile_of(0) * LT + (row | 31)];
         float dt_n = dtT ? dtT[(size_t)tile_of(0) * LT + row] : 1.f;
+        float sk_n = skipT ? skipT[(size_t)tile_of(0) * LT + row] : Dhead;
 
         for (int it = 0; it < nt; ++it) {
             const int k = tile_of(it);
             const int s = it % NST, buf = it & 1;
             const uint32_t ph = it & 1;
-            const float c_i = c_n, cend = cend_n, dtv = dt_n;
+            const float c_i = c_n, cend = cend_n, dtv = dt_n, Dh = sk_n;
             if (it + 1 < nt) {
                 const size_t o = (size_t)tile_of(it + 1) * LT;
                 c_n = tcum[o + row];
                 cend_n = tcum[o + (row | 31)];
                 dt_n = dtT ? dtT[o + row] : 1.f;
+                if (skipT) sk_n = skipT[o + row];
             }
             if (hf == 0) {
                 scum2[buf * LT + row] = c_i;
@@ -357,7 +361,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
 #pragma unroll
                     for (int q = 0; q < 16; ++q) {
                         float2 v = fma2(e2, O2[q], A2[q]);
-                        if (P.D) v = fma2(D2, __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xrow[q])), v);
+                        if (has_skip) v = fma2(D2, __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&xrow[q])), v);
                         Y2[q] = v;
                     }
                 }

@@ -160,7 +160,7 @@ class LazySSDCache(dict):
         return dict.get(self, key)
 
 
-def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=False, ysq=None):
+def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=False, ysq=None, skip=None):
     """Common forward launcher.  Returns (y, final_state fp32 (b,h,p,n), a_cumsum, shape, states or None).
     ``ysq``: optional fp32 buffer (b, T/128, h, 2, 128) for the per-half-row sums of y^2 (tensor-core path)."""
     lib = _cabi.load()
@@ -189,7 +189,7 @@ def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=
                 states = torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
         args = _cabi.FwdArgs(shape, _ptr(x), _ptr(a), _ptr(dt), _ptr(A_head), _ptr(D), _ptr(B), _ptr(Cm), _ptr(init4),
                              _ptr(y), _ptr(final), _ptr(cum), 1 if a_cumsum_in is not None else 0, 0, _ptr(ws),
-                             ws.numel(), _ptr(states), None, _ptr(ysq))
+                             ws.numel(), _ptr(states), None, _ptr(ysq), _ptr(skip))
         _cabi.check(lib.ssd_b200_fwd(C.byref(args), _stream(dev)))
         _status(lib, shape, ws, dev)
     return y, final, cum, shape, states
@@ -357,6 +357,26 @@ def ssd_mamba2(x: Tensor, dt: Tensor, A_head: Tensor, B: Tensor, C: Tensor, D: T
     initial_states (b,h,p,n) or (b,1,h,p,n).  Returns (Y, final_state fp32 (b,h,p,n)).
     """
     return _SSDMamba2.apply(x, dt, A_head, B, C, D, int(chunk_size), initial_states)
+
+
+def _run_bwd_scaled(shape, x, a, w, skip, B, Cm, cum, dY, states):
+    """Backward launcher of the scaled operator form (X = x * w, log-decay a, y += skip * x).  Returns
+    (dx, da, dw, dskip, dB, dC): dx complete, the three (b,T,h) gradients fp32."""
+    lib = _cabi.load()
+    dev = x.device
+    b, T, h, p = x.shape
+    with torch.cuda.device(dev):
+        dy = dY.contiguous().to(x.dtype)
+        dx, dB, dC = torch.empty_like(x), torch.empty_like(B), torch.empty_like(Cm)
+        da = torch.empty(b, T, h, dtype=torch.float32, device=dev)
+        dw, dskip = torch.empty_like(da), torch.empty_like(da)
+        ws = _workspace(lib, shape, _cabi.PASS_BWD, dev)
+        args = _cabi.BwdArgs(shape, _ptr(x), _ptr(a), _ptr(w), None, None, _ptr(B), _ptr(Cm), None, _ptr(cum), _ptr(dy),
+                             None, _ptr(dx), _ptr(dB), _ptr(dC), _ptr(da), _ptr(dw), None, None, None, 0, 0, _ptr(ws),
+                             ws.numel(), _ptr(states), _ptr(skip), _ptr(dskip))
+        _cabi.check(lib.ssd_b200_bwd(C.byref(args), _stream(dev)))
+        _status(lib, shape, ws, dev)
+    return dx, da, dw, dskip, dB, dC
 
 
 def _mamba2_backward(ctx_shape, x, dt, Ah, B, Cm, cum, D, init4, states, dY, dfinal, has_D, has_init):

@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define SSD_B200_ABI_VERSION 2
+#define SSD_B200_ABI_VERSION 3
 
 enum {
     SSD_B200_OK = 0,
@@ -77,10 +77,14 @@ typedef struct ssd_b200_shape {
  * with dt/A_head/D given, also the caller's input products and D skip
  * (src/mamba_base_engine.py:170-173, :187).
  *
- * Two ways to give the decay and the input scaling:
+ * Three ways to give the decay and the input scaling:
  *   (1) operator form:  a != NULL, dt == A_head == D == NULL:  X = x, log-decay = a   (b,T,h)
  *   (2) Mamba-2 form:   a == NULL, dt (b,T,h) fp32, A_head (h) fp32, D (h) fp32 or NULL:
  *                       X = x * dt, log-decay = dt * A_head, y += D * x
+ *   (3) scaled operator form (tensor-core path only): a != NULL and dt (b,T,h) fp32 != NULL, A_head == D == NULL:
+ *                       X = x * dt, log-decay = a, and with skip (b,T,h) fp32 != NULL  y += skip * x
+ *       (a per-position input weight and a per-position skip coefficient: what the Mamba-3 style block's
+ *       single-scan form needs, src/mamba_base_engine.py:170-187, without materialising x * weight).
  *
  *   x (b,T,h,p)  B,C (b,T,g,n)  init (b,h,p,n) fp32 or NULL  ->  y (b,T,h,p), final_state (b,h,p,n) fp32
  *   a_cumsum (b,h,c,l) fp32: within-chunk inclusive cumulative log-decay; written unless
@@ -115,6 +119,7 @@ typedef struct ssd_b200_fwd_args {
                               position 128 * tile + i, stored [b][tile][h][half][i].  Summed over h and half it is the
                               row's sum of squares that the RMS norm after the scan needs
                               (ssd_b200_rmsnorm_fwd_presummed), which then reads y once instead of twice. */
+    const float *skip;     /* form (3) only: per-position skip coefficient (b,T,h) fp32, or NULL */
 } ssd_b200_fwd_args;
 
 /*
@@ -124,7 +129,9 @@ typedef struct ssd_b200_fwd_args {
  *   operator form : da (b,T,h) fp32 -- gradient of the per-position log-decay; skipped (may be
  *                   NULL) when cumsum_is_input != 0, matching the reference, whose cached call
  *                   returns no decay gradient (src/kernels/ssd_scan.py:494-500, :533);
- *   Mamba-2 form  : ddt (b,T,h) fp32, dA_head (h) fp32, dD (h) fp32 (dD only when D != NULL).
+ *   Mamba-2 form  : ddt (b,T,h) fp32, dA_head (h) fp32, dD (h) fp32 (dD only when D != NULL);
+ *   scaled operator form: da (b,T,h) fp32, ddt (b,T,h) fp32 = gradient of the input weight (sum_p dX x), and with
+ *                   skip given dskip (b,T,h) fp32 = sum_p dy x; dx already contains skip * dy.
  * a_cumsum is the tensor the forward produced (or was given).
  */
 typedef struct ssd_b200_bwd_args {
@@ -153,6 +160,8 @@ typedef struct ssd_b200_bwd_args {
     void *workspace;
     size_t workspace_bytes;
     const void *states; /* optional: what the forward wrote into its `states`; NULL = recompute */
+    const float *skip;  /* scaled operator form: the forward's skip (b,T,h) fp32, or NULL */
+    float *dskip;       /* scaled operator form with skip: (b,T,h) fp32 */
 } ssd_b200_bwd_args;
 
 /* ABI version of the loaded library (compare with SSD_B200_ABI_VERSION). */
@@ -265,17 +274,22 @@ int ssd_b200_state_prefix_all(const float *pieces, const float *logp, const floa
  *     Y = SSD(x w, a, Br, Cr) + (D - u s) x,   w = lam dt + u,  u[t] = (1 - lam[t+1]) dt[t+1] (0 at the end),
  * s = <B, C> per group (the rotation preserves it), a = dt A_head.
  *   prologue_fwd: cum = -cumsum_T(raw_angles) (b,T,h,n/2); Br, Cr = rope(B, cum), rope(C, cum) (b,T,h,n);
- *                 sdot = s (b,T,g); xw = x w; dA = a.
+ *                 sdot = s (b,T,g); dA = a; and either xw = x w (xw != NULL) or, with xw == NULL, the per-position
+ *                 coefficients w_out = w and skip_out = D - u s (b,T,h) for the scan's scaled operator form, which
+ *                 then applies them itself (x is not read here).
  *   skip_fwd:     y = y_scan + (D - u s) x   (y may be y_scan; D may be NULL).
- *   prologue_bwd: from dy, the scan's gradients dxw, dBr, dCr:  dx = dxw w + (D - u s) dy,  dw = <dxw, x>,
- *                 dyx = <dy, x> per (b,t,h), dB, dC (b,T,g,n) (rotation undone, heads of a group summed, plus the
- *                 s term) and d raw_angles.
- * x, B, C, raw_angles and the tensor outputs are in shape->dtype; dt, lam, A_head, D, dA, sdot, cum, dw, dyx
- * are fp32.  segsum_ws: b * ceil(T/128) * h * n/2 floats of scratch; dcum_ws: (b,T,h,n/2) fp32 scratch.
+ *   prologue_bwd: from the scan's gradients dBr, dCr and dw = <dxw, x>, dyx = <dy, x> per (b,t,h):  dB, dC (b,T,g,n)
+ *                 (rotation undone, heads of a group summed, plus the s term) and d raw_angles.  With dxw != NULL it
+ *                 first forms dx = dxw w + (D - u s) dy, dw and dyx itself; with dxw == NULL dw and dyx are inputs
+ *                 (the scaled operator form's ddt and dskip) and x, dy, dx are not touched.
+ * x, B, C and the tensor outputs are in shape->dtype; raw_angles / d_raw_angles in angles_dtype (fp32 or shape->dtype;
+ * the cumulative angle is fp32 either way); dt, lam, A_head, D, dA, sdot, cum, dw, dyx, w_out, skip_out are fp32.
+ * segsum_ws: b * ceil(T/128) * h * n/2 floats of scratch; dcum_ws: (b,T,h,n/2) fp32 scratch.
  */
 int ssd_b200_m3_prologue_fwd(const ssd_b200_shape *shape, const void *x, const float *dt, const float *lam,
-                             const float *A_head, const void *B, const void *C, const void *raw_angles, void *xw,
-                             float *dA, void *Br, void *Cr, float *sdot, float *cum, float *segsum_ws, void *stream);
+                             const float *A_head, const void *B, const void *C, const void *raw_angles,
+                             int32_t angles_dtype, void *xw, float *dA, void *Br, void *Cr, float *sdot, float *cum,
+                             float *segsum_ws, const float *D, float *w_out, float *skip_out, void *stream);
 int ssd_b200_m3_skip_fwd(const ssd_b200_shape *shape, const void *y_scan, const void *x, const float *D, const float *dt,
                          const float *lam, const float *sdot, void *y, void *stream);
 /* Chain rule of the single-scan form on the (b,T,h) fp32 tensors, after ssd_b200_m3_prologue_bwd (dw, dyx) and the
@@ -292,8 +306,8 @@ int ssd_b200_m3_chain_bwd(const ssd_b200_shape *shape, const float *dw, const fl
 int ssd_b200_m3_prologue_bwd(const ssd_b200_shape *shape, const void *x, const void *dy, const float *dt,
                              const float *lam, const float *D, const void *B, const void *C, const float *cum,
                              const float *sdot, const void *dxw, const void *dBr, const void *dCr, void *dx, float *dw,
-                             float *dyx, void *dB, void *dC, void *d_raw_angles, float *dcum_ws, float *segsum_ws,
-                             void *stream);
+                             float *dyx, void *dB, void *dC, void *d_raw_angles, int32_t angles_dtype, float *dcum_ws,
+                             float *segsum_ws, void *stream);
 
 /*
  * The two element-wise operators that feed the scan in the reference's block, stand-alone:

@@ -276,6 +276,29 @@ def test_saved_states_equal_recomputed_states(pkg, cabi):
         assert torch.equal(kept[k], redone[k]), k
 
 
+def test_mamba3_variant_takes_fp32_angles_with_bf16_tensors(pkg, cabi, oracle):
+    """Angles given in fp32 (the reference's fp32 dt * theta product) are summed at that precision although x, B and C
+    are bf16; their gradient comes back in fp32."""
+    cfg = pkg.shrink(pkg.CONFIGS[3], 1, 512)
+    inp = pkg.make_inputs(cfg)
+    g = torch.Generator().manual_seed(3)
+    inp["raw_angles"] = (torch.rand(inp["raw_angles"].shape, generator=g) * 2 - 1) * 0.37   # not bf16-representable
+    names = ("x", "dt", "A_head", "B", "C", "D", "raw_angles", "lam")
+    lv = {k: inp[k].to(DEV).requires_grad_(True) for k in names}
+    y = pkg.ssd_mamba3(*[lv[k] for k in names], cfg.chunk)
+    grads = torch.autograd.grad([y], list(lv.values()), [inp["dy"].to(DEV)])
+    torch.cuda.synchronize()
+    assert grads[6].dtype == torch.float32
+    ol = {k: inp[k].float().requires_grad_(True) for k in names}
+    yo = oracle.mamba3_operator(*[ol[k] for k in names], cfg.chunk)
+    go = torch.autograd.grad([yo], list(ol.values()), [inp["dy"].float()])
+    errs = {"y": rel_err(y, yo)}
+    for k, a, b in zip(names, grads, go):
+        errs["d" + k] = rel_err(a, b)
+    bad = {k: v for k, v in errs.items() if not v < TOL_BF16}
+    assert not bad, errs
+
+
 @pytest.mark.parametrize("dtype,tol", [("fp32", TOL_FP32), ("bf16", TOL_BF16)])
 def test_mamba3_variant(pkg, cabi, oracle, dtype, tol):
     """Rotary state angles + trapezoidal two-term form (config 3 per-token shape, reduced batch / sequence)
