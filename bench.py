@@ -276,7 +276,7 @@ def seq_parallel_record(pkg, dmod, cabi, args, dev, rank, world, barrier):
         return float(t.item()) / steps
 
     steps = max(3, min(args.steps, 10))
-    comm = dmod.TorchDistComm()
+    comm, comm_kind = dmod.make_comm(prefer_peer_stores=not args.nccl_exchange)
     step = make_step(cfg, rank, comm)
     ms = timed(step, barrier, steps, True)
     # phases of one step: kernels per slot, collectives from the communicator's own events
@@ -290,7 +290,7 @@ def seq_parallel_record(pkg, dmod, cabi, args, dev, rank, world, barrier):
     coll = comm.read_timings()
     comm.timings = None
     phases = {k: v[0] / steps for k, v in prof.items()}
-    phases.update({f"nccl_{k}": v / steps for k, v in coll.items()})
+    phases.update({f"comm_{k}": v / steps for k, v in coll.items()})
     del step
     torch.cuda.empty_cache()
     barrier()
@@ -306,7 +306,9 @@ def seq_parallel_record(pkg, dmod, cabi, args, dev, rank, world, barrier):
             "ms_per_step": ms, "value": full.tokens / (ms * 1e-3), "unit": "tokens/s", "steps": steps,
             "one_gpu_segmented": one_gpu,
             "segments_per_rank": dmod.pick_segments(cfg.batch, cfg.nheads, cfg.seqlen),
-            "exchange": "1 all_gather (forward) + 1 all_gather + 1 all_reduce (backward) per step, on a side stream",
+            "exchange": "1 gather of one state per rank (forward) + 1 gather + 1 small all_reduce (backward) per step; gathers by "
+                        + comm_kind,
+            "exchange_status": comm.status() if hasattr(comm, "status") else 0,
             "phase_ms_per_step": phases}
 
 
@@ -324,6 +326,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-seq-parallel", action="store_true", help="N > 1: skip the sequence-split sub-record")
+    ap.add_argument("--nccl-exchange", action="store_true", help="sequence split: gather the summaries with NCCL instead of peer stores")
     ap.add_argument("--op", default="scan", choices=["scan", "elementwise"],
                     help="elementwise: time the rotation and trapezoidal-coefficient operators instead of the scan")
     args = ap.parse_args()

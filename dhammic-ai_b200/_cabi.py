@@ -18,7 +18,7 @@ BWD_DINIT_ONLY = 1
 EXPORTS = (
     "ssd_b200_abi_version", "ssd_b200_last_error", "ssd_b200_workspace_bytes", "ssd_b200_states_bytes",
     "ssd_b200_resolve_path",
-    "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix_all",
+    "ssd_b200_fwd", "ssd_b200_bwd", "ssd_b200_materialize_cache", "ssd_b200_state_prefix_all", "ssd_b200_ipc_export", "ssd_b200_ipc_import", "ssd_b200_ipc_close", "ssd_b200_enable_peer_access", "ssd_b200_exchange_push", "ssd_b200_exchange_arrive",
     "ssd_b200_m3_prologue_fwd", "ssd_b200_m3_skip_fwd", "ssd_b200_m3_prologue_bwd", "ssd_b200_m3_chain_ws_floats", "ssd_b200_m3_chain_bwd", "ssd_b200_rope_fwd", "ssd_b200_rope_bwd",
     "ssd_b200_trapezoid_ws_floats", "ssd_b200_trapezoid_fwd", "ssd_b200_trapezoid_bwd",
     "ssd_b200_rmsnorm_ws_floats", "ssd_b200_rmsnorm_fwd", "ssd_b200_rmsnorm_fwd_presummed", "ssd_b200_rmsnorm_bwd", "ssd_b200_fwd_static_scratch", "ssd_b200_static_scratch_bytes", "ssd_b200_device_status", "ssd_b200_selftest_bounded_wait",
@@ -85,6 +85,18 @@ def load() -> C.CDLL:
                                                C.c_void_p]
     lib.ssd_b200_state_prefix_all.restype = C.c_int
     lib.ssd_b200_state_prefix_all.argtypes = [C.c_void_p] * 6 + [C.c_int64] * 8 + [C.c_int32, C.c_void_p]
+    lib.ssd_b200_ipc_export.restype = C.c_int
+    lib.ssd_b200_ipc_export.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+    lib.ssd_b200_ipc_import.restype = C.c_int
+    lib.ssd_b200_ipc_import.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    lib.ssd_b200_ipc_close.restype = C.c_int
+    lib.ssd_b200_ipc_close.argtypes = [C.c_void_p]
+    lib.ssd_b200_enable_peer_access.restype = C.c_int
+    lib.ssd_b200_enable_peer_access.argtypes = [C.c_int32]
+    lib.ssd_b200_exchange_push.restype = C.c_int
+    lib.ssd_b200_exchange_push.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    lib.ssd_b200_exchange_arrive.restype = C.c_int
+    lib.ssd_b200_exchange_arrive.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     lib.ssd_b200_m3_prologue_fwd.restype = C.c_int
     lib.ssd_b200_m3_prologue_fwd.argtypes = [C.POINTER(Shape)] + [C.c_void_p] * 7 + [C.c_int32] + [C.c_void_p] * 11
     lib.ssd_b200_rope_fwd.restype = C.c_int

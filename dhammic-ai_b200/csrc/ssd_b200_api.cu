@@ -20,7 +20,7 @@ namespace prof {
 const char* const kNames[K_COUNT] = {
     "chunk_cumsum", "chunk_state", "state_passing", "chunk_scan", "chunk_dstate", "state_passing_rev",
     "bwd_row", "bwd_col", "decay_grad", "reduce_batch", "cache_L", "cache_decay_chunk", "state_prefix",
-    "tc_fwd_walk", "tc_bwd_state", "tc_bwd_walk", "tc_aux", "tc_summary", "tc_bwd_walk_alt", "tc_fwd_walk_alt"};
+    "tc_fwd_walk", "tc_bwd_state", "tc_bwd_walk", "tc_aux", "tc_summary", "tc_bwd_walk_alt", "tc_fwd_walk_alt", "exchange"};
 std::atomic<long long> g_launches{0};
 bool g_enabled = false;
 struct Rec {
@@ -863,6 +863,101 @@ int ssd_b200_materialize_cache(const ssd_b200_shape* shape, const float* a_cumsu
             SSD_LAUNCH(ssd::prof::K_CACHE_DC, st, ssd::simt::cache_decay_chunk_kernel<<<g, 128, 0, st>>>(a_cumsum, (float*)decay_chunk, d.c, d.l));
         CUDA_LAUNCH_CHECK("cache_decay_chunk");
     }
+    return 0;
+}
+
+// CUDA IPC of a device buffer between the processes of one node.  The importing side opens the handle with ITS OWN
+// device current and cudaIpcMemLazyEnablePeerAccess, which is what makes the mapping usable by kernels of that device
+// when the memory lives on another GPU.
+int ssd_b200_ipc_export(const void* ptr, unsigned char* handle64, int64_t* offset) {
+    if (!ptr || !handle64 || !offset) return fail(SSD_B200_EINVAL, "null pointer");
+    typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static RangeFn range = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &q) != cudaSuccess) f = nullptr;
+        return (RangeFn)f;
+    }();
+    if (!range) return fail(SSD_B200_ECUDA, "cuMemGetAddressRange is not available");
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (range(&base, &size, (CUdeviceptr)ptr) != CUDA_SUCCESS) return fail(SSD_B200_ECUDA, "cuMemGetAddressRange failed");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, (void*)base);
+    if (e != cudaSuccess) return fail(SSD_B200_ECUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    memcpy(handle64, &h, 64);
+    *offset = (int64_t)((CUdeviceptr)ptr - base);
+    return 0;
+}
+
+int ssd_b200_ipc_import(const unsigned char* handle64, void** base_out) {
+    if (!handle64 || !base_out) return fail(SSD_B200_EINVAL, "null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(SSD_B200_ECUDA, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+    }
+    unsigned int probe = 0;  // a copy through the runtime fails with an error code (not a fault) if the mapping is unusable
+    e = cudaMemcpy(&probe, p, sizeof(probe), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        cudaIpcCloseMemHandle(p);
+        return fail(SSD_B200_ECUDA, "imported memory is not readable from this device: %s", cudaGetErrorString(e));
+    }
+    *base_out = p;
+    return 0;
+}
+
+int ssd_b200_ipc_close(void* base) {
+    if (!base) return 0;
+    cudaError_t e = cudaIpcCloseMemHandle(base);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(SSD_B200_ECUDA, "cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+int ssd_b200_enable_peer_access(int32_t peer_device) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(SSD_B200_ECUDA, "cudaGetDevice failed");
+    if (peer_device == dev) return 0;
+    int can = 0;
+    cudaError_t e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+    if (e != cudaSuccess || !can) return fail(SSD_B200_EUNSUPPORTED, "device %d cannot access device %d as a peer", dev, peer_device);
+    e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();  // clear the sticky-less error state
+        return 0;
+    }
+    if (e != cudaSuccess) return fail(SSD_B200_ECUDA, "cudaDeviceEnablePeerAccess(%d): %s", peer_device, cudaGetErrorString(e));
+    return 0;
+}
+
+int ssd_b200_exchange_push(const float* src, int64_t n, float* const* peer_bufs, int64_t nranks, int64_t dst_offset,
+                           void* stream) {
+    if (!src || !peer_bufs) return fail(SSD_B200_EINVAL, "null pointer");
+    if (n <= 0 || n % 4 || nranks <= 0 || nranks > 32 || dst_offset < 0 || dst_offset % 4 || ((uintptr_t)src & 15))
+        return fail(SSD_B200_EINVAL, "exchange_push: sizes and offsets must be positive multiples of 4 floats, src 16-byte aligned");
+    const size_t n4 = (size_t)n / 4;
+    cudaStream_t st = (cudaStream_t)stream;
+    SSD_LAUNCH(ssd::prof::K_EXCHANGE, st, ssd::simt::exchange_push_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
+        (const float4*)src, n4, peer_bufs, (int)nranks, (size_t)dst_offset));
+    CUDA_LAUNCH_CHECK("exchange_push");
+    return 0;
+}
+
+int ssd_b200_exchange_arrive(unsigned int* const* peer_flags, int64_t rank, int64_t nranks, uint32_t epoch, int32_t* status,
+                             uint32_t max_polls, void* stream) {
+    if (!peer_flags || !status) return fail(SSD_B200_EINVAL, "null pointer");
+    if (nranks <= 0 || nranks > 32 || rank < 0 || rank >= nranks || max_polls == 0) return fail(SSD_B200_EINVAL, "bad exchange_arrive arguments");
+    cudaStream_t st = (cudaStream_t)stream;
+    SSD_LAUNCH(ssd::prof::K_EXCHANGE, st, ssd::simt::exchange_arrive_kernel<<<1, 32, 0, st>>>(peer_flags, (int)rank, (int)nranks, epoch, status, max_polls));
+    CUDA_LAUNCH_CHECK("exchange_arrive");
     return 0;
 }
 

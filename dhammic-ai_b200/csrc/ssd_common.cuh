@@ -36,7 +36,7 @@ namespace prof {
 enum Kernel {
     K_CUMSUM = 0, K_CHUNK_STATE, K_STATE_PASS, K_CHUNK_SCAN, K_CHUNK_DSTATE, K_STATE_PASS_REV, K_BWD_ROW, K_BWD_COL,
     K_DECAY, K_REDUCE, K_CACHE_L, K_CACHE_DC, K_PREFIX, K_TC_FWD, K_TC_BWD_STATE, K_TC_BWD, K_TC_AUX, K_TC_SUMMARY,
-    K_TC_BWD_ALT, K_TC_FWD_ALT, K_COUNT
+    K_TC_BWD_ALT, K_TC_FWD_ALT, K_EXCHANGE, K_COUNT
 };
 void begin(int k, cudaStream_t st);
 void end(cudaStream_t st);

@@ -842,6 +842,43 @@ __global__ void state_prefix_all_kernel(const float* __restrict__ pieces, const 
     if (total_logp && e == 0) total_logp[m] = lsum;
 }
 
+// ------------------------------------------------------------------------------------------
+// Exchange of the per-rank summaries by direct stores into the other GPUs' memory (NVLink peer access), for the
+// sequence-parallel schedule: every rank owns a receive buffer with one slot per source rank and a row of arrival
+// counters; `bufs[q]` / `flags[q]` are rank q's buffer and counters as mapped into this process.
+//
+// push:    copy the local block into slot `rank` of every rank's buffer (plain 16-byte stores; own buffer included).
+// arrive:  one thread per peer: after a system-wide fence (the push kernel before it on the stream has completed, so
+//          its stores are performed), store this step's epoch into counter `rank` of peer q, then wait until peer q's
+//          epoch shows up in the local counter q.  The wait is bounded; when it runs out the kernel records it in
+//          `status` and returns (the gathered data is then invalid, nothing hangs).
+__global__ void __launch_bounds__(256) exchange_push_kernel(const float4* __restrict__ src, size_t n4, float* const* bufs, int R,
+                                                            size_t dst_offset) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const float4 v = src[i];
+    for (int q = 0; q < R; ++q) reinterpret_cast<float4*>(bufs[q] + dst_offset)[i] = v;
+}
+
+__global__ void __launch_bounds__(32) exchange_arrive_kernel(unsigned int* const* flags, int rank, int R, unsigned int epoch,
+                                                             int* status, unsigned int max_polls) {
+    const int q = threadIdx.x;
+    if (q >= R) return;
+    __threadfence_system();
+    volatile unsigned int* theirs = flags[q] + rank;
+    *theirs = epoch;
+    __threadfence_system();
+    volatile unsigned int* mine = flags[rank] + q;
+    bool ok = false;
+    for (unsigned int i = 0; i < max_polls; ++i) {
+        // epochs only grow; a later one means the peer is already a step ahead, which also covers this step
+        if ((int)(*mine - epoch) >= 0) { ok = true; break; }
+        __nanosleep(64);
+    }
+    if (!ok) atomicExch(status, 3);
+    __threadfence_system();
+}
+
 // Total log-decay of every (batch, head) sequence from the within-chunk cumulative sums: sum of the chunks' last entries.
 __global__ void logdecay_total_kernel(const float* __restrict__ cum, float* __restrict__ out, int bh, int c, int l) {
     const int m = blockIdx.x * blockDim.x + threadIdx.x;

@@ -120,6 +120,117 @@ class TorchDistComm:
             torch.cuda.current_stream().wait_event(handle)
 
 
+class PeerStoreComm(TorchDistComm):
+    """all_gather of the per-rank summaries by direct stores into the other GPUs' memory over NVLink, one process per
+    GPU on one node.  Every rank allocates a receive buffer (one slot per source rank, two buffers used alternately)
+    and a row of arrival counters, shares them with the other processes through CUDA IPC (the handles travel
+    through the process group once per buffer size; every process opens them with its own device as the accessor)
+    and keeps the peers' mappings.  An
+    exchange is two small launches of the library on the current stream: ``ssd_b200_exchange_push`` stores the
+    block into every rank's slot, ``ssd_b200_exchange_arrive`` signals the peers and waits (bounded) for theirs.
+    What was received is then read from this GPU's own memory.  No TMA, no multicast, no NCCL kernel on this path;
+    the small all_reduce of the parameter gradients stays on the process group.
+
+    ``status()`` must be checked by the caller where it matters: a wait that ran out leaves 3 there."""
+
+    MAX_POLLS = 1 << 25
+
+    def __init__(self, group=None):
+        super().__init__(group)
+        self._bufs = {}      # block size -> dict of tensors
+        self._imported = {}  # IPC handle bytes -> base address of the peer allocation as mapped into this process
+        self._epoch = 0
+        self._dev = torch.device("cuda", torch.cuda.current_device())
+        self._status = torch.zeros(1, dtype=torch.int32, device=self._dev)
+
+    def _setup(self, n: int) -> dict:
+        # one allocation per block size: [2 buffers][world slots][n floats] followed by [2][world] arrival counters
+        nbuf = 2 * self.world * n
+        mem = torch.zeros(nbuf + 2 * self.world, dtype=torch.float32, device=self._dev)
+        torch.cuda.synchronize(self._dev)
+        lib = _cabi.load()
+        handle = (C.c_ubyte * 64)()
+        off = C.c_int64(0)
+        why = ""
+        try:
+            _cabi.check(lib.ssd_b200_ipc_export(_op._ptr(mem), handle, C.byref(off)))
+        except Exception as e:
+            why = f"{type(e).__name__}: {e}"
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, (bytes(handle), int(off.value), self._dev.index, why), group=self.group)
+        bases = []   # float32 base address of every rank's allocation as mapped here
+        if not any(w for _, _, _, w in everyone):
+            try:
+                with torch.cuda.device(self._dev):   # the accessor is THIS device
+                    for q, (hb, ofs, _, _) in enumerate(everyone):
+                        if q == self.rank:
+                            bases.append(mem.data_ptr())
+                            continue
+                        base = self._imported.get(hb)
+                        if base is None:   # an allocation is opened once per process
+                            out = C.c_void_p()
+                            _cabi.check(lib.ssd_b200_ipc_import(hb, C.byref(out)))
+                            base = self._imported[hb] = int(out.value)
+                        bases.append(base + ofs)
+            except Exception as e:   # reported to every rank below, so that all of them give up together
+                why = f"{type(e).__name__}: {e}"
+        else:
+            why = "; ".join(w for _, _, _, w in everyone if w)
+        ok = torch.tensor([0 if why else 1], device=self._dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)   # also: nobody stores before everyone has mapped
+        if int(ok.item()) == 0:
+            raise RuntimeError("the ranks of this group cannot map each other's device memory" + (f" ({why})" if why else ""))
+        ptr_b = torch.tensor(bases, dtype=torch.int64, device=self._dev)
+        ptr_f = ptr_b + 4 * nbuf
+        return {"mem": mem, "buf": mem[:nbuf], "ptr_b": ptr_b,
+                "ptr_f": (ptr_f, ptr_f + 4 * self.world),   # the two rows of counters (one per buffer parity) of every rank
+                "epoch": 0}
+
+    def all_gather(self, flat: Tensor):
+        if not flat.is_cuda:
+            return super().all_gather(flat)
+        if flat.dim() != 1 or not flat.is_contiguous() or flat.dtype != torch.float32 or flat.numel() % 4:
+            raise ValueError("the peer-store exchange takes a flat contiguous fp32 buffer of a multiple of 4 elements")
+        n = flat.numel()
+        st = self._bufs.get(n)
+        if st is None:
+            st = self._bufs[n] = self._setup(n)
+        lib = _cabi.load()
+        st["epoch"] += 1
+        epoch, par = st["epoch"], st["epoch"] & 1
+        stream = _op._stream(self._dev)
+        rec = self.timings is not None
+        if rec:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        _cabi.check(lib.ssd_b200_exchange_push(_op._ptr(flat), n, _op._ptr(st["ptr_b"]), self.world,
+                                               (par * self.world + self.rank) * n, stream))
+        _cabi.check(lib.ssd_b200_exchange_arrive(_op._ptr(st["ptr_f"][par]), self.rank, self.world, epoch,
+                                                 _op._ptr(self._status), self.MAX_POLLS, stream))
+        if rec:
+            e1.record()
+            self.timings.append(("peer_store_gather", e0, e1))
+        return st["buf"][par * self.world * n:(par + 1) * self.world * n], None
+
+    def status(self) -> int:
+        """0, or 3 when a bounded wait for a peer ran out since the start (synchronises)."""
+        return int(self._status.item())
+
+
+def make_comm(group=None, prefer_peer_stores: bool = True):
+    """The communicator of the sequence-parallel schedule on GPUs: direct peer stores when the ranks of the group can
+    map each other's memory (one node, CUDA IPC), otherwise the process group's collectives.  Returns
+    (communicator, description)."""
+    if prefer_peer_stores and torch.cuda.is_available() and dist.get_backend(group) == "nccl":
+        try:   # mapping is agreed on by all ranks: either every rank gets the communicator or every rank gets the exception
+            comm = PeerStoreComm(group)
+            comm.all_gather(torch.zeros(4, dtype=torch.float32, device=comm._dev))
+            return comm, "direct stores into the peers' buffers over NVLink (CUDA IPC mappings), bounded arrival wait"
+        except RuntimeError as e:
+            return TorchDistComm(group), f"process-group collectives ({e})"
+    return TorchDistComm(group), "process-group collectives"
+
+
 def allreduce_head_grads(dA_head: Tensor, dD: Tensor | None, group=None) -> None:
     """Sum the per-head parameter gradients over the ranks of a batch- or sequence-sharded group."""
     dist.all_reduce(dA_head, op=dist.ReduceOp.SUM, group=group)

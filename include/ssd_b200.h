@@ -268,6 +268,35 @@ int ssd_b200_state_prefix_all(const float *pieces, const float *logp, const floa
                               int32_t reverse, void *stream);
 
 /*
+ * Exchange of the per-rank summaries by direct stores into the other GPUs' memory over NVLink peer access (no
+ * counterpart in the reference; an alternative to an NCCL all_gather for the 2 MiB blocks above, whose cost is
+ * latency).  Every rank owns a receive buffer of nranks slots and a row of nranks arrival counters (uint32, zero at
+ * start); peer_bufs[q] / peer_flags[q] are DEVICE arrays holding rank q's buffer and counters as mapped into this
+ * process (entry `rank` = the own ones).  The host side that allocates, maps (CUDA IPC) and owns them is
+ * dhammic-ai_b200/distributed.py (PeerStoreComm).
+ *   exchange_push:   copies src[0, n) into every rank's buffer at float offset dst_offset (n, dst_offset multiples
+ *                    of 4; src 16-byte aligned) with plain stores -- no TMA, no multicast.
+ *   exchange_arrive: (after the push, same stream) stores `epoch` into counter `rank` of every peer and waits until
+ *                    every peer's counter here has reached `epoch` (epochs grow by one per exchange).  The wait polls
+ *                    at most max_polls times per peer; if it runs out, *status (device memory) is set to 3 and the
+ *                    kernel returns -- nothing hangs, the gathered data is invalid and the host must check status.
+ */
+/* CUDA IPC plumbing for the buffers above (host-side, no kernels).  export: the 64-byte handle of the allocation that
+ * contains `ptr` and ptr's byte offset inside it.  import: maps that allocation into this process with the CURRENT
+ * device as the accessor (peer access to the owning GPU is enabled as part of the open) and returns its base; the
+ * same allocation must be imported once per process.  close: unmaps. */
+int ssd_b200_ipc_export(const void *ptr, unsigned char *handle64, int64_t *offset);
+int ssd_b200_ipc_import(const unsigned char *handle64, void **base_out);
+int ssd_b200_ipc_close(void *base);
+/* Lets kernels of the current device access memory of `peer_device` (cudaDeviceEnablePeerAccess; already enabled is
+ * fine).  SSD_B200_EUNSUPPORTED when the two devices are not peers. */
+int ssd_b200_enable_peer_access(int32_t peer_device);
+int ssd_b200_exchange_push(const float *src, int64_t n, float *const *peer_bufs, int64_t nranks, int64_t dst_offset,
+                           void *stream);
+int ssd_b200_exchange_arrive(unsigned int *const *peer_flags, int64_t rank, int64_t nranks, uint32_t epoch,
+                             int32_t *status, uint32_t max_polls, void *stream);
+
+/*
  * Element-wise kernels of the Mamba-3 style variant (no counterpart in the reference's operator file: its
  * block does these steps with tensor arithmetic, src/mamba_base_engine.py:128-187).  The block's two scan
  * calls  SSD(x gamma, a, Br, Cr) + SSD(shift(x) beta, a, shift(Br), Cr)  collapse into ONE scan
