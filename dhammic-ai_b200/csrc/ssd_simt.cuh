@@ -807,7 +807,7 @@ __global__ void cache_decay_chunk_kernel(const float* cum, T* dc, int c, int l) 
 // `edge` (b, h, pn) or null: the state before the first piece / the gradient behind the last one.  `total` (b, h, pn)
 // or null receives acc after the last of rank's pieces has been folded in (the summary of everything walked so far)
 // and `total_logp` (b, h) or null the sum of the log-decays of rank's own S pieces.
-__global__ void state_prefix_all_kernel(const float* __restrict__ pieces, const float* __restrict__ logp,
+__global__ void __launch_bounds__(256) state_prefix_all_kernel(const float* __restrict__ pieces, const float* __restrict__ logp,
                                         const float* __restrict__ edge, float* __restrict__ out, float* __restrict__ total,
                                         float* __restrict__ total_logp, int R, int rank, int S, int h, size_t pn,
                                         size_t rank_stride, size_t logp_stride, int reverse) {
@@ -819,23 +819,34 @@ __global__ void state_prefix_all_kernel(const float* __restrict__ pieces, const 
     const int lo = rank * S, hi = lo + S;
     auto rec = [&](int g) { return ((size_t)bb * S + (g % S)) * h + hh; };  // (b, S, h) record of piece g inside its rank's block
     float lsum = 0.f;
-    if (!reverse) {
-#pragma unroll 4
-        for (int g = 0; g < hi; ++g) {
-            if (g >= lo && out) out[rec(g) * pn + e] = acc;
-            const size_t r = (size_t)(g / S);
-            const float lp = logp[r * logp_stride + rec(g)];
-            if (g >= lo) lsum += lp;
-            acc = __expf(lp) * acc + pieces[r * rank_stride + rec(g) * pn + e];
+    // pieces walked: forward 0 .. hi-1, reverse R S - 1 .. lo; piece of step i
+    const int steps = reverse ? R * S - lo : hi;
+    auto piece_of = [&](int i) { return reverse ? R * S - 1 - i : i; };
+    // The recurrence is a chain of dependent multiply-adds, but its operands are not: they are fetched a batch at a
+    // time (eight loads in flight per thread) before the chain consumes them.
+    constexpr int BATCH = 8;
+    for (int i0 = 0; i0 < steps; i0 += BATCH) {
+        float v[BATCH], lp[BATCH];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+            const int i = i0 + j;
+            if (i < steps) {
+                const int g = piece_of(i);
+                const size_t r = (size_t)(g / S);
+                lp[j] = logp[r * logp_stride + rec(g)];
+                v[j] = pieces[r * rank_stride + rec(g) * pn + e];
+            }
         }
-    } else {
-#pragma unroll 4
-        for (int g = R * S - 1; g >= lo; --g) {
-            if (g < hi && out) out[rec(g) * pn + e] = acc;
-            const size_t r = (size_t)(g / S);
-            const float lp = logp[r * logp_stride + rec(g)];
-            if (g < hi) lsum += lp;
-            acc = __expf(lp) * acc + pieces[r * rank_stride + rec(g) * pn + e];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+            const int i = i0 + j;
+            if (i < steps) {
+                const int g = piece_of(i);
+                const bool own = g >= lo && g < hi;
+                if (own && out) out[rec(g) * pn + e] = acc;
+                if (own) lsum += lp[j];
+                acc = __expf(lp[j]) * acc + v[j];
+            }
         }
     }
     if (total) total[(size_t)m * pn + e] = acc;
