@@ -325,6 +325,7 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tc"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--micro-batches", type=int, default=8, help="e2e: micro-batches of the host pipeline")
     ap.add_argument("--no-seq-parallel", action="store_true", help="N > 1: skip the sequence-split sub-record")
     ap.add_argument("--nccl-exchange", action="store_true", help="sequence split: gather the summaries with NCCL instead of peer stores")
     ap.add_argument("--op", default="scan", choices=["scan", "elementwise"],
@@ -467,7 +468,7 @@ def main():
                 runner.run(pinned, out_host, cfg.chunk)
         elif not plain:
             # the package's host-buffer entry: micro-batches, copies overlapped with the kernels on three streams
-            pipe = pkg.HostPipeline(dev, micro_batches=8)
+            pipe = pkg.HostPipeline(dev, micro_batches=args.micro_batches)
             out_host = pkg.HostPipeline.alloc_outputs(pinned)
 
             def step_e2e():
@@ -503,7 +504,7 @@ def main():
         e2e = {"value": tokens_all * e2e_steps / (float(t2.item()) * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                "api": ("SequenceStreamer.run (16384-position slices, state carried across)" if streamed else
-                       "HostPipeline.run (8 micro-batches, 3 streams)" if not plain else "operator call on pinned buffers")}
+                       f"HostPipeline.run ({args.micro_batches} micro-batches, 3 streams)" if not plain else "operator call on pinned buffers")}
 
     # N > 1: the long-context configuration, whose sequence is split over the ranks (the only one with a collective
     # on the data path), rides along as a sub-record; `value` stays the batch-sharded configuration

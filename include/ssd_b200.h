@@ -87,6 +87,8 @@ typedef struct ssd_b200_shape {
  *       single-scan form needs, src/mamba_base_engine.py:170-187, without materialising x * weight).
  *
  *   x (b,T,h,p)  B,C (b,T,g,n)  init (b,h,p,n) fp32 or NULL  ->  y (b,T,h,p), final_state (b,h,p,n) fp32
+ *   Log-decays are expected to be <= 0 (the reference's parametrisation, A = -exp(.), guarantees it); the kernels
+ *   do not clamp positive values the way the reference's exp-clamp does at +20.
  *   a_cumsum (b,h,c,l) fp32: within-chunk inclusive cumulative log-decay; written unless
  *   cumsum_is_input != 0, in which case it is read as given (the reference's cached call,
  *   src/kernels/ssd_scan.py:364-373).

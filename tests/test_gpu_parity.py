@@ -409,3 +409,26 @@ def test_scan_with_gated_norm_output_stage(pkg, cabi, oracle, idx, batch, seqlen
     y2, _ = pkg.ssd_mamba2(lv["x"], lv["dt"], lv["A_head"], lv["B"], lv["C"], lv["D"], cfg.chunk)
     o2 = pkg.fused_gate_norm(y2.reshape(b, T, h * p), zl, wl, 1e-6).reshape(b, T, h, p)
     assert rel_err(out, o2) < (1e-2 if cfg.dtype == "bf16" else 1e-5)
+
+
+def test_scaled_operator_form_matches_mamba2_form(pkg, cabi):
+    """The scan's third calling form (log-decay a, input weight dt and skip coefficient all per position; what the
+    one-scan Mamba-3 composition uses) against the Mamba-2 form with a = dt * A_head and skip = D on the same data:
+    same y, dx, dB, dC, and  ddt = d weight + da * A_head,  dA_head = sum da * dt,  dD = sum dskip."""
+    import importlib
+    S = importlib.import_module("dhammic-ai_b200.ssd_scan")
+    cfg = pkg.shrink(pkg.CONFIGS[2], 2, 512)
+    inp = {k: v.to(DEV) for k, v in pkg.make_inputs(cfg).items()}
+    want = mamba2_gpu(pkg, {k: v.cpu() for k, v in inp.items()}, cfg.chunk)
+    b, T, h, p = inp["x"].shape
+    a = (inp["dt"] * inp["A_head"]).contiguous()
+    skip = inp["D"].expand(b, T, h).contiguous()
+    y, final, cum, shape, states = S._run_fwd(inp["x"], a, inp["dt"], None, None, inp["B"], inp["C"], cfg.chunk, None, None,
+                                             want_states=True, skip=skip)
+    dx, da, dw, dskip, dB, dC = S._run_bwd_scaled(shape, inp["x"], a, inp["dt"], skip, inp["B"], inp["C"], cum, inp["dy"], states)
+    torch.cuda.synchronize()
+    got = {"y": y, "final_state": final, "dx": dx, "dB": dB, "dC": dC,
+           "ddt": dw + da * inp["A_head"], "dA_head": (da * inp["dt"]).sum((0, 1)), "dD": dskip.sum((0, 1))}
+    errs = {k: rel_err(got[k], want[k]) for k in got}
+    bad = {k: v for k, v in errs.items() if not v < 1e-3}   # same kernels, same roundings up to the order of the sums
+    assert not bad, errs
