@@ -13,6 +13,7 @@ PASS_FWD, PASS_BWD = 0, 1
 PATH_AUTO, PATH_SIMT, PATH_TC = 0, 1, 2
 OK, EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA, EDEVICE = 0, -1, -2, -3, -4, -5
 FWD_STATES_ONLY = 1
+FWD_AUX_VALID = 2
 BWD_DINIT_ONLY = 1
 
 EXPORTS = (
@@ -84,7 +85,8 @@ def load() -> C.CDLL:
     lib.ssd_b200_materialize_cache.argtypes = [C.POINTER(Shape), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                                C.c_void_p]
     lib.ssd_b200_state_prefix_all.restype = C.c_int
-    lib.ssd_b200_state_prefix_all.argtypes = [C.c_void_p] * 6 + [C.c_int64] * 8 + [C.c_int32, C.c_void_p]
+    lib.ssd_b200_state_prefix_all.argtypes = ([C.c_void_p] * 6 + [C.c_int64] * 8 + [C.c_int32] + [C.c_void_p] * 2 + [C.c_int64] * 4
+                                              + [C.c_void_p])
     lib.ssd_b200_ipc_export.restype = C.c_int
     lib.ssd_b200_ipc_export.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
     lib.ssd_b200_ipc_import.restype = C.c_int

@@ -964,18 +964,23 @@ int ssd_b200_exchange_arrive(unsigned int* const* peer_flags, int64_t rank, int6
 int ssd_b200_state_prefix_all(const float* pieces, const float* logp, const float* edge, float* out, float* total,
                               float* total_logp, int64_t nranks, int64_t rank, int64_t segments, int64_t batch,
                               int64_t nheads, int64_t state_elems, int64_t rank_stride, int64_t logp_stride, int32_t reverse,
-                              void* stream) {
+                              const float* outer, const float* outer_logp, int64_t outer_n, int64_t outer_rank,
+                              int64_t outer_stride, int64_t outer_logp_stride, void* stream) {
     if (!pieces || !logp || (!out && !total)) return fail(SSD_B200_EINVAL, "null pointer");
     if (nranks <= 0 || rank < 0 || rank >= nranks || segments <= 0 || batch <= 0 || nheads <= 0 || state_elems <= 0 ||
         batch * nheads > 65535 || nranks * segments > 2147483647LL)
         return fail(SSD_B200_EINVAL, "bad state_prefix_all dimensions");
     if (rank_stride < batch * segments * nheads * state_elems || logp_stride < batch * segments * nheads)
         return fail(SSD_B200_EINVAL, "state_prefix_all: a rank's block is smaller than its (b, S, h) records");
+    if (outer && (!outer_logp || outer_n <= 0 || outer_n > 65535 || outer_rank < 0 || outer_rank >= outer_n ||
+                  outer_stride < batch * nheads * state_elems || outer_logp_stride < batch * nheads))
+        return fail(SSD_B200_EINVAL, "state_prefix_all: bad outer (per-rank) summaries");
     dim3 g((unsigned)((state_elems + 255) / 256), (unsigned)(batch * nheads));
     cudaStream_t st = (cudaStream_t)stream;
     SSD_LAUNCH(ssd::prof::K_PREFIX, st, ssd::simt::state_prefix_all_kernel<<<g, 256, 0, st>>>(
         pieces, logp, edge, out, total, total_logp, (int)nranks, (int)rank, (int)segments, (int)nheads, (size_t)state_elems,
-        (size_t)rank_stride, (size_t)logp_stride, reverse));
+        (size_t)rank_stride, (size_t)logp_stride, reverse, outer, outer_logp, (int)outer_n, (int)outer_rank,
+        (size_t)outer_stride, (size_t)outer_logp_stride));
     CUDA_LAUNCH_CHECK("state_prefix_all");
     return 0;
 }

@@ -804,18 +804,31 @@ __global__ void cache_decay_chunk_kernel(const float* cum, T* dc, int c, int l) 
 // leaving it (reverse) into out (b, S, h, pn); every piece is read once:
 //     forward   acc = edge;  for g = 0 ..        : out[g] = acc;  acc = exp(logp[g]) acc + pieces[g]
 //     reverse   acc = edge;  for g = R S - 1 .. : out[g] = acc;  acc = exp(logp[g]) acc + pieces[g]
-// `edge` (b, h, pn) or null: the state before the first piece / the gradient behind the last one.  `total` (b, h, pn)
+// `edge` (b, h, pn) or null: the state before the first piece / the gradient behind the last one.  With `outer` given the
+// walk is preceded by the slice summaries of the other ranks (one per rank, `outer_n` of them, this rank at `outer_rank`),
+// so that the rank-level and the segment-level prefix of the sequence split are one launch.  `total` (b, h, pn)
 // or null receives acc after the last of rank's pieces has been folded in (the summary of everything walked so far)
 // and `total_logp` (b, h) or null the sum of the log-decays of rank's own S pieces.
 __global__ void __launch_bounds__(256) state_prefix_all_kernel(const float* __restrict__ pieces, const float* __restrict__ logp,
                                         const float* __restrict__ edge, float* __restrict__ out, float* __restrict__ total,
                                         float* __restrict__ total_logp, int R, int rank, int S, int h, size_t pn,
-                                        size_t rank_stride, size_t logp_stride, int reverse) {
+                                        size_t rank_stride, size_t logp_stride, int reverse,
+                                        const float* __restrict__ outer, const float* __restrict__ outer_logp, int outer_n,
+                                        int outer_rank, size_t outer_stride, size_t outer_logp_stride) {
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int m = blockIdx.y;  // (b,h)
     if (e >= pn) return;
     const int bb = m / h, hh = m - bb * h;
     float acc = edge ? edge[(size_t)m * pn + e] : 0.f;
+    if (outer) {
+        // first the summaries of the other ranks' whole slices (one (b, h, pn) block and one (b, h) log-decay per rank):
+        // forward those before `outer_rank`, reverse those behind it; `edge` lies beyond all of them
+        const int n = reverse ? outer_n - 1 - outer_rank : outer_rank;
+        for (int i = 0; i < n; ++i) {
+            const size_t q = (size_t)(reverse ? outer_n - 1 - i : i);
+            acc = __expf(outer_logp[q * outer_logp_stride + m]) * acc + outer[q * outer_stride + (size_t)m * pn + e];
+        }
+    }
     const int lo = rank * S, hi = lo + S;
     auto rec = [&](int g) { return ((size_t)bb * S + (g % S)) * h + hh; };  // (b, S, h) record of piece g inside its rank's block
     float lsum = 0.f;

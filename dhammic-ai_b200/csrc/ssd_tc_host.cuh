@@ -144,12 +144,14 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     float* dtT = a->dt ? (float*)(ws + w.dtT) : nullptr;
     float* skipT = a->skip ? (float*)(ws + w.skipT) : nullptr;
     int* extreme = status + 1;  // raised by tile_cumsum_kernel (see kMaskSafeLog2)
-    if (a->states && !states_only) {  // kept for the backward call, behind the tile states
+    const bool aux_valid = (a->flags & SSD_B200_FWD_AUX_VALID) != 0;
+    if (aux_valid && !a->states) SSD_TC_FAIL(SSD_B200_EINVAL, "SSD_B200_FWD_AUX_VALID needs the `states` buffer that holds the arrays");
+    if (a->states) {  // the per-position arrays live behind the tile states, kept for later calls on the same inputs
         tcum = (float*)((char*)a->states + tile_states_bytes(d));
         if (a->dt) dtT = tcum + (size_t)d.b * d.h * d.T;
         if (a->skip) skipT = tcum + 2 * (size_t)d.b * d.h * d.T;
         extreme = (int*)(tcum + 3 * (size_t)d.b * d.h * d.T);
-        if (cudaMemsetAsync(extreme, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
+        if (!aux_valid && cudaMemsetAsync(extreme, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     }
     if (cudaMemsetAsync(status, 0, 8, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     if (!a->cumsum_is_input) {
@@ -163,7 +165,8 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
         SSD_LAUNCH(prof::K_CUMSUM, st, simt::chunk_cumsum_kernel<<<dim3(d.c, d.b), simt::NTHR, sm, st>>>(P));
         SSD_TC_CHECK("chunk_cumsum");
     }
-    if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, a->skip, skipT, extreme, st, err, errn)) return rc;
+    if (!aux_valid)
+        if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, a->skip, skipT, extreme, st, err, errn)) return rc;
     if (int rc = set_walk_attrs(err, errn)) return rc;
     WalkParams P{};
     P.skipT = skipT;
@@ -174,7 +177,7 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
               make_map(&P.mC, a->C, rows, (uint64_t)d.g * DN) &&
               make_map(&P.mY, states_only ? a->x : (const void*)a->y, rows, (uint64_t)d.h * HP);
     if (a->states && ((uintptr_t)a->states & 15)) SSD_TC_FAIL(SSD_B200_EINVAL, "`states` must be 16-byte aligned");
-    if (ok && a->states) {
+    if (ok && a->states && !states_only) {
         ok = make_map(&P.mS, a->states, (uint64_t)d.b * (d.T / LT) * d.h * DN, HP);
         P.save_states = 1;
     } else {
@@ -219,7 +222,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
     if (cudaMemsetAsync(status, 0, 8, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     int* extreme = status + 1;
     float* skipT = a->skip ? (float*)(ws + w.skipT) : nullptr;
-    if (a->states && !(a->flags & SSD_B200_BWD_DINIT_ONLY)) {  // the forward left the arrays and the flag behind the tile states
+    if (a->states) {  // the forward left the arrays and the flag behind the tile states
         tcum = (float*)((uintptr_t)a->states + tile_states_bytes(d));
         dtT = a->dt ? tcum + (size_t)d.b * d.h * d.T : nullptr;
         skipT = a->skip ? tcum + 2 * (size_t)d.b * d.h * d.T : nullptr;

@@ -272,17 +272,21 @@ class CudaBackend:
             logp = out_logp if out_logp is not None else torch.empty(b, h, dtype=torch.float32, device=dev)
             cum = torch.empty(b, h, T // s.chunk, s.chunk, dtype=torch.float32, device=dev)
             ws = _op._workspace(lib, shape, _cabi.PASS_FWD, dev)
+            # the buffer the full pass keeps its per-tile states in: this pass already fills its per-position arrays
+            nbytes = int(lib.ssd_b200_states_bytes(C.byref(shape)))
+            states = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
             args = _cabi.FwdArgs(shape, _op._ptr(s.x), None, _op._ptr(s.dt), _op._ptr(s.A_head), None, _op._ptr(s.B),
                                  _op._ptr(s.C), None, None, _op._ptr(final), _op._ptr(cum), 0, _cabi.FWD_STATES_ONLY,
-                                 _op._ptr(ws), ws.numel(), None, _op._ptr(logp))
+                                 _op._ptr(ws), ws.numel(), _op._ptr(states), _op._ptr(logp))
             _cabi.check(lib.ssd_b200_fwd(C.byref(args), _op._stream(dev)))
             _op._status(lib, shape, ws, dev)
-        return final, logp, cum
+        return final, logp, (cum, states)
 
     def forward(self, s: Slice, init: Tensor | None, cum: Tensor):
-        # the within-chunk cumulative sums of the summary pass are reused, not rebuilt
+        # the cumulative sums and per-position arrays of the summary pass are reused, not rebuilt
+        cum, states = cum
         y, final, cum, shape, states = _op._run_fwd(s.x, None, s.dt, s.A_head, s.D, s.B, s.C, s.chunk, init, cum,
-                                                    want_states=True)
+                                                    want_states=True, states=states, aux_valid=states is not None)
         return y, final, {"cum": cum, "shape": shape, "states": states}
 
     def dinit_only(self, s: Slice, saved: dict, dy: Tensor, dfinal: Tensor | None = None, out: Tensor | None = None) -> Tensor:
@@ -296,7 +300,7 @@ class CudaBackend:
             ws = _op._workspace(lib, shape, _cabi.PASS_BWD, dev)
             args = _cabi.BwdArgs(shape, None, None, None, None, None, None, _op._ptr(s.C), None, _op._ptr(saved["cum"]),
                                  _op._ptr(dy), _op._ptr(dfinal), None, None, None, None, None, None, None,
-                                 _op._ptr(dinit), 0, _cabi.BWD_DINIT_ONLY, _op._ptr(ws), ws.numel(), None)
+                                 _op._ptr(dinit), 0, _cabi.BWD_DINIT_ONLY, _op._ptr(ws), ws.numel(), _op._ptr(saved.get("states")))
             _cabi.check(lib.ssd_b200_bwd(C.byref(args), _op._stream(dev)))
             _op._status(lib, shape, ws, dev)
         return dinit
@@ -322,12 +326,15 @@ class CudaBackend:
             _op._status(lib, shape, ws, dev)
         return out
 
-    def prefix_all(self, pieces: Tensor, logp: Tensor, edge: Tensor | None, rank: int, reverse: bool, total: bool = False):
+    def prefix_all(self, pieces: Tensor, logp: Tensor, edge: Tensor | None, rank: int, reverse: bool, total: bool = False,
+                   outer=None):
         """pieces (R,b,S,h,p,n) and logp (R,b,S,h): summaries and total log-decays of all R*S pieces (rank-major; the
         rank dimension may be strided, the rest dense).  Returns (b*S,h,p,n): for each of rank's S pieces the state
         entering it (forward) or the state gradient leaving it (reverse); ``edge`` (b,h,p,n) is the state before the
         first piece / the gradient behind the last one.  One launch, every piece read once.  With ``total`` it returns
-        instead (fold of everything walked including rank's own pieces (b,h,p,n), sum of rank's log-decays (b,h))."""
+        instead (fold of everything walked including rank's own pieces (b,h,p,n), sum of rank's log-decays (b,h)).
+        ``outer`` = (summaries (W,b,1,h,p,n), log-decays (W,b,1,h), this rank's index): whole-slice summaries of the
+        other ranks, folded in before the walk (those before this rank forward, those behind it reverse)."""
         lib = _cabi.load()
         R, b, S, h, p, n = pieces.shape
         dev = pieces.device
@@ -341,10 +348,17 @@ class CudaBackend:
             else:
                 out = torch.empty(b * S, h, p, n, dtype=torch.float32, device=dev)
                 tot = tlp = None
+            if outer is not None:
+                op, ol, orank = outer
+                assert op[0].is_contiguous() and ol[0].is_contiguous()
+                oargs = (_op._ptr(op), _op._ptr(ol), op.shape[0], orank, op.stride(0) if op.shape[0] > 1 else b * h * p * n,
+                         ol.stride(0) if ol.shape[0] > 1 else b * h)
+            else:
+                oargs = (None, None, 0, 0, 0, 0)
             _cabi.check(lib.ssd_b200_state_prefix_all(
                 _op._ptr(pieces), _op._ptr(logp), _op._ptr(ed), _op._ptr(out), _op._ptr(tot), _op._ptr(tlp), R, rank, S,
                 b, h, p * n, pieces.stride(0) if R > 1 else b * S * h * p * n, logp.stride(0) if R > 1 else b * S * h,
-                1 if reverse else 0, _op._stream(dev)))
+                1 if reverse else 0, *oargs, _op._stream(dev)))
         return (tot, tlp) if total else out
 
 
@@ -404,8 +418,12 @@ class _SeqSplitSSD(torch.autograd.Function):
             G = gathered.view(comm.world, nR + b * h)
             rank_pieces, rank_logp = G[:, :nR].view(comm.world, b, 1, h, p, n), G[:, nR:].view(comm.world, b, 1, h)
             comm.wait(hnd)
-            init_rank = backend.prefix_all(rank_pieces, rank_logp, init_rank, comm.rank, reverse=False)
-        inits = backend.prefix_all(loc_pieces, loc_logp, init_rank, 0, reverse=False)
+            # rank-level and segment-level prefix in one launch: the other ranks' summaries first, then the local segments
+            inits = backend.prefix_all(loc_pieces, loc_logp, init_rank, 0, reverse=False,
+                                       outer=(rank_pieces, rank_logp, comm.rank))
+        else:
+            rank_pieces = None
+            inits = backend.prefix_all(loc_pieces, loc_logp, init_rank, 0, reverse=False)
         y, final, saved = backend.forward(seg, inits, cum)
         ctx.seg, ctx.saved, ctx.inits, ctx.loc_logp, ctx.rank_logp = seg, saved, inits, loc_logp, rank_logp
         ctx.comm, ctx.backend, ctx.S, ctx.dims = comm, backend, S, (b, T, h, p, n, g)
@@ -429,15 +447,15 @@ class _SeqSplitSSD(torch.autograd.Function):
         Dl = torch.empty(b * S * h * p * n, dtype=torch.float32, device=dys.device)
         backend.dinit_only(seg, ctx.saved, dys, seed, Dl.view(b * S, h, p, n))
         loc_pieces = Dl.view(1, b, S, h, p, n)
-        dfin_rank = None
         if comm.world > 1:
             D_rank, _ = backend.prefix_all(loc_pieces, ctx.loc_logp, None, 0, reverse=True, total=True)
             gathered, hnd = comm.all_gather(D_rank.reshape(-1))
             _check_gathered(gathered, comm.world * b * h * p * n)
             comm.wait(hnd)
-            dfin_rank = backend.prefix_all(gathered.view(comm.world, b, 1, h, p, n), ctx.rank_logp, None, comm.rank,
-                                           reverse=True)
-        dfin = backend.prefix_all(loc_pieces, ctx.loc_logp, dfin_rank, 0, reverse=True)
+            dfin = backend.prefix_all(loc_pieces, ctx.loc_logp, None, 0, reverse=True,
+                                      outer=(gathered.view(comm.world, b, 1, h, p, n), ctx.rank_logp, comm.rank))
+        else:
+            dfin = backend.prefix_all(loc_pieces, ctx.loc_logp, None, 0, reverse=True)
         if last:
             dfin.view(b, S, h, p, n)[:, -1] += dfinal_global.float()
         gr = backend.backward(seg, ctx.saved, ctx.inits, dys, dfin)

@@ -160,9 +160,12 @@ class LazySSDCache(dict):
         return dict.get(self, key)
 
 
-def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=False, ysq=None, skip=None):
+def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=False, ysq=None, skip=None, states=None,
+             aux_valid=False):
     """Common forward launcher.  Returns (y, final_state fp32 (b,h,p,n), a_cumsum, shape, states or None).
-    ``ysq``: optional fp32 buffer (b, T/128, h, 2, 128) for the per-half-row sums of y^2 (tensor-core path)."""
+    ``ysq``: optional fp32 buffer (b, T/128, h, 2, 128) for the per-half-row sums of y^2 (tensor-core path).
+    ``states``: a buffer to use instead of allocating one; with ``aux_valid`` its per-position arrays were filled by an
+    earlier call on the same inputs and are reused."""
     lib = _cabi.load()
     b, T, h, p = x.shape
     n = B.shape[3]
@@ -182,13 +185,13 @@ def _run_fwd(x, a, dt, A_head, D, B, Cm, chunk, init4, a_cumsum_in, want_states=
         else:
             cum = torch.empty(b, h, T // chunk, chunk, dtype=torch.float32, device=dev)
         ws = _workspace(lib, shape, _cabi.PASS_FWD, dev)
-        states = None
-        if want_states and _SAVE_STATES:
+        if states is None and want_states and _SAVE_STATES:
             nbytes = lib.ssd_b200_states_bytes(C.byref(shape))
             if nbytes:
                 states = torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
+        flags = _cabi.FWD_AUX_VALID if (aux_valid and states is not None) else 0
         args = _cabi.FwdArgs(shape, _ptr(x), _ptr(a), _ptr(dt), _ptr(A_head), _ptr(D), _ptr(B), _ptr(Cm), _ptr(init4),
-                             _ptr(y), _ptr(final), _ptr(cum), 1 if a_cumsum_in is not None else 0, 0, _ptr(ws),
+                             _ptr(y), _ptr(final), _ptr(cum), 1 if a_cumsum_in is not None else 0, flags, _ptr(ws),
                              ws.numel(), _ptr(states), None, _ptr(ysq), _ptr(skip))
         _cabi.check(lib.ssd_b200_fwd(C.byref(args), _stream(dev)))
         _status(lib, shape, ws, dev)

@@ -60,8 +60,12 @@ enum { SSD_B200_PATH_AUTO = 0, SSD_B200_PATH_SIMT = 1, SSD_B200_PATH_TC = 2 };
  * sequence and only per-rank states cross NVLink):
  *   SSD_B200_FWD_STATES_ONLY  forward: write final_state (and a_cumsum, logdecay_total) only; y may be NULL.
  *   SSD_B200_BWD_DINIT_ONLY   backward: from dy, C, a_cumsum (and dfinal, NULL = zero) alone write dinit, the
- *                             gradient of the initial state; every other output may be NULL. */
-enum { SSD_B200_FWD_STATES_ONLY = 1 };
+ *                             gradient of the initial state; every other output may be NULL.
+ *   SSD_B200_FWD_AUX_VALID    forward, tensor-core path, with `states` given: the per-position arrays in `states` were
+ *                             already written by an earlier forward call on the same dt / a / skip (e.g. the STATES_ONLY
+ *                             pass of the same slice, which takes `states` too and fills only that part) and are
+ *                             reused instead of rebuilt.  Combine with cumsum_is_input to reuse a_cumsum as well. */
+enum { SSD_B200_FWD_STATES_ONLY = 1, SSD_B200_FWD_AUX_VALID = 2 };
 enum { SSD_B200_BWD_DINIT_ONLY = 1 };
 
 typedef struct ssd_b200_shape {
@@ -262,12 +266,17 @@ int ssd_b200_materialize_cache(const ssd_b200_shape *shape, const float *a_cumsu
  * be NULL when only these are wanted): total (batch, h, state_elems) = acc after the last of rank's pieces has been
  * folded in, total_logp (batch, h) = sum of the log-decays of rank's own pieces -- with nranks = 1 these are the
  * summary and log-decay of the rank's whole slice, i.e. what the ranks exchange (one state per rank, not one per
- * segment).
+ * segment).  With `outer` != NULL the walk is preceded by such slice summaries of the other ranks: outer + q *
+ * outer_stride is rank q's (batch, h, state_elems) summary, outer_logp + q * outer_logp_stride its (batch, h)
+ * log-decay, outer_n ranks with this one at outer_rank; forward folds those before it, reverse those behind it, and
+ * `edge` lies beyond all of them.  That makes the rank-level and the segment-level prefix one launch (pass nranks = 1,
+ * rank = 0 and the local segments as `pieces`).
  */
 int ssd_b200_state_prefix_all(const float *pieces, const float *logp, const float *edge, float *out, float *total,
                               float *total_logp, int64_t nranks, int64_t rank, int64_t segments, int64_t batch,
                               int64_t nheads, int64_t state_elems, int64_t rank_stride, int64_t logp_stride,
-                              int32_t reverse, void *stream);
+                              int32_t reverse, const float *outer, const float *outer_logp, int64_t outer_n,
+                              int64_t outer_rank, int64_t outer_stride, int64_t outer_logp_stride, void *stream);
 
 /*
  * Exchange of the per-rank summaries by direct stores into the other GPUs' memory over NVLink peer access (no

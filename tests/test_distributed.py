@@ -38,7 +38,7 @@ class OracleBackend:
         if out_F is not None:
             out_F.copy_(final)
             out_logp.copy_(logp)
-        return final, logp, None
+        return final, logp, (None, None)
 
     def forward(self, s, init, cum):
         with torch.no_grad():
@@ -68,11 +68,16 @@ class OracleBackend:
         out["dinit"] = g[-1]
         return out
 
-    def prefix_all(self, pieces, logp, edge, rank, reverse, total=False):
+    def prefix_all(self, pieces, logp, edge, rank, reverse, total=False, outer=None):
         R, b, S, h, p, n = pieces.shape
         P = pieces.transpose(1, 2).reshape(R * S, b, h, p, n)   # piece-major
         L = logp.transpose(1, 2).reshape(R * S, b, h)
         acc = torch.zeros_like(P[0]) if edge is None else edge.reshape(P[0].shape).to(P.dtype).clone()
+        if outer is not None:   # the other ranks' whole-slice summaries first
+            op, ol, orank = outer
+            W = op.shape[0]
+            for q in (range(W - 1, orank, -1) if reverse else range(orank)):
+                acc = torch.exp(ol[q, :, 0])[..., None, None] * acc + op[q, :, 0]
         out = [None] * S
         order = range(R * S - 1, rank * S - 1, -1) if reverse else range(rank * S + S)
         lsum = torch.zeros_like(L[0])
