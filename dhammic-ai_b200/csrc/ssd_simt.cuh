@@ -830,35 +830,35 @@ __global__ void __launch_bounds__(256) state_prefix_all_kernel(const float* __re
         }
     }
     const int lo = rank * S, hi = lo + S;
-    auto rec = [&](int g) { return ((size_t)bb * S + (g % S)) * h + hh; };  // (b, S, h) record of piece g inside its rank's block
     float lsum = 0.f;
-    // pieces walked: forward 0 .. hi-1, reverse R S - 1 .. lo; piece of step i
+    // pieces walked: forward 0 .. hi-1, reverse R S - 1 .. lo.  (r, sg) = rank and segment of the piece of a step, kept
+    // incrementally (no division in the loop); a piece's (b, S, h) record inside its rank's block is (bb S + sg) h + hh.
     const int steps = reverse ? R * S - lo : hi;
-    auto piece_of = [&](int i) { return reverse ? R * S - 1 - i : i; };
+    const size_t rec0 = (size_t)bb * S * h + hh;
+    int r = reverse ? R - 1 : 0, sg = reverse ? S - 1 : 0;
     // The recurrence is a chain of dependent multiply-adds, but its operands are not: they are fetched a batch at a
     // time (eight loads in flight per thread) before the chain consumes them.
     constexpr int BATCH = 8;
     for (int i0 = 0; i0 < steps; i0 += BATCH) {
         float v[BATCH], lp[BATCH];
+        int rr = r, ss = sg;
 #pragma unroll
         for (int j = 0; j < BATCH; ++j) {
-            const int i = i0 + j;
-            if (i < steps) {
-                const int g = piece_of(i);
-                const size_t r = (size_t)(g / S);
-                lp[j] = logp[r * logp_stride + rec(g)];
-                v[j] = pieces[r * rank_stride + rec(g) * pn + e];
+            if (i0 + j < steps) {
+                const size_t rc = rec0 + (size_t)ss * h;
+                lp[j] = logp[(size_t)rr * logp_stride + rc];
+                v[j] = pieces[(size_t)rr * rank_stride + rc * pn + e];
+                if (reverse) { if (--ss < 0) { ss = S - 1; --rr; } } else { if (++ss == S) { ss = 0; ++rr; } }
             }
         }
 #pragma unroll
         for (int j = 0; j < BATCH; ++j) {
-            const int i = i0 + j;
-            if (i < steps) {
-                const int g = piece_of(i);
-                const bool own = g >= lo && g < hi;
-                if (own && out) out[rec(g) * pn + e] = acc;
+            if (i0 + j < steps) {
+                const bool own = r == rank;
+                if (own && out) out[(rec0 + (size_t)sg * h) * pn + e] = acc;
                 if (own) lsum += lp[j];
                 acc = __expf(lp[j]) * acc + v[j];
+                if (reverse) { if (--sg < 0) { sg = S - 1; --r; } } else { if (++sg == S) { sg = 0; ++r; } }
             }
         }
     }
