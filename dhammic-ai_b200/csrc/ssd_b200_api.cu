@@ -457,8 +457,7 @@ int trapezoid_impl(bool backward, size_t M, int H, const void* dt_raw, const voi
         float* pb = part_ws;
         float* pa = part_ws + nblk * H;
         SSD_LAUNCH(ssd::prof::K_TC_AUX, st, trapezoid_bwd_kernel<T><<<(unsigned)nblk, 256, 0, st>>>((const T*)dt_raw, (const T*)lam_raw, dt_bias, A_log, (const T*)g[0], (const T*)g[1], (const T*)g[2], (const T*)g[3], (T*)out[0], (T*)out[1], pb, pa, M, H));
-        SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<H, 256, 0, st>>>(pb, d_dt_bias, (int)nblk, H));
-        SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<H, 256, 0, st>>>(pa, d_A_log, (int)nblk, H));
+        SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<dim3(H, 2), 256, 0, st>>>(pb, d_dt_bias, (int)nblk, H, pa, d_A_log));
     }
     CUDA_LAUNCH_CHECK("trapezoid");
     return 0;
@@ -719,8 +718,7 @@ int ssd_b200_m3_chain_bwd(const ssd_b200_shape* shape, const float* dw, const fl
     float* pA = ws;
     float* pD = ws + nblk * d.h;
     SSD_LAUNCH(ssd::prof::K_TC_AUX, st, ssd::m3::chain_bwd_kernel<<<(unsigned)nblk, 256, 0, st>>>(dw, dyx, sdot, dt, lam, da, A_head, dlam, ddt, pA, pD, M, d.T, d.h, d.g));
-    SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<d.h, 256, 0, st>>>(pA, dA_head, (int)nblk, d.h));
-    if (dD) SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<d.h, 256, 0, st>>>(pD, dD, (int)nblk, d.h));
+    SSD_LAUNCH(ssd::prof::K_REDUCE, st, ssd::tc::reduce_rows_kernel<<<dim3(d.h, dD ? 2 : 1), 256, 0, st>>>(pA, dA_head, (int)nblk, d.h, pD, dD));
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(SSD_B200_ECUDA, cudaGetErrorString(e));
     return SSD_B200_OK;

@@ -107,6 +107,69 @@ __global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restric
 }
 
 // ------------------------------------------------------------------------------------------
+// The two kernels above in one, for chunk size = tile size (128): reads the per-position log-decay once (dt * A_head,
+// or `a` as given, fp32 or bf16) in the caller's (b,T,h) layout through a shared-memory transpose, scans it inside each
+// 128-tile (warp per head, four 32-lane segments) and writes a_cumsum (b,h,c,l) in natural-log units, the same in
+// log2 units (tcum), dt and skip in (b,h,T) order, and the extreme-decay flag.
+__global__ void __launch_bounds__(256) cumsum_tile_fused_kernel(const void* __restrict__ a, int a_is_bf16,
+                                                                const float* __restrict__ dt, const float* __restrict__ A_head,
+                                                                float* __restrict__ cum, float* __restrict__ tcum,
+                                                                float* __restrict__ dtT, const float* __restrict__ skip,
+                                                                float* __restrict__ skipT, int* __restrict__ extreme, int T, int h) {
+    __shared__ float sa[64][33];
+    __shared__ float sdt[64][33];
+    __shared__ float ssk[64][33];
+    const int kt = blockIdx.x, hg = blockIdx.y, bb = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h0 = hg * 32;
+    const bool head_ok = h0 + lane < h;
+    const float Ah = (!a && head_ok) ? A_head[h0 + lane] : 0.f;
+    float carry[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int half = 0; half < 2; ++half) {  // 64 positions at a time (shared memory), the running sums carried over
+        if (half) __syncthreads();
+#pragma unroll
+        for (int t = warp; t < 64; t += 8) {
+            const size_t i = ((size_t)bb * T + (size_t)kt * LT + half * 64 + t) * h + h0 + lane;
+            float d = 0.f, av = 0.f;
+            if (head_ok) {
+                if (dt) d = dt[i];
+                if (a) av = a_is_bf16 ? __bfloat162float(((const __nv_bfloat16*)a)[i]) : ((const float*)a)[i];
+                else av = d * Ah;
+                if (skip) ssk[t][lane] = skip[i];
+            }
+            sa[t][lane] = av;
+            sdt[t][lane] = d;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i4 = 0; i4 < 4; ++i4) {
+            const int hl = warp * 4 + i4, hh = h0 + hl;
+            if (hh >= h) break;  // warp-uniform
+            const size_t o = ((size_t)bb * h + hh) * T + (size_t)kt * LT + half * 64;  // (b,h,T) = (b,h,c,l), l = 128
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2) {
+                const int tt = s2 * 32 + lane;
+                float incl = sa[tt][hl];
+#pragma unroll
+                for (int of = 1; of < 32; of <<= 1) {
+                    const float u = __shfl_up_sync(0xffffffffu, incl, of);
+                    if (lane >= of) incl += u;
+                }
+                incl += carry[i4];
+                carry[i4] = __shfl_sync(0xffffffffu, incl, 31);
+                cum[o + tt] = incl;
+                const float v = incl * 1.4426950408889634f;
+                tcum[o + tt] = v;
+                const float span = __shfl_sync(0xffffffffu, v, 0) - __shfl_sync(0xffffffffu, v, 31);
+                if (lane == 0 && !(span <= kMaskSafeLog2)) atomicOr(extreme, 1);
+                if (dt) dtT[o + tt] = sdt[tt][hl];
+                if (skip) skipT[o + tt] = ssk[tt][hl];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // Decay gradient of the tensor-core backward, one block per (128-tile, 32 heads, batch).
 // Inputs in (b,h,T) layout (coalesced along t): the per-row gradients g w.r.t. the tile-cumulative
 // log-decay, ddtx = sum_p dX x, dyx = sum_p dy x, and gS, the terms that act through the tile's last row.  Within a tile
@@ -245,9 +308,15 @@ __global__ void __launch_bounds__(256) decay_tile_kernel(DecayTileParams P) {
 }
 
 // out[hh] = sum_r part[r, hh] over `rows` rows, one block per head, fixed summation tree (deterministic).
-__global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restrict__ part, float* __restrict__ out, int rows, int h) {
+// A second (part, out) pair, when given, is reduced by the blocks with blockIdx.y = 1 of the same launch.
+__global__ void __launch_bounds__(256) reduce_rows_kernel(const float* __restrict__ part, float* __restrict__ out, int rows, int h,
+                                                          const float* __restrict__ part2 = nullptr, float* __restrict__ out2 = nullptr) {
     __shared__ float red[8];
     const int hh = blockIdx.x;
+    if (blockIdx.y) {
+        part = part2;
+        out = out2;
+    }
     float s = 0.f;
     for (int r = threadIdx.x; r < rows; r += 256) s += part[(size_t)r * h + hh];
 #pragma unroll

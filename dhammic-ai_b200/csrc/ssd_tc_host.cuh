@@ -154,19 +154,27 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
         if (!aux_valid && cudaMemsetAsync(extreme, 0, 4, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
     }
     if (cudaMemsetAsync(status, 0, 8, st) != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "memset failed");
-    if (!a->cumsum_is_input) {
-        simt::Params P{};
-        P.d = d; P.a = a->a; P.dt = a->a ? nullptr : a->dt; P.A_head = a->A_head; P.cum = a->a_cumsum;
-        P.a_is_bf16 = a->shape.a_dtype == SSD_B200_BF16;
-        size_t sm = (size_t)d.l * (d.h + 1) * 4;
-        if (sm > 48 * 1024 &&
-            cudaFuncSetAttribute(simt::chunk_cumsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
-            SSD_TC_FAIL(SSD_B200_ECUDA, "chunk_cumsum: set shared memory size failed");
-        SSD_LAUNCH(prof::K_CUMSUM, st, simt::chunk_cumsum_kernel<<<dim3(d.c, d.b), simt::NTHR, sm, st>>>(P));
-        SSD_TC_CHECK("chunk_cumsum");
+    if (!a->cumsum_is_input && !aux_valid && d.l == LT) {
+        // chunk = tile: the within-chunk cumulative sums, their log2 copies, the transposes and the flag in one kernel
+        dim3 g(d.T / LT, (d.h + 31) / 32, d.b);
+        SSD_LAUNCH(prof::K_CUMSUM, st, cumsum_tile_fused_kernel<<<g, 256, 0, st>>>(
+            a->a, a->shape.a_dtype == SSD_B200_BF16, a->dt, a->A_head, a->a_cumsum, tcum, dtT, a->skip, skipT, extreme, d.T, d.h));
+        SSD_TC_CHECK("cumsum_tile_fused");
+    } else {
+        if (!a->cumsum_is_input) {
+            simt::Params P{};
+            P.d = d; P.a = a->a; P.dt = a->a ? nullptr : a->dt; P.A_head = a->A_head; P.cum = a->a_cumsum;
+            P.a_is_bf16 = a->shape.a_dtype == SSD_B200_BF16;
+            size_t sm = (size_t)d.l * (d.h + 1) * 4;
+            if (sm > 48 * 1024 &&
+                cudaFuncSetAttribute(simt::chunk_cumsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
+                SSD_TC_FAIL(SSD_B200_ECUDA, "chunk_cumsum: set shared memory size failed");
+            SSD_LAUNCH(prof::K_CUMSUM, st, simt::chunk_cumsum_kernel<<<dim3(d.c, d.b), simt::NTHR, sm, st>>>(P));
+            SSD_TC_CHECK("chunk_cumsum");
+        }
+        if (!aux_valid)
+            if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, a->skip, skipT, extreme, st, err, errn)) return rc;
     }
-    if (!aux_valid)
-        if (int rc = launch_tile_cumsum(d, a->a_cumsum, a->dt, tcum, dtT, a->skip, skipT, extreme, st, err, errn)) return rc;
     if (int rc = set_walk_attrs(err, errn)) return rc;
     WalkParams P{};
     P.skipT = skipT;
@@ -293,8 +301,8 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         SSD_LAUNCH(prof::K_DECAY, st, decay_tile_kernel<<<dim3(nt, (d.h + 31) / 32, d.b), 256, 0, st>>>(P));
         SSD_TC_CHECK("decay_grad");
         if (a->dt && a->A_head) {
-            SSD_LAUNCH(prof::K_REDUCE, st, reduce_rows_kernel<<<d.h, 256, 0, st>>>(P.dAh_part, a->dA_head, d.b * nt, d.h));
-            if (a->D) SSD_LAUNCH(prof::K_REDUCE, st, reduce_rows_kernel<<<d.h, 256, 0, st>>>(P.dD_part, a->dD, d.b * nt, d.h));
+            SSD_LAUNCH(prof::K_REDUCE, st, reduce_rows_kernel<<<dim3(d.h, a->D ? 2 : 1), 256, 0, st>>>(
+                P.dAh_part, a->dA_head, d.b * nt, d.h, P.dD_part, a->dD));
             SSD_TC_CHECK("reduce_batch");
         }
     }
