@@ -28,11 +28,51 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrive from the threads whose `pred` is set, as a predicated instruction: no branch, so a warp in which one lane
+// arrives for all stays converged (a divergent arrive may be scheduled long after the other lanes have moved on).
+__device__ __forceinline__ void mbar_arrive_if(uint64_t* bar, bool pred) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+        ::"r"(smem_u32(bar)), "r"((uint32_t)pred)
+        : "memory");
+}
+// The same, returning the low word of the state token of the arriving thread (0 elsewhere): arithmetic made to depend
+// on it cannot be scheduled ahead of the arrive (an arrive without consumers is otherwise sunk past any amount of
+// register-only work, and the waiter sees the phase that much later).
+__device__ __forceinline__ uint32_t mbar_arrive_if_token(uint64_t* bar, bool pred) {
+    uint32_t lo;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 st;\n\t.reg .b32 hi;\n\t"
+        "setp.ne.b32 p, %2, 0;\n\t"
+        "mov.b64 st, 0;\n\t"
+        "@p mbarrier.arrive.shared::cta.b64 st, [%1];\n\t"
+        "mov.b64 {%0, hi}, st;\n\t}"
+        : "=r"(lo)
+        : "r"(smem_u32(bar)), "r"((uint32_t)pred)
+        : "memory");
+    return lo;
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Non-blocking test of a phase (mbarrier.try_wait may suspend the thread for a system-chosen time when the phase is
+// still open; measured here: a waiter that polled just before the last arrive of OTHER THREADS saw the phase about
+// 0.75 us late, while completions by tcgen05.commit or TMA bytes woke it at once).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
@@ -46,6 +86,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *failed) return false;
+    }
+    *failed = 1;
+    return false;
+}
+
+// The same for phases that other threads complete with mbarrier.arrive: polls without suspending.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* failed, uint32_t limit = 16u * kSpinLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((i & 4095u) == 4095u && *failed) return false;
     }
     *failed = 1;
     return false;
@@ -73,6 +123,27 @@ __device__ __forceinline__ void tma_store_wait_read() {  // smem source may be r
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Four bytes global -> shared without a register in between (generic proxy); wait_all covers the caller's own copies.
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// Per-thread register budget of the calling warpgroup (4 consecutive warps, all of which must execute it): release
+// registers to the pool / take them from it.  The kernel needs a compile-time register cap (__maxnreg__).
+template <int R>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R));
+}
+template <int R>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R));
+}
+
+// Barrier among `count` threads (a multiple of 32) of the CTA; id 0 is __syncthreads.
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -135,6 +206,43 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+// The same products from the low words of the operand descriptors (address and leading offset); the high word
+// (stride offset 1024, version, SWIZZLE_128B) is the same for every operand of these kernels.  An issuing thread
+// derives the descriptor of each K step with one integer add.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr >> 4) & 0x3FFFu) | ((lbo_bytes >> 4) << 16);
+}
+template <bool ACC>
+__device__ __forceinline__ void mma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "n"(ACC ? 1 : 0), "r"(kDescHi)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"((uint32_t)accumulate), "r"(kDescHi)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"((uint32_t)accumulate), "r"(kDescHi)
         : "memory");
 }
 // mbarrier arrives once all tcgen05.mma issued so far by this thread have completed.

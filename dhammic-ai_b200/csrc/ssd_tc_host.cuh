@@ -286,8 +286,8 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.items = nt * d.g * d.b;
         P.extreme = extreme;
         const dim3 grid(std::min(P.items, sm_count()));
-        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<false><<<grid, 512, kBwdSmem, st>>>(P));
-        SSD_LAUNCH(prof::K_TC_BWD_ALT, st, bwd_tile_kernel<true><<<grid, 512, kBwdSmem, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD, st, bwd_tile_kernel<false><<<grid, kBwdThreads, kBwdSmem, st>>>(P));
+        SSD_LAUNCH(prof::K_TC_BWD_ALT, st, bwd_tile_kernel<true><<<grid, kBwdThreads, kBwdSmem, st>>>(P));
         SSD_TC_CHECK("tc_bwd_walk");
     }
     {
