@@ -38,6 +38,11 @@ __device__ __forceinline__ void mbar_arrive_if(uint64_t* bar, bool pred) {
         ::"r"(smem_u32(bar)), "r"((uint32_t)pred)
         : "memory");
 }
+// One arrival for the whole (converged) warp: every lane has fenced its own writes, the warp meets, lane 0 arrives.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+    __syncwarp();
+    mbar_arrive_if(bar, (threadIdx.x & 31) == 0);
+}
 // The same, returning the low word of the state token of the arriving thread (0 elsewhere): arithmetic made to depend
 // on it cannot be scheduled ahead of the arrive (an arrive without consumers is otherwise sunk past any amount of
 // register-only work, and the waiter sees the phase that much later).

@@ -16,9 +16,9 @@
 // Threads: head hs = tid / 256 owns warps 8 hs .. 8 hs + 7 (thread = row, column half); the last warp issues TMA and MMA.
 // mbarriers (index = tile parity, phase = (tile / 2) & 1, unless noted):
 //   bar_ld[s]  TMA bytes of stage s landed                            (index tile % 3, phase (tile / 3) & 1)
-//   bar_u[b]   weighted rows of the tile written, 256 NH arrive        (row warps -> control)
+//   bar_u[b]   weighted rows of the tile written, one arrival per warp (row warps -> control)
 //   bar_m[b]   the MMA of the tile has completed                       (control -> row warps; frees the stage)
-//   bar_a[b]   accumulator of the tile read, 256 NH arrive             (row warps -> control)
+//   bar_a[b]   accumulator of the tile read, one arrival per warp     (row warps -> control)
 #pragma once
 
 namespace ssd {
@@ -61,9 +61,9 @@ __global__ void __launch_bounds__(RevCfg<NH>::THREADS, 1) rev_walk_kernel(const 
         failed = 0;
         for (int s = 0; s < kRevStages; ++s) mbar_init(&bar_ld[s], 1);
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&bar_u[b], 256 * NH);
+            mbar_init(&bar_u[b], 8 * NH);
             mbar_init(&bar_m[b], 1);
-            mbar_init(&bar_a[b], 256 * NH);
+            mbar_init(&bar_a[b], 8 * NH);
         }
         mbar_fence_init();
     }
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(RevCfg<NH>::THREADS, 1) rev_walk_kernel(const 
                 *p = v;
             }
             fence_async_smem();
-            mbar_arrive(&bar_u[it & 1]);
+            mbar_arrive_warp(&bar_u[it & 1]);
         };
         c_i = tcum[(size_t)(nt - 1) * LT + row];
         float Sk = tcum[(size_t)(nt - 1) * LT + LT - 1];
@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(RevCfg<NH>::THREADS, 1) rev_walk_kernel(const 
             tmem_ld32(tm + b * 64 * NH + hs * 64 + lanes + hf * 32, r);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(&bar_a[b]);
+            mbar_arrive_warp(&bar_a[b]);
             {
                 float2* H2 = reinterpret_cast<float2*>(H);
                 const float2 d2 = make_float2(dec, dec);

@@ -13,8 +13,8 @@
 // where the weights are largest), the reverse from the first to the last.
 //
 // A given seed (initial state, or final-state gradient) enters as  exp(total log-decay) * seed.
-// mbarriers, per stage s (phase (it / kSumStages) & 1): bar_ld[s] TMA bytes landed; bar_u[s] rows scaled, 256
-// arrive; bar_m[s] the products of the stage completed (the stage may be reloaded; the last one also releases the
+// mbarriers, per stage s (phase (it / kSumStages) & 1): bar_ld[s] TMA bytes landed; bar_u[s] rows scaled, one
+// arrival per warp; bar_m[s] the products of the stage completed (the stage may be reloaded; the last one also releases the
 // accumulator to the row warps).
 #pragma once
 
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(288, 1) summary_kernel(const __grid_constant__
         failed = 0;
         for (int s = 0; s < kSumStages; ++s) {
             mbar_init(&bar_ld[s], 1);
-            mbar_init(&bar_u[s], 256);
+            mbar_init(&bar_u[s], 8);
             mbar_init(&bar_m[s], 1);
         }
         mbar_fence_init();
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(288, 1) summary_kernel(const __grid_constant__
                 *p = v;
             }
             fence_async_smem();
-            mbar_arrive(&bar_u[s]);
+            mbar_arrive_warp(&bar_u[s]);
         }
         // `run` is now the total log2-decay of the piece
         const int last = nt - 1;

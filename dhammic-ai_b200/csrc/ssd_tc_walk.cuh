@@ -12,10 +12,10 @@
 // mbarriers (phase = tile parity unless noted):
 //   bar_ld[s]  TMA bytes of stage s landed                        (phase = (tile / NST) & 1)
 //   bar_s      S = C.B^T of the tile is in TMEM                   (control -> row warps)
-//   bar_u      weighted rows written, 256 arrive                   (row warps -> control)
-//   bar_g      masked operand written (mode 0), 256 arrive         (row warps -> control)
+//   bar_u      weighted rows written, one arrival per warp         (row warps -> control)
+//   bar_g      masked operand written (mode 0), one per warp       (row warps -> control)
 //   bar_m2     every MMA of the tile has completed                (control -> row warps)
-//   bar_h      accumulators read, new state written, 256 arrive   (row warps -> control)
+//   bar_h      accumulators read, new state written, one per warp (row warps -> control)
 //
 // MODE 0 forward (writes y), MODE 1 states only (stores the state entering every tile, bf16).  The reverse walk
 // of the backward pass is rev_walk_kernel (ssd_tc_revwalk.cuh).
@@ -97,10 +97,10 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
         failed = 0;
         for (int s = 0; s < NST; ++s) mbar_init(&bar_ld[s], 1);
         mbar_init(&bar_s, 1);
-        mbar_init(&bar_u, 256);
-        mbar_init(&bar_g, 256);
+        mbar_init(&bar_u, 8);
+        mbar_init(&bar_g, 8);
         mbar_init(&bar_m2, 1);
-        mbar_init(&bar_h, 256);
+        mbar_init(&bar_h, 8);
         mbar_fence_init();
     }
     if (warp == 8) {
@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 }
             }
             fence_async_smem();
-            mbar_arrive(&bar_u);
+            mbar_arrive_warp(&bar_u);
             if (MODE == 0) {
                 mbar_wait(&bar_s, ph, &failed);
                 tc_fence_after();
@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
             }
             if (MODE == 0) {
                 tc_fence_before();
-                mbar_arrive(&bar_g);
+                mbar_arrive_warp(&bar_g);
             }
 
             mbar_wait(&bar_m2, ph, &failed);
@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
             }
             tc_fence_before();
             fence_async_smem();
-            mbar_arrive(&bar_h);
+            mbar_arrive_warp(&bar_h);
         }
         if (P.out_state) {
             float* o = P.out_state + bh * (size_t)HP * DN;
