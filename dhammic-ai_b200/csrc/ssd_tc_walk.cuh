@@ -1,21 +1,25 @@
 // Tile walk kernels of the tensor-core path (included by ssd_tc.cuh).
 //
 // One CTA per (batch, head) walks the 128-position tiles in order with the recurrent state
-// (64 x 128, fp32) in registers.  Nine warps:
+// (64 x 128, fp32) in registers.  Ten warps:
 //   warps 0-7  "row" warps: thread (row = tid & 127, half = tid >> 7) owns TMEM lane `row` and one
 //              half of the columns of every accumulator; they do the decay-mask epilogue, the output
 //              epilogue and the state update;
-//   warp 8     control: one lane issues every TMA load and every tcgen05.mma.
+//   warp 8     one lane issues every tcgen05.mma (the issuing lane is held about as long as the products take,
+//              so it does nothing else);
+//   warp 9     one lane issues every TMA load and store.
 // Loads are multi-buffered (NST stages), the decay-masked C.B^T operand lives in TMEM (bf16 pairs,
 // A operand of the next MMA), and S = C.B^T of tile k+1 is issued before the epilogue of tile k.
 //
 // mbarriers (phase = tile parity unless noted):
 //   bar_ld[s]  TMA bytes of stage s landed                        (phase = (tile / NST) & 1)
-//   bar_s      S = C.B^T of the tile is in TMEM                   (control -> row warps)
-//   bar_u      weighted rows written, one arrival per warp         (row warps -> control)
-//   bar_g      masked operand written (mode 0), one per warp       (row warps -> control)
-//   bar_m2     every MMA of the tile has completed                (control -> row warps)
-//   bar_h      accumulators read, new state written, one per warp (row warps -> control)
+//   bar_s      S = C.B^T of the tile is in TMEM                   (products -> row warps)
+//   bar_u      weighted rows written, one arrival per warp         (row warps -> products)
+//   bar_g      masked operand written (mode 0), one per warp       (row warps -> products)
+//   bar_mh     Yo and Hl of the tile have completed: the state update runs while Yd does   (products -> row warps)
+//   bar_m2     every MMA of the tile has completed                (products -> row warps, TMA lane: stage free)
+//   bar_h      accumulators read, new state written, one per warp (row warps -> products, TMA lane)
+//   bar_sr     the stores of the tile before have read sH / sY    (TMA lane -> products)
 //
 // MODE 0 forward (writes y), MODE 1 states only (stores the state entering every tile, bf16).  The reverse walk
 // of the backward pass is rev_walk_kernel (ssd_tc_revwalk.cuh).
@@ -67,8 +71,10 @@ struct WalkCfg {
 // MODE 0 exists in two instantiations (EXACT: diagonal mask blocks entry by entry, see kMaskSafeLog2); both are
 // launched and the flag raised by tile_cumsum_kernel decides on the device which of the two does the work.  (As
 // one kernel with two out-of-line bodies the walk was a quarter slower: the call boundary costs it registers.)
+constexpr int kWalkThreads = 320;  // 8 row warps, the product-issue warp, the TMA warp
+
 template <int MODE, bool EXACT = false>
-__global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ WalkParams P) {
+__global__ void __launch_bounds__(kWalkThreads, 1) walk_kernel(const __grid_constant__ WalkParams P) {
     if (MODE == 0 && (P.extreme[0] != 0) != EXACT) return;
     using Cfg = WalkCfg<MODE>;
     constexpr int NST = Cfg::NST;
@@ -83,7 +89,7 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
     float* scum2 = reinterpret_cast<float*>(sH + PANEL + (MODE == 0 ? PANEL : 0));  // [2][128]
     float* sf = scum2 + 2 * LT;                            // [2][128] column factors dt_j 2^(cend - c_j)
     float* sdtc = sf + 2 * LT;                             // [2][128] dt_j (EXACT instantiation only)
-    __shared__ uint64_t bar_ld[3], bar_s, bar_u, bar_g, bar_m2, bar_h;
+    __shared__ uint64_t bar_ld[3], bar_s, bar_u, bar_g, bar_mh, bar_m2, bar_h, bar_sr;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
 
@@ -99,8 +105,10 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
         mbar_init(&bar_s, 1);
         mbar_init(&bar_u, 8);
         mbar_init(&bar_g, 8);
+        mbar_init(&bar_mh, 1);
         mbar_init(&bar_m2, 1);
         mbar_init(&bar_h, 8);
+        mbar_init(&bar_sr, 1);
         mbar_fence_init();
     }
     if (warp == 8) {
@@ -129,16 +137,73 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
     // S double-buffered [0,256), masked operand (bf16 pairs) [256,320), Yd [320,384), Yo [384,448), Hl [448,512)
     const uint32_t tG = tm + 256, tYd = tm + 320, tYo = tm + 384, tHl = tm + 448;
 
+    auto state_row = [&](int it) {  // row of tile `it` of this walk in the [b*nt*h*128][64] state tensor
+        return (int)((((size_t)bb * nt + it) * P.h + hh) * DN);
+    };
     if (warp == 8) {
-        // ------------------------------------------------------------------ control lane
+        // ------------------------------------------------------------------ product lane: every tcgen05.mma
+        if (lane == 0) {
+            // low descriptor words (see desc_lo): K-major operands have leading offset 16, MN-major ones the panel pitch
+            const uint32_t hMN = desc_lo(smem_u32(sH), PANEL), udMN = desc_lo(smem_u32(sUd), PANEL);
+            const uint32_t stK = desc_lo(smem_u32(sStage), 16), stMN = desc_lo(smem_u32(sStage), PANEL);
+            constexpr uint32_t PU = PANEL >> 4, SU = Cfg::STAGE_BYTES >> 4;  // panel and stage pitch in 16-byte units
+            auto offK = [](int kk) { return (uint32_t)(((kk >> 2) * (int)PANEL + (kk & 3) * 32) >> 4); };
+            auto offMN = [](int kk) { return (uint32_t)(kk * 128); };
+            auto issue_S = [&](int it) {  // S = C B^T of tile `it` into TMEM buffer it & 1
+                const uint32_t vK = stK + (uint32_t)(it % NST) * SU, cK = vK + 3 * PU, tS = tm + (it & 1) * 128;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) mma_ss_lo(tS, cK + offK(kk), vK + offK(kk), kIdescS, kk > 0);
+                mma_commit(&bar_s);
+            };
+            for (int it = 0; it < nt; ++it) {
+                const int s = it % NST;
+                const uint32_t ph = it & 1;
+                mbar_wait(&bar_ld[s], (it / NST) & 1, &failed);
+                const uint32_t vMN = stMN + (uint32_t)s * SU, uMN = vMN + 2 * PU, cK = stK + (uint32_t)s * SU + 3 * PU;
+                if (MODE == 0 && it == 0) {
+                    tc_fence_after();
+                    issue_S(0);
+                }
+                if (it > 0) mbar_wait_spin(&bar_h, (it - 1) & 1, &failed);  // new state in sH, accumulators free
+                tc_fence_after();
+                if (MODE == 0) {
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)  // Yo = C H^T : A = C K-major, B = the running state in sH, [n][p] MN-major
+                        mma_ss_lo(tYo, cK + offK(kk), hMN + offMN(kk), kIdescKM, kk > 0);
+                }
+                mbar_wait_spin(&bar_u, ph, &failed);
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)  // Hl = V^T Ud : both MN-major, K = position
+                    mma_ss_lo(tHl, vMN + offMN(kk), udMN + offMN(kk), kIdescMM, kk > 0);
+                // the rows rewrite sH after bar_mh and sY after bar_m2: the stores of the tile before must have read them
+                mbar_wait_spin(&bar_sr, ph, &failed);
+                mma_commit(&bar_mh);  // Yo and Hl done: the state update may start while Yd runs
+                if (MODE == 0) {
+                    mbar_wait_spin(&bar_g, ph, &failed);
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)  // Yd = G' x : A in TMEM (K = j), B = x [j][p] MN-major
+                        mma_ts_lo(tYd, tG + kk * 8, uMN + offMN(kk), kIdescKM, kk > 0);
+                }
+                mma_commit(&bar_m2);
+                if (MODE == 0 && it + 1 < nt) {
+                    mbar_wait(&bar_ld[(it + 1) % NST], ((it + 1) / NST) & 1, &failed);
+                    tc_fence_after();
+                    issue_S(it + 1);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ TMA lane: every load and store
         if (lane == 0) {
             prefetch_tmap(&P.mU);
             prefetch_tmap(&P.mV);
             auto issue_loads = [&](int it) {
-                const int k = it;
                 const int s = it % NST;
                 uint8_t* st = sStage + (size_t)s * Cfg::STAGE_BYTES;
-                const int grow = bb * P.T + k * LT;
+                const int grow = bb * P.T + it * LT;
                 mbar_expect_tx(&bar_ld[s], Cfg::STAGE_BYTES);
                 tma_load_2d(st, &P.mV, &bar_ld[s], gg * DN, grow);
                 tma_load_2d(st + PANEL, &P.mV, &bar_ld[s], gg * DN + 64, grow);
@@ -148,75 +213,28 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     tma_load_2d(st + 4 * PANEL, &P.mC, &bar_ld[s], gg * DN + 64, grow);
                 }
             };
-            auto issue_S = [&](int it) {  // S = C B^T of tile `it` into TMEM buffer it & 1
-                const uint32_t st = smem_u32(sStage + (size_t)(it % NST) * Cfg::STAGE_BYTES);
-                const uint32_t v0 = st, c0 = st + 3 * PANEL, tS = tm + (it & 1) * 128;
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                    mma_ss(tS, smem_desc(c0 + off, 16, 1024), smem_desc(v0 + off, 16, 1024), kIdescS, kk > 0);
-                }
-                mma_commit(&bar_s);
-            };
-            auto state_row = [&](int it) {  // row of tile `it` of this walk in the [b*nt*h*128][64] state tensor
-                const int k = it;
-                return (int)((((size_t)bb * nt + k) * P.h + hh) * DN);
-            };
             for (int it = 0; it < NST - 1 && it < nt; ++it) issue_loads(it);
             if (P.save_states) {  // the seed is the state entering the first tile
                 tma_store_2d(&P.mS, sH, 0, state_row(0));
                 tma_store_commit();
             }
             for (int it = 0; it < nt; ++it) {
-                const int s = it % NST;
-                const uint32_t ph = it & 1;
-                if (it + NST - 1 < nt) issue_loads(it + NST - 1);  // its stage was released by bar_m2 of tile it-1
-                mbar_wait(&bar_ld[s], (it / NST) & 1, &failed);
-                const uint32_t st = smem_u32(sStage + (size_t)s * Cfg::STAGE_BYTES);
-                const uint32_t v0 = st, u0 = st + 2 * PANEL, c0 = st + 3 * PANEL;
-                if (MODE == 0 && it == 0) issue_S(0);
+                if (it + NST - 1 < nt) {
+                    // the stage of tile it-1 is free once every product of that tile has completed
+                    if (it > 0) mbar_wait(&bar_m2, (it - 1) & 1, &failed);
+                    issue_loads(it + NST - 1);
+                }
                 if (it > 0) {
-                    mbar_wait(&bar_h, (it - 1) & 1, &failed);  // new state in sH, y staged, accumulators free
+                    mbar_wait_spin(&bar_h, (it - 1) & 1, &failed);  // new state in sH, y staged
                     if (MODE == 0) tma_store_2d(&P.mY, sY, hh * HP, bb * P.T + (it - 1) * LT);
                     if (P.save_states) tma_store_2d(&P.mS, sH, 0, state_row(it));
                     tma_store_commit();
                 }
-                tc_fence_after();
-                if (MODE == 0) {
-                    // Yo = C H^T : A = C K-major, B = the running state in sH, [n][p] MN-major
-                    const uint32_t h0 = smem_u32(sH);
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        const uint32_t off = (kk >> 2) * PANEL + (kk & 3) * 32;
-                        mma_ss(tYo, smem_desc(c0 + off, 16, 1024), smem_desc(h0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
-                    }
-                }
-                mbar_wait(&bar_u, ph, &failed);
-                tc_fence_after();
-                {
-                    const uint32_t ud0 = smem_u32(sUd);
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)  // Hl = V^T Ud : both MN-major, K = position
-                        mma_ss(tHl, smem_desc(v0 + kk * 2048, PANEL, 1024), smem_desc(ud0 + kk * 2048, PANEL, 1024), kIdescMM, kk > 0);
-                }
-                if (MODE == 0) {
-                    mbar_wait(&bar_g, ph, &failed);
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)  // Yd = G' x : A in TMEM (K = j), B = x [j][p] MN-major
-                        mma_ts(tYd, tG + kk * 8, smem_desc(u0 + kk * 2048, PANEL, 1024), kIdescKM, kk > 0);
-                }
-                tma_store_wait_read();  // the stores issued above have read sH / sY before the row warps rewrite them
-                mma_commit(&bar_m2);
-                if (MODE == 0 && it + 1 < nt) {
-                    mbar_wait(&bar_ld[(it + 1) % NST], ((it + 1) / NST) & 1, &failed);
-                    tc_fence_after();
-                    issue_S(it + 1);
-                }
-                mbar_wait(&bar_m2, ph, &failed);  // stage s and sUd may be overwritten from here on
+                tma_store_wait_read();
+                mbar_arrive(&bar_sr);  // sH and sY may be rewritten
             }
             if (MODE == 0) {
-                mbar_wait(&bar_h, (nt - 1) & 1, &failed);
+                mbar_wait_spin(&bar_h, (nt - 1) & 1, &failed);
                 tma_store_2d(&P.mY, sY, hh * HP, bb * P.T + (nt - 1) * LT);
                 tma_store_commit();
             }
@@ -343,6 +361,21 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                 mbar_arrive_warp(&bar_g);
             }
 
+            // the state update needs Hl only, which completes before Yd: it runs while the rows would wait for Yd
+            mbar_wait(&bar_mh, ph, &failed);
+            tc_fence_after();
+            {
+                uint32_t r[32];
+                tmem_ld32(tHl + lanes + hf * 32, r);
+                const float dec = exp2f(Sk);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    float2* H2 = reinterpret_cast<float2*>(H);
+                    H2[q] = fma2(make_float2(dec, dec), H2[q], reinterpret_cast<const float2*>(r)[q]);
+                }
+                store_half_row(sH, row, hf * 4, H);
+            }
             mbar_wait(&bar_m2, ph, &failed);
 
             tc_fence_after();
@@ -373,18 +406,6 @@ __global__ void __launch_bounds__(288, 1) walk_kernel(const __grid_constant__ Wa
                     for (int q = 0; q < 16; ++q) q2 = fma2(Y2[q], Y2[q], q2);
                     P.ysq[((((size_t)bb * nt + k) * P.h + hh) * 2 + hf) * LT + row] = q2.x + q2.y;
                 }
-            }
-            {
-                uint32_t r[32];
-                tmem_ld32(tHl + lanes + hf * 32, r);
-                const float dec = exp2f(Sk);
-                tmem_ld_wait();
-#pragma unroll
-                for (int q = 0; q < 16; ++q) {
-                    float2* H2 = reinterpret_cast<float2*>(H);
-                    H2[q] = fma2(make_float2(dec, dec), H2[q], reinterpret_cast<const float2*>(r)[q]);
-                }
-                store_half_row(sH, row, hf * 4, H);
             }
             tc_fence_before();
             fence_async_smem();
