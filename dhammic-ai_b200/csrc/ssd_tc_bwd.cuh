@@ -89,7 +89,7 @@ __global__ void __maxnreg__(kBwdRegsLaunch) bwd_tile_kernel(const __grid_constan
     float* swred = sred + 12 * LT;     // [16]: per-warp partials of the S-borne term
     // TMA arrivals (count 1 + bytes): bar_cb, bar_xy[2], bar_hq.  Product completions (tcgen05.commit): bar_m1 (S, dG),
     // bar_m2 (dX1, dX2), bar_m2y (Yo), bar_m2b (dC, dB of the head), bar_m3 (group terms).  Row warps -> control (one arrival per warp):
-    // bar_a (G staged), bar_b (Xd, dYe staged), bar_e (dX1, dX2 read), bar_c (Yo read, dx staged),
+    // bar_a (G staged), bar_b (Xd, dYe staged), bar_e (Yo, dX1, dX2 read), bar_c (dx staged),
     // bar_g1 (sum dS staged), bar_g2 (dC, dB staged).  TMA lane -> product lane: bar_sr (dx store has read its staging
     // panel), bar_sr2 (dC / dB stores have read theirs).
     __shared__ uint64_t bar_cb, bar_xy[2], bar_hq, bar_m1, bar_m2, bar_m2y, bar_m2b, bar_m3, bar_a, bar_b, bar_e, bar_c, bar_g1, bar_g2, bar_sr, bar_sr2;
@@ -98,7 +98,7 @@ __global__ void __maxnreg__(kBwdRegsLaunch) bwd_tile_kernel(const __grid_constan
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // Persistent over work items (tile k, group gg, batch bb).  `hc` counts heads and `ic` items since the start of
-    // the kernel; every buffer index and mbarrier phase derives from them, in the row warps and in the control warp alike.
+    // the kernel; every buffer index and mbarrier phase derives from them, in the row warps and in the control lanes alike.
     const int hpg = P.hpg, ngroups = P.h / P.hpg;
     const int item0 = blockIdx.x;
     const int k0 = item0 % P.nt, gg0 = (item0 / P.nt) % ngroups, bb0 = item0 / (P.nt * ngroups);
