@@ -8,6 +8,7 @@
 //
 // Kernels
 //   tile_cumsum_kernel  a_cumsum (b,h,c,l) -> tcum (b,h,T), dt (b,T,h) -> dtT (b,h,T)
+//   cumsum_tile_fused_kernel  the same together with the cumulative sums themselves, for chunk = 128
 //   walk_kernel<MODE>   one CTA per (batch, head) walks the tiles with the state (64 x 128 fp32)
 //                       in registers:
 //        MODE 0  forward:   Y = ((C B^T) o L) X + diag(e) C H^T (+ D x);  H <- e^{S} H + X^T diag(d) B
@@ -16,12 +17,13 @@
 //                       before it (the quantities the sequence-parallel schedule exchanges): a stream, no recurrence
 //   rev_walk_kernel     reverse walk of the backward pass, Q <- e^{S} Q + dY^T diag(e) C, software-pipelined
 //                       over tiles; reads dY and C only, stores Q_k = dH_{k+1} as bf16
-//   bwd_tile_kernel     one CTA per (batch, tile, group), heads of the group in an inner loop so
+//   bwd_tile_kernel     persistent over (batch, tile, group) items, heads of the group in an inner loop so
 //                       that dB and dC accumulate over heads in TMEM:
 //        dG = dY X^T, dS = dG o L, dX = G^T dY + diag(d) B Q^T, dC += dS B + diag(e) dY H,
 //        dB += dS^T C + diag(d) X Q, and the per-position decay-gradient terms.
 //
-// TMEM lane = tile row; every epilogue is one thread per row (tcgen05.ld 32x32b).
+// TMEM lane = tile row; every epilogue is one thread per row (tcgen05.ld 32x32b).  In the walk and the tile kernels one
+// lane of a warp of its own issues the products and one lane of another warp the TMA copies.
 #pragma once
 #include "ssd_common.cuh"
 #include "ssd_ptx.cuh"
