@@ -9,10 +9,9 @@
 // Kernels
 //   tile_cumsum_kernel  a_cumsum (b,h,c,l) -> tcum (b,h,T), dt (b,T,h) -> dtT (b,h,T)
 //   cumsum_tile_fused_kernel  the same together with the cumulative sums themselves, for chunk = 128
-//   walk_kernel<MODE>   one CTA per (batch, head) walks the tiles with the state (64 x 128 fp32)
-//                       in registers:
-//        MODE 0  forward:   Y = ((C B^T) o L) X + diag(e) C H^T (+ D x);  H <- e^{S} H + X^T diag(d) B
-//        MODE 1  states:    only the recurrence; stores H_k (state entering tile k) as bf16
+//   fwd_walk_kernel     one CTA per (batch, head) walks the tiles with the state (64 x 128 fp32) in registers:
+//                       Y = ((C B^T) o L) X + diag(e) C H^T (+ D x);  H <- e^{S} H + X^T diag(d) B
+//   states_walk_kernel  only the recurrence; stores H_k (state entering tile k) as bf16
 //   summary_kernel      what a whole piece of the sequence adds to the state after it / to the state gradient
 //                       before it (the quantities the sequence-parallel schedule exchanges): a stream, no recurrence
 //   rev_walk_kernel     reverse walk of the backward pass, Q <- e^{S} Q + dY^T diag(e) C, software-pipelined
@@ -407,6 +406,7 @@ __device__ __forceinline__ void store_row32(uint8_t* panel, int row, int col0_in
 }  // namespace tc
 }  // namespace ssd
 #include "ssd_tc_walk.cuh"
+#include "ssd_tc_fwd.cuh"
 #include "ssd_tc_revwalk.cuh"
 #include "ssd_tc_summary.cuh"
 #include "ssd_tc_bwd.cuh"

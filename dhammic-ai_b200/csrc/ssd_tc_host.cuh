@@ -109,9 +109,9 @@ inline int set_walk_attrs(char* err, size_t errn) {
     const unsigned long long bit = 1ull << (dev & 63);
     if (done.load(std::memory_order_acquire) & bit) return 0;
     const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
-    cudaError_t e = cudaFuncSetAttribute(walk_kernel<0, false>, attr, (int)WalkCfg<0>::SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<0, true>, attr, (int)WalkCfg<0>::SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(walk_kernel<1, false>, attr, (int)WalkCfg<1>::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(fwd_walk_kernel<false>, attr, (int)kFwdSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fwd_walk_kernel<true>, attr, (int)kFwdSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(states_walk_kernel, attr, (int)WalkCfg<1>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel<1>, attr, (int)RevCfg<1>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel<2>, attr, (int)RevCfg<2>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<false>, attr, (int)kSumSmem);
@@ -202,8 +202,8 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
         SSD_TC_CHECK("tc_summary_fwd");
         return 0;
     }
-    SSD_LAUNCH(prof::K_TC_FWD, st, (walk_kernel<0, false><<<dim3(d.h, d.b), kWalkThreads, WalkCfg<0>::SMEM, st>>>(P)));
-    SSD_LAUNCH(prof::K_TC_FWD_ALT, st, (walk_kernel<0, true><<<dim3(d.h, d.b), kWalkThreads, WalkCfg<0>::SMEM, st>>>(P)));
+    SSD_LAUNCH(prof::K_TC_FWD, st, (fwd_walk_kernel<false><<<dim3(d.h, d.b), kFwdThreads, kFwdSmem, st>>>(P)));
+    SSD_LAUNCH(prof::K_TC_FWD_ALT, st, (fwd_walk_kernel<true><<<dim3(d.h, d.b), kFwdThreads, kFwdSmem, st>>>(P)));
     SSD_TC_CHECK("tc_fwd_walk");
     if (a->logdecay_total) {
         SSD_LAUNCH(prof::K_CUMSUM, st, simt::logdecay_total_kernel<<<(d.b * d.h + 127) / 128, 128, 0, st>>>(a->a_cumsum, a->logdecay_total, d.b * d.h, d.c, d.l));
@@ -263,7 +263,7 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
         P.mU = mX; P.mV = mB; P.mC = mC; P.mY = mdX; P.mS = mH; P.save_states = 1;
         P.tcum = tcum; P.dtT = dtT; P.D = nullptr; P.seed = a->init; P.out_state = fin; P.status = status;
         P.T = d.T; P.h = d.h; P.hpg = d.hpg; P.nt = nt;
-        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, (walk_kernel<1, false><<<dim3(d.h, d.b), kWalkThreads, WalkCfg<1>::SMEM, st>>>(P)));
+        SSD_LAUNCH(prof::K_TC_BWD_STATE, st, (states_walk_kernel<<<dim3(d.h, d.b), kWalkThreads, WalkCfg<1>::SMEM, st>>>(P)));
         SSD_TC_CHECK("tc_bwd_state");
     }
     {   // reverse walk: gradient of the state leaving every tile, and d(initial state)
