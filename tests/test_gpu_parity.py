@@ -154,6 +154,18 @@ def test_tensor_core_path_with_several_items_per_cta(pkg, cabi, oracle, heads, g
     check_mamba2(pkg, oracle, cfg, TOL_BF16, init=True, dfinal=True, seed=21)
 
 
+@pytest.mark.parametrize("batch,seqlen,heads,groups", [(1, 128, 3, 1), (2, 256, 3, 1), (1, 128, 1, 1), (3, 384, 5, 5),
+                                                       (1, 512, 6, 2), (2, 128, 9, 3), (5, 256, 7, 1), (1, 1024, 10, 2)])
+@pytest.mark.parametrize("states", [False, True])
+def test_tensor_core_path_edge_shapes(pkg, cabi, oracle, batch, seqlen, heads, groups, states):
+    """Shapes at the edges of the tensor-core kernels' bookkeeping: one tile per sequence, one head, an odd number of
+    heads per group (the double-buffered x / dy tiles and the mbarrier phases of the backward tile kernel then start an
+    item on either parity, and the reverse walk runs one head per CTA), fewer work items than SMs."""
+    cfg = replace(pkg.shrink(pkg.CONFIGS[2], batch, seqlen), nheads=heads, ngroups=groups)
+    assert pkg.resolved_path_name(cfg) == "tc"
+    check_mamba2(pkg, oracle, cfg, TOL_BF16, init=states, dfinal=states, seed=33)
+
+
 @pytest.mark.parametrize("h,p,n,g,l,T", [(3, 24, 12, 1, 32, 96), (4, 80, 40, 2, 48, 96), (6, 16, 72, 3, 100, 200),
                                          (2, 128, 130, 1, 64, 64), (2, 8, 8, 2, 16, 16)])
 def test_ragged_shapes_fp32(pkg, cabi, oracle, h, p, n, g, l, T):
