@@ -112,31 +112,35 @@ __global__ void __launch_bounds__(256) tile_cumsum_kernel(const float* __restric
 // or `a` as given, fp32 or bf16) in the caller's (b,T,h) layout through a shared-memory transpose, scans it inside each
 // 128-tile (warp per head, four 32-lane segments) and writes a_cumsum (b,h,c,l) in natural-log units, the same in
 // log2 units (tcum), dt and skip in (b,h,T) order, and the extreme-decay flag.
+// CH positions per pass: 128 (one pass) when there is no skip array to transpose, 64 (two passes, the running sums
+// carried over) with it — three [CH][33] arrays must fit the 48 KB of static shared memory.
+template <int CH, bool SKIP>
 __global__ void __launch_bounds__(256) cumsum_tile_fused_kernel(const void* __restrict__ a, int a_is_bf16,
                                                                 const float* __restrict__ dt, const float* __restrict__ A_head,
                                                                 float* __restrict__ cum, float* __restrict__ tcum,
                                                                 float* __restrict__ dtT, const float* __restrict__ skip,
                                                                 float* __restrict__ skipT, int* __restrict__ extreme, int T, int h) {
-    __shared__ float sa[64][33];
-    __shared__ float sdt[64][33];
-    __shared__ float ssk[64][33];
+    __shared__ float sa[CH][33];
+    __shared__ float sdt[CH][33];
+    __shared__ float ssk[SKIP ? CH : 1][33];
     const int kt = blockIdx.x, hg = blockIdx.y, bb = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h0 = hg * 32;
     const bool head_ok = h0 + lane < h;
     const float Ah = (!a && head_ok) ? A_head[h0 + lane] : 0.f;
     float carry[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int half = 0; half < 2; ++half) {  // 64 positions at a time (shared memory), the running sums carried over
-        if (half) __syncthreads();
 #pragma unroll
-        for (int t = warp; t < 64; t += 8) {
-            const size_t i = ((size_t)bb * T + (size_t)kt * LT + half * 64 + t) * h + h0 + lane;
+    for (int part = 0; part < LT / CH; ++part) {
+        if (part) __syncthreads();
+#pragma unroll
+        for (int t = warp; t < CH; t += 8) {
+            const size_t i = ((size_t)bb * T + (size_t)kt * LT + part * CH + t) * h + h0 + lane;
             float d = 0.f, av = 0.f;
             if (head_ok) {
                 if (dt) d = dt[i];
                 if (a) av = a_is_bf16 ? __bfloat162float(((const __nv_bfloat16*)a)[i]) : ((const float*)a)[i];
                 else av = d * Ah;
-                if (skip) ssk[t][lane] = skip[i];
+                if (SKIP) ssk[t][lane] = skip[i];
             }
             sa[t][lane] = av;
             sdt[t][lane] = d;
@@ -146,9 +150,9 @@ __global__ void __launch_bounds__(256) cumsum_tile_fused_kernel(const void* __re
         for (int i4 = 0; i4 < 4; ++i4) {
             const int hl = warp * 4 + i4, hh = h0 + hl;
             if (hh >= h) break;  // warp-uniform
-            const size_t o = ((size_t)bb * h + hh) * T + (size_t)kt * LT + half * 64;  // (b,h,T) = (b,h,c,l), l = 128
+            const size_t o = ((size_t)bb * h + hh) * T + (size_t)kt * LT + part * CH;  // (b,h,T) = (b,h,c,l), l = 128
 #pragma unroll
-            for (int s2 = 0; s2 < 2; ++s2) {
+            for (int s2 = 0; s2 < CH / 32; ++s2) {
                 const int tt = s2 * 32 + lane;
                 float incl = sa[tt][hl];
 #pragma unroll
@@ -164,7 +168,7 @@ __global__ void __launch_bounds__(256) cumsum_tile_fused_kernel(const void* __re
                 const float span = __shfl_sync(0xffffffffu, v, 0) - __shfl_sync(0xffffffffu, v, 31);
                 if (lane == 0 && !(span <= kMaskSafeLog2)) atomicOr(extreme, 1);
                 if (dt) dtT[o + tt] = sdt[tt][hl];
-                if (skip) skipT[o + tt] = ssk[tt][hl];
+                if (SKIP) skipT[o + tt] = ssk[tt][hl];
             }
         }
     }

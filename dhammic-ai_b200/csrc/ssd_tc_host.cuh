@@ -157,8 +157,12 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
     if (!a->cumsum_is_input && !aux_valid && d.l == LT) {
         // chunk = tile: the within-chunk cumulative sums, their log2 copies, the transposes and the flag in one kernel
         dim3 g(d.T / LT, (d.h + 31) / 32, d.b);
-        SSD_LAUNCH(prof::K_CUMSUM, st, cumsum_tile_fused_kernel<<<g, 256, 0, st>>>(
-            a->a, a->shape.a_dtype == SSD_B200_BF16, a->dt, a->A_head, a->a_cumsum, tcum, dtT, a->skip, skipT, extreme, d.T, d.h));
+        if (a->skip)
+            SSD_LAUNCH(prof::K_CUMSUM, st, (cumsum_tile_fused_kernel<64, true><<<g, 256, 0, st>>>(
+                a->a, a->shape.a_dtype == SSD_B200_BF16, a->dt, a->A_head, a->a_cumsum, tcum, dtT, a->skip, skipT, extreme, d.T, d.h)));
+        else
+            SSD_LAUNCH(prof::K_CUMSUM, st, (cumsum_tile_fused_kernel<128, false><<<g, 256, 0, st>>>(
+                a->a, a->shape.a_dtype == SSD_B200_BF16, a->dt, a->A_head, a->a_cumsum, tcum, dtT, nullptr, nullptr, extreme, d.T, d.h)));
         SSD_TC_CHECK("cumsum_tile_fused");
     } else {
         if (!a->cumsum_is_input) {
