@@ -114,8 +114,10 @@ inline int set_walk_attrs(char* err, size_t errn) {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(states_walk_kernel, attr, (int)WalkCfg<1>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel<1>, attr, (int)RevCfg<1>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(rev_walk_kernel<2>, attr, (int)RevCfg<2>::SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<false>, attr, (int)kSumSmem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<true>, attr, (int)kSumSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<false, 1>, attr, (int)SumCfg<1>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<true, 1>, attr, (int)SumCfg<1>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<false, 2>, attr, (int)SumCfg<2>::SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(summary_kernel<true, 2>, attr, (int)SumCfg<2>::SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel<false>, attr, (int)kBwdSmem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_tile_kernel<true>, attr, (int)kBwdSmem);
     if (e != cudaSuccess) SSD_TC_FAIL(SSD_B200_ECUDA, "set shared memory size: %s", cudaGetErrorString(e));
@@ -202,7 +204,10 @@ inline int forward(const ssd_b200_fwd_args* a, const Dims& d, cudaStream_t st, c
         SummaryParams S{};
         S.mU = P.mU; S.mV = P.mV; S.tcum = tcum; S.dtT = dtT; S.seed = a->init; S.out = a->final_state;
         S.logdecay = a->logdecay_total; S.status = status; S.T = d.T; S.h = d.h; S.hpg = d.hpg; S.nt = d.T / LT;
-        SSD_LAUNCH(prof::K_TC_SUMMARY, st, summary_kernel<false><<<dim3(d.h, d.b), 288, kSumSmem, st>>>(S));
+        if (d.hpg % 2 == 0)  // two heads of a group per CTA share the group's panels
+            SSD_LAUNCH(prof::K_TC_SUMMARY, st, (summary_kernel<false, 2><<<dim3(d.h / 2, d.b), SumCfg<2>::THREADS, SumCfg<2>::SMEM, st>>>(S)));
+        else
+            SSD_LAUNCH(prof::K_TC_SUMMARY, st, (summary_kernel<false, 1><<<dim3(d.h, d.b), SumCfg<1>::THREADS, SumCfg<1>::SMEM, st>>>(S)));
         SSD_TC_CHECK("tc_summary_fwd");
         return 0;
     }
@@ -251,7 +256,10 @@ inline int backward(const ssd_b200_bwd_args* a, const Dims& d, cudaStream_t st, 
             SSD_TC_FAIL(SSD_B200_ECUDA, "tensor map encoding failed");
         S.tcum = tcum; S.dtT = nullptr; S.seed = a->dfinal; S.out = a->dinit; S.logdecay = nullptr; S.status = status;
         S.T = d.T; S.h = d.h; S.hpg = d.hpg; S.nt = nt;
-        SSD_LAUNCH(prof::K_TC_SUMMARY, st, summary_kernel<true><<<dim3(d.h, d.b), 288, kSumSmem, st>>>(S));
+        if (d.hpg % 2 == 0)
+            SSD_LAUNCH(prof::K_TC_SUMMARY, st, (summary_kernel<true, 2><<<dim3(d.h / 2, d.b), SumCfg<2>::THREADS, SumCfg<2>::SMEM, st>>>(S)));
+        else
+            SSD_LAUNCH(prof::K_TC_SUMMARY, st, (summary_kernel<true, 1><<<dim3(d.h, d.b), SumCfg<1>::THREADS, SumCfg<1>::SMEM, st>>>(S)));
         SSD_TC_CHECK("tc_summary_rev");
         return 0;
     }
