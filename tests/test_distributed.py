@@ -183,12 +183,16 @@ def _allreduce_worker(rank, world, port, result_file):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("idx,world,seqlen,tol", [(0, 2, 512, TOL_FP32), (2, 2, 512, TOL_BF16), (2, 4, 1024, TOL_BF16)])
-def test_sequence_parallel_cuda_passes(pkg, cabi, idx, world, seqlen, tol):
+@pytest.mark.parametrize("idx,world,seqlen,tol,heads_groups", [(0, 2, 512, TOL_FP32, None), (2, 2, 512, TOL_BF16, None),
+                                                               (2, 4, 1024, TOL_BF16, None), (2, 2, 512, TOL_BF16, (6, 2))])
+def test_sequence_parallel_cuda_passes(pkg, cabi, idx, world, seqlen, tol, heads_groups):
     """States-only / dinit-only passes, the prefix kernel and the chained full passes on the GPU (the ranks
-    emulated phase by phase in this process), against one call over the whole sequence."""
+    emulated phase by phase in this process), against one call over the whole sequence.  With 6 heads in 2 groups
+    (three heads per group) the summary kernel and the reverse walk run one head per CTA instead of two."""
     D = importlib.import_module("dhammic-ai_b200.distributed")
     cfg = pkg.shrink(pkg.CONFIGS[idx], 1, seqlen)
+    if heads_groups:
+        cfg = replace(cfg, nheads=heads_groups[0], ngroups=heads_groups[1])
     inp = {k: v.cuda() for k, v in pkg.make_inputs(cfg).items()}
     g = torch.Generator().manual_seed(5)
     init = (torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.d_state, generator=g) * 0.3).cuda()
