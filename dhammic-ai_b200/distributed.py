@@ -397,6 +397,7 @@ class _SeqSplitSSD(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, dt, A_head, B, C_, D, chunk, initial_state, S, comm, backend):
+        ctx.set_materialize_grads(False)
         b, T, h, p = x.shape
         n, g = B.shape[3], B.shape[2]
         Ts = T // S
@@ -435,6 +436,8 @@ class _SeqSplitSSD(torch.autograd.Function):
     def backward(ctx, dy, dfinal_global):
         seg, comm, backend, S = ctx.seg, ctx.comm, ctx.backend, ctx.S
         b, T, h, p, n, g = ctx.dims
+        if dy is None:
+            dy = torch.zeros(b, T, h, p, dtype=seg.x.dtype, device=seg.x.device)
         dys = dy.contiguous().to(seg.x.dtype).view(b * S, T // S, h, p)
         # the caller's d final_state belongs to the last piece of the last rank: it seeds that piece's summary and is
         # that piece's own dfinal

@@ -230,6 +230,7 @@ class FusedSSDScan(torch.autograd.Function):
     def forward(ctx, x: Tensor, A: Tensor, B: Tensor, C_: Tensor, chunk_size: int,
                 initial_states: Tensor | None, L_cache_in: Tensor | None,
                 decay_chunk_cache_in: Tensor | None, A_cumsum_cache_in: Tensor | None):
+        ctx.set_materialize_grads(False)  # an unused final state must not cost a zero tensor and a seeded reverse walk
         _check_inputs(x, B, C_)
         assert A.is_cuda
         chunk = int(chunk_size)
@@ -263,6 +264,8 @@ class FusedSSDScan(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dY, dfinal_state, dL_unused, ddecay_chunk_unused, dA_cumsum_unused):
         x, A, B, Cm, init4, cum = ctx.saved_tensors
+        if dY is None:
+            dY = torch.zeros_like(x)
         dx, da, dB, dC, dinit = _run_bwd_operator(ctx.shape_struct, x, A, B, Cm, cum, dY, ctx.states,
                                                   init4 if ctx.has_init else None, dfinal_state, ctx.cached)
         dA = None if da is None else da.to(A.dtype)
@@ -301,6 +304,7 @@ class _SSDMamba2(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dt, A_head, B, C_, D, chunk_size, initial_states):
         _check_inputs(x, B, C_)
+        ctx.set_materialize_grads(False)  # an unused final state must not cost a zero tensor and a seeded reverse walk
         chunk = int(chunk_size)
         xc, Bc, Cc = x.contiguous(), B.contiguous(), C_.contiguous()
         dtc = dt.float().contiguous()
@@ -325,6 +329,8 @@ class _SSDMamba2(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dY, dfinal):
         x, dt, Ah, B, Cm, cum, D, init4 = ctx.saved_tensors
+        if dY is None:
+            dY = torch.zeros_like(x)
         lib = _cabi.load()
         shape = ctx.shape_struct
         dev = x.device
@@ -416,6 +422,7 @@ class _SSDMamba2Gated(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dt, A_head, B, C_, D, z, norm_weight, eps, chunk_size, initial_states):
         _check_inputs(x, B, C_)
+        ctx.set_materialize_grads(False)
         lib = _cabi.load()
         chunk = int(chunk_size)
         xc, Bc, Cc = x.contiguous(), B.contiguous(), C_.contiguous()
@@ -462,6 +469,8 @@ class _SSDMamba2Gated(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout, dfinal):
         x, dt, Ah, B, Cm, cum, D, init4, y, zc, w, rstd = ctx.saved_tensors
+        if dout is None:
+            dout = torch.zeros_like(x)
         lib = _cabi.load()
         dev = x.device
         b, T, h, p = x.shape

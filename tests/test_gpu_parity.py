@@ -444,3 +444,27 @@ def test_scaled_operator_form_matches_mamba2_form(pkg, cabi):
     errs = {k: rel_err(got[k], want[k]) for k in got}
     bad = {k: v for k, v in errs.items() if not v < 1e-3}   # same kernels, same roundings up to the order of the sums
     assert not bad, errs
+
+
+def test_unused_outputs_are_not_materialised(pkg, cabi):
+    """The operators ask autograd not to build zero gradients for outputs the loss does not use: with only y used the
+    backward runs without a final-state gradient (no seed for the reverse walk), with only the final state used it
+    builds the zero dY itself.  Both must equal the calls with explicit zeros."""
+    cfg = pkg.shrink(pkg.CONFIGS[2], 2, 512)
+    inp = {k: v.to(DEV) for k, v in pkg.make_inputs(cfg).items()}
+    names = ("x", "dt", "A_head", "B", "C", "D")
+
+    def grads(use_y, use_final, explicit):
+        lv = {k: inp[k].clone().requires_grad_(True) for k in names}
+        y, fs = pkg.ssd_mamba2(*[lv[k] for k in names], cfg.chunk)
+        gfs = torch.ones_like(fs) * 0.5
+        if explicit:
+            outs, gs = [y, fs], [inp["dy"] if use_y else torch.zeros_like(y), gfs if use_final else torch.zeros_like(fs)]
+        else:
+            outs, gs = ([y] if use_y else []) + ([fs] if use_final else []), ([inp["dy"]] if use_y else []) + ([gfs] if use_final else [])
+        return torch.autograd.grad(outs, list(lv.values()), gs)
+
+    for use_y, use_final in ((True, False), (False, True)):
+        a, b = grads(use_y, use_final, False), grads(use_y, use_final, True)
+        for name, u, v in zip(names, a, b):
+            assert torch.equal(u, v), (use_y, use_final, name)
